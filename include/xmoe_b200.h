@@ -1,0 +1,202 @@
+/*
+ * xmoe_b200.h -- C ABI of the B200 (sm_100a) fused Mixture-of-Experts layer.
+ *
+ * This is the drop-in boundary for the fused-MoE hot path of xCaliber. Each entry point
+ * names the reference interface it replaces (paths are relative to the xCaliber tree).
+ * All pointers are DEVICE pointers unless the name says host. Every function enqueues
+ * on `stream` and returns immediately with one of the XMOE_* status codes below; none
+ * of them allocates device memory (the caller owns the workspace) and none of them
+ * synchronises, except xmoe_forward_host and xmoe_read_status.
+ *
+ * Tensor contracts (row-major, innermost dimension last):
+ *   x               bf16 [N, H]                activations
+ *   router_logits   bf16 [N, E]                gate output (the gate GEMM stays outside, as
+ *                                              in the reference: method.py:240-264)
+ *   w13_packed      u8   [E_tot, 2I, H/2]      NVFP4 E2M1 pairs, low nibble = lower K, rows
+ *                                              [0,I) gate (W1) and [I,2I) up (W3): the
+ *                                              checkpoint layout of xR64FF1.cu:17-20
+ *   w13_sf          u8   prepared by xmoe_prep_nvfp4_sf from E4M3 [E_tot, 2I, H/16]
+ *   w13_gs          f32  [E_tot, 2]            dequant multipliers (gate, up)
+ *   w2_q            u32  [E_tot, H, I/8]       int4 (offset binary), prepared by
+ *                                              xmoe_repack_gptq / xmoe_repack_int4_kmajor
+ *   w2_scale        bf16 [E_tot, I/128, H]     group-128 scales (GPTQ order: group major)
+ *   y               bf16 [N, H]
+ * E_tot = num_experts + num_shared_experts; shared experts are the trailing matrices.
+ */
+#ifndef XMOE_B200_H_
+#define XMOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XMOE_OK 0
+#define XMOE_ERR_ARG 1
+#define XMOE_ERR_SHAPE 2
+#define XMOE_ERR_WORKSPACE 3
+#define XMOE_ERR_CUDA 4
+#define XMOE_ERR_TIMEOUT 5
+#define XMOE_ERR_LIMIT 6
+
+typedef void* xmoe_stream_t; /* a cudaStream_t */
+
+typedef struct xmoe_config {
+    int32_t hidden;             /* H, multiple of 64 */
+    int32_t inter;              /* I, multiple of 32 */
+    int32_t num_experts;        /* E <= 1024 routed experts */
+    int32_t top_k;              /* 1..8 */
+    int32_t num_shared_experts; /* 0..8, every token, weight 1 */
+    int32_t scoring;            /* 0 softmax, 1 sigmoid */
+    int32_t renormalize;        /* normalise the k gate weights to sum 1 (reference: always) */
+    int32_t n_group;            /* 1 = flat routing */
+    int32_t topk_group;
+    int32_t activation;         /* 0 silu(g)*u, 1 clamped swiglu (alpha, limit), 2 gelu_tanh(g)*u */
+    int32_t act_topk_keep;      /* 0 = dense; else entries kept per FF1 output row */
+    int32_t token_tile;         /* 0 = choose from N; else 32, 64 or 128 */
+    float routed_scale;
+    float swiglu_alpha;
+    float swiglu_limit;
+} xmoe_config;
+
+typedef struct xmoe_weights {
+    const void* w13_packed;
+    const void* w13_sf;
+    const float* w13_gs;
+    const void* w2_q;
+    const void* w2_scale;
+    const float* router_bias;  /* f32 [E] selection bias, or NULL */
+    const void* expert_scale;  /* bf16 [E] per-expert output scale, or NULL */
+    const float* sigmoid_lut;  /* f32 [65536], required when n_group > 1 or router_bias != NULL */
+} xmoe_weights;
+
+/* ---- whole layer ------------------------------------------------------------------- */
+
+/* Replaces _C.build_info (vllm/csrc/xr64_abs_bridge.cu:239-241). Static string. */
+const char* xmoe_build_info(void);
+const char* xmoe_status_string(int status);
+
+/* Packed-row capacity and workspace size for a batch of N tokens. The reference allocates
+ * its scratch inside the op with torch::empty (xr64_abs_bridge.cu:160-173); here the
+ * caller owns it so the call allocates nothing and can be captured in a CUDA graph. */
+size_t xmoe_packed_rows(const xmoe_config* cfg, int32_t n_tokens);
+size_t xmoe_workspace_bytes(const xmoe_config* cfg, int32_t n_tokens);
+size_t xmoe_workspace_bytes_host_io(const xmoe_config* cfg, int32_t n_tokens);
+
+/* Replaces _C.forward (xr64_abs_bridge.cu:81-232): router -> route pack -> activation
+ * quantise+scatter -> FF1 -> FF2 -> combine, all on `stream`. N == 0 is a no-op. */
+int xmoe_forward(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* router_logits,
+                 int32_t n_tokens, void* y, void* workspace, size_t workspace_bytes, xmoe_stream_t stream);
+
+/* Same call with HOST x / router_logits / y (pinned memory recommended): copies in, runs,
+ * copies out and synchronises the stream. Workspace: xmoe_workspace_bytes_host_io. */
+int xmoe_forward_host(const xmoe_config* cfg, const xmoe_weights* w, const void* x_host, const void* logits_host,
+                      int32_t n_tokens, void* y_host, void* workspace, size_t workspace_bytes, xmoe_stream_t stream);
+
+/* Synchronises `stream`, then returns the device status word of the last forward on this
+ * workspace (0 = ok; 0x100..0x5ff = a bounded device wait gave up, low byte = CTA;
+ * 0x600 = an expert id outside [0, E) reached the route pack). */
+int xmoe_read_status(const void* workspace, uint32_t* host_out, xmoe_stream_t stream);
+
+/* Variant of _C.forward with routing supplied by the caller, as in the reference's
+ * operator(...) (xR64ABSBinding.cu:8-121): topk_idx i32 / topk_w bf16, both [N, top_k]. */
+int xmoe_forward_routed(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const int32_t* topk_idx,
+                        const void* topk_w, int32_t n_tokens, void* y, void* workspace, size_t workspace_bytes,
+                        xmoe_stream_t stream);
+
+/* Device pointers into a workspace after a forward, for inspection and tests. */
+typedef struct xmoe_workspace_view {
+    uint32_t* status;
+    float* act_scale;      /* [2]: XGS, XGSINV */
+    int32_t* topk_idx;     /* [N, k_eff] */
+    void* topk_w;          /* bf16 [N, k_eff] */
+    int32_t* topk_off;     /* [N, k_eff] */
+    int32_t* topk_row;     /* [N, k_eff] */
+    int32_t* counts;       /* [E_tot] */
+    int32_t* offsets;      /* [E_tot + 1] */
+    int32_t* row_token;    /* [R] */
+    void* row_weight;      /* bf16 [R] */
+    void* xq;              /* u8 [R, H/2] */
+    void* sfx;             /* u8 [R/128, KB, 512] */
+    void* yact;            /* bf16 [R, I] */
+    void* out_rows;        /* bf16 [R, H] */
+    int32_t k_eff;
+    int32_t packed_rows;   /* R */
+    int32_t kb_pad;        /* KB */
+    int32_t token_tile;
+} xmoe_workspace_view;
+int xmoe_workspace_view_get(const xmoe_config* cfg, int32_t n_tokens, void* workspace, size_t workspace_bytes,
+                            xmoe_workspace_view* out);
+
+/* ---- single stages (each replaces one launcher of xR64ABS.cuh:129-199) --------------- */
+
+/* Replaces launch_xr64_abs_topk (xR64ABS.cuh:141-148) / moe_topk_bf16 (sm120a/topk.cuh:25-142).
+ * topk_idx / topk_w have row stride idx_stride >= top_k. */
+int xmoe_router_topk(const void* router_logits, const float* router_bias, const float* sigmoid_lut,
+                     const void* expert_scale, int32_t n_tokens, int32_t num_experts, int32_t top_k,
+                     int32_t idx_stride, int32_t scoring, int32_t renormalize, int32_t n_group, int32_t topk_group,
+                     float routed_scale, int32_t* topk_idx, void* topk_w, xmoe_stream_t stream);
+
+/* Replaces launch_xr64_abs_route_pack (xR64ABS.cuh:150-160) / moe_route_pack_contiguous
+ * (sm120a/preamble.cuh:466-535). scratch: xmoe_route_pack_scratch_bytes. */
+size_t xmoe_route_pack_scratch_bytes(int32_t n_tokens, int32_t num_experts, int32_t num_shared);
+int xmoe_route_pack(int32_t* topk_idx, void* topk_w, int32_t n_tokens, int32_t num_experts, int32_t top_k,
+                    int32_t idx_stride, int32_t num_shared, void* scratch, int32_t* counts, int32_t* offsets,
+                    int32_t* topk_off, int32_t* topk_row, int32_t* row_token, void* row_weight, uint32_t* status,
+                    xmoe_stream_t stream);
+
+/* Replaces moe_act_absmax_partial + moe_act_scale_finalize (sm120a/preamble.cuh:69-128).
+ * scratch: 2 x u32, zero on entry (left zero on exit). act_scale: 2 x f32. */
+int xmoe_act_amax(const void* x, size_t n_elems, uint32_t* scratch, float* act_scale, xmoe_stream_t stream);
+
+/* Replaces launch_xr64_abs_preamble (xR64ABS.cuh:129-139) / moe_act_pack_expert_contiguous
+ * (sm120a/preamble.cuh:549-630). */
+int xmoe_act_quant_pack(const void* x, const float* act_scale, const int32_t* topk_row, int32_t n_tokens,
+                        int32_t hidden, int32_t k_eff, int32_t idx_stride, void* xq, void* sfx,
+                        xmoe_stream_t stream);
+
+/* Replaces launch_xr64_abs_ff1 (xR64ABS.cuh:162-176) / xR64FF1 (xR64FF1FF2/xR64FF1.cu:65). */
+int xmoe_ff1(const void* w13_packed, const void* w13_sf, const float* w13_gs, const void* xq, const void* sfx,
+             const float* act_scale, const int32_t* counts, const int32_t* offsets, const void* row_weight,
+             void* yact, uint32_t* status, int32_t e_tot, int32_t hidden, int32_t inter, int32_t packed_rows,
+             int32_t token_tile, int32_t activation, float alpha, float limit, xmoe_stream_t stream);
+
+/* No counterpart in the reference: keep the `keep` largest |y| of every FF1 output row. */
+int xmoe_act_topk(void* yact, const int32_t* counts, const int32_t* offsets, int32_t e_tot, int32_t inter,
+                  int32_t keep, int32_t packed_rows, xmoe_stream_t stream);
+
+/* Replaces launch_xr64_abs_ff2 (xR64ABS.cuh:178-190) / xR64FF2 (xR64FF1FF2/xR64FF2.cu:81),
+ * minus its reduce tail: rows stay expert-major. */
+int xmoe_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int32_t* counts, const int32_t* offsets,
+             void* out_rows, uint32_t* status, int32_t e_tot, int32_t hidden, int32_t inter, int32_t packed_rows,
+             int32_t token_tile, xmoe_stream_t stream);
+
+/* Replaces the cp.reduce tail of xR64FF2 / the atomicAdd tail of xR64ABSFF2 plus
+ * xR64ABSF32ToBF16 (xr64_abs_bridge.cu:218-229): ordered fp32 sum over the k rows. */
+int xmoe_combine(const void* out_rows, const int32_t* topk_row, int32_t n_tokens, int32_t hidden, int32_t k_eff,
+                 int32_t idx_stride, void* y, xmoe_stream_t stream);
+
+/* ---- weight preparation (load time) ---------------------------------------------------- */
+
+/* E4M3 block scales [n_mats, rows, K/16] -> MMA scale-factor tiles; out bytes:
+ * xmoe_nvfp4_sf_bytes. For w13 pass n_mats = 2*E_tot, rows = I (gate and up are padded
+ * to 128 rows separately). No reference counterpart (its layouts are sm_120 fragments). */
+size_t xmoe_nvfp4_sf_bytes(int32_t n_mats, int32_t rows, int32_t k);
+int xmoe_prep_nvfp4_sf(const void* sf_in, void* sf_out, int32_t n_mats, int32_t rows, int32_t k,
+                       xmoe_stream_t stream);
+
+/* Replaces _C.repack_gptq / launch_xr64_abs_repack_gptq (xR64ABS.cuh:192-198, xr64_abs_bridge.cu:61-79,
+ * xR64ABSRepack.cu:3-24): GPTQ i32 [E, K/8, O] uint4b8 -> u32 [E, O, K/8]. */
+int xmoe_repack_gptq(const void* qweight, void* out, int32_t num_mats, int32_t k, int32_t o, xmoe_stream_t stream);
+/* Same target layout from K-major bytes [.., K/2] with low nibble = lower K. */
+int xmoe_repack_int4_kmajor(const void* w_in, void* out, size_t n_words, xmoe_stream_t stream);
+
+/* Host helper: the 65536-entry sigmoid table indexed by bf16 bit pattern. */
+void xmoe_fill_sigmoid_lut(float* host_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XMOE_B200_H_ */

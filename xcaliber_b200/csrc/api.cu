@@ -1,0 +1,602 @@
+// C ABI of the fused MoE layer: argument checks, workspace carving, TMA tensor-map
+// encoding, and the stage sequence. Mirrors the role of the reference bridge
+// (xFused-XXXX-Kernels/xMoE/xW4A16/sm75/xR64/vllm/csrc/xr64_abs_bridge.cu:81-232) with
+// two differences: scratch is caller-owned instead of torch::empty per call, and
+// errors come back as status codes instead of TORCH_CHECK exceptions.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/xmoe_b200.h"
+#include "common.cuh"
+#include "kernels.h"
+
+using namespace xmoe;
+
+#define XMOE_STR2(x) #x
+#define XMOE_STR(x) XMOE_STR2(x)
+
+namespace {
+
+// ---- driver entry point for tensor-map encoding (no link-time libcuda dependency) -----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+// 2-D row-major tensor [rows, inner] of `elem_bytes` elements, box [box_rows, box_inner].
+int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner,
+                 uint64_t rows, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swz) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return XMOE_ERR_CUDA;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((inner * elem_bytes) & 15u)) return XMOE_ERR_SHAPE;
+    cuuint64_t dims[2] = {inner, rows};
+    cuuint64_t strides[1] = {inner * (uint64_t)elem_bytes};
+    cuuint32_t box[2] = {box_inner, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+int num_sms() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int check_cfg(const xmoe_config* c) {
+    if (!c) return XMOE_ERR_ARG;
+    if (c->hidden <= 0 || c->inter <= 0 || c->num_experts <= 0 || c->top_k <= 0) return XMOE_ERR_ARG;
+    if (c->hidden % 64 || c->inter % 32) return XMOE_ERR_SHAPE;
+    if (c->num_experts > 1024 || c->top_k > 8 || c->top_k > c->num_experts) return XMOE_ERR_SHAPE;
+    if (c->num_shared_experts < 0 || c->num_shared_experts > 8) return XMOE_ERR_SHAPE;
+    if (c->scoring < 0 || c->scoring > 1 || c->activation < 0 || c->activation > 2) return XMOE_ERR_SHAPE;
+    if (c->n_group < 0 || c->n_group > 32) return XMOE_ERR_SHAPE;
+    if (c->token_tile != 0 && c->token_tile != 32 && c->token_tile != 64 && c->token_tile != 128)
+        return XMOE_ERR_SHAPE;
+    if (c->act_topk_keep < 0 || c->act_topk_keep > c->inter) return XMOE_ERR_SHAPE;
+    return XMOE_OK;
+}
+
+int pick_token_tile(const xmoe_config* c, int n) {
+    if (c->token_tile) return c->token_tile;
+    const int k_eff = c->top_k + c->num_shared_experts;
+    const int e_tot = c->num_experts + c->num_shared_experts;
+    const double avg = (double)n * k_eff / e_tot;
+    if (avg > 48.0 || c->num_shared_experts) return n * k_eff > 64 ? 128 : (n > 32 ? 64 : 32);
+    if (avg > 20.0) return 64;
+    return 32;
+}
+
+struct Layout {
+    int k_eff, e_tot, kb_pad, mb, groups, nt, chunks;
+    size_t rows;  // packed-row capacity
+    size_t off_status, off_amax, off_scale, off_topk_idx, off_topk_w, off_topk_off, off_topk_row, off_hist, off_counts,
+        off_offsets, off_row_token, off_row_weight, off_xq, off_sfx, off_yact, off_out, total;
+    size_t off_x_in, off_logits_in, off_y_out, total_host_io;
+};
+
+size_t packed_rows(const xmoe_config* c, int n) {
+    const size_t k_eff = (size_t)c->top_k + c->num_shared_experts;
+    const size_t e_tot = (size_t)c->num_experts + c->num_shared_experts;
+    const size_t assign = (size_t)n * k_eff;
+    const size_t live = assign < e_tot ? assign : e_tot;
+    return align_up(assign + live * 127, 128);
+}
+
+Layout make_layout(const xmoe_config* c, int n) {
+    Layout L;
+    L.k_eff = c->top_k + c->num_shared_experts;
+    L.e_tot = c->num_experts + c->num_shared_experts;
+    L.kb_pad = (int)align_up((size_t)c->hidden / 64, 4);
+    L.mb = (c->inter + 127) / 128;
+    L.groups = (c->inter + 127) / 128;
+    L.nt = pick_token_tile(c, n);
+    L.chunks = route_pack_chunks(n > 0 ? n : 1);
+    L.rows = packed_rows(c, n);
+    size_t o = 0;
+    auto take = [&](size_t bytes) {
+        const size_t at = o;
+        o = align_up(o + bytes, 1024);
+        return at;
+    };
+    L.off_status = take(16);  // status word shares the first KiB with the scalars below
+    L.off_amax = 16;
+    L.off_scale = 32;
+    L.off_topk_idx = take((size_t)n * L.k_eff * 4);
+    L.off_topk_w = take((size_t)n * L.k_eff * 2);
+    L.off_topk_off = take((size_t)n * L.k_eff * 4);
+    L.off_topk_row = take((size_t)n * L.k_eff * 4);
+    L.off_hist = take((size_t)L.chunks * L.e_tot * 4);
+    L.off_counts = take((size_t)L.e_tot * 4);
+    L.off_offsets = take((size_t)(L.e_tot + 1) * 4);
+    L.off_row_token = take(L.rows * 4);
+    L.off_row_weight = take(L.rows * 2);
+    L.off_xq = take(L.rows * (size_t)(c->hidden / 2));
+    L.off_sfx = take((L.rows / 128) * (size_t)L.kb_pad * 512);
+    L.off_yact = take(L.rows * (size_t)c->inter * 2);
+    L.off_out = take(L.rows * (size_t)c->hidden * 2);
+    L.total = o;
+    L.off_x_in = take((size_t)n * c->hidden * 2);
+    L.off_logits_in = take((size_t)n * c->num_experts * 2);
+    L.off_y_out = take((size_t)n * c->hidden * 2);
+    L.total_host_io = o;
+    return L;
+}
+
+int run_ff1(const void* w13_packed, const void* w13_sf, const float* w13_gs, const void* xq, const void* sfx,
+            const float* act_scale, const int32_t* counts, const int32_t* offsets, const void* row_weight, void* yact,
+            uint32_t* status, int e_tot, int H, int I, size_t rows, int nt, int activation, float alpha, float limit,
+            cudaStream_t stream) {
+    Ff1Args a;
+    memset(&a, 0, sizeof(a));
+    int rc = make_tmap_2d(&a.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w13_packed, (uint64_t)H / 2,
+                          (uint64_t)e_tot * 2 * I, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tmap_2d(&a.tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, (uint64_t)H / 2, rows, 128, (uint32_t)nt,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    a.sfw = (const uint8_t*)w13_sf;
+    a.sfx = (const uint8_t*)sfx;
+    a.w13_gs = w13_gs;
+    a.scale = (const ActScale*)act_scale;
+    a.counts = counts;
+    a.offsets = offsets;
+    a.row_weight = row_weight;
+    a.yact = yact;
+    a.status = status;
+    a.E_tot = e_tot;
+    a.H = H;
+    a.I = I;
+    a.kb_pad = (int)align_up((size_t)H / 64, 4);
+    a.mb = (I + 127) / 128;
+    a.nt = nt;
+    a.activation = activation;
+    a.alpha = alpha;
+    a.limit = limit;
+    a.num_sms = num_sms();
+    return launch_ff1(a, stream);
+}
+
+int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int32_t* counts, const int32_t* offsets,
+            void* out_rows, uint32_t* status, int e_tot, int H, int I, size_t rows, int nt, cudaStream_t stream) {
+    Ff2Args a;
+    memset(&a, 0, sizeof(a));
+    int rc = make_tmap_2d(&a.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2_q, (uint64_t)I / 2, (uint64_t)e_tot * H, 64,
+                          128, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    rc = make_tmap_2d(&a.tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64, (uint32_t)nt,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    a.w2_scale = w2_scale;
+    a.counts = counts;
+    a.offsets = offsets;
+    a.out = out_rows;
+    a.status = status;
+    a.E_tot = e_tot;
+    a.H = H;
+    a.I = I;
+    a.groups = (I + 127) / 128;
+    a.nt = nt;
+    a.num_sms = num_sms();
+    return launch_ff2(a, stream);
+}
+
+int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* logits,
+                 const int32_t* ext_idx, const void* ext_w, int n, void* y, void* ws, size_t ws_bytes,
+                 cudaStream_t stream) {
+    int rc = check_cfg(cfg);
+    if (rc) return rc;
+    if (n < 0) return XMOE_ERR_ARG;
+    if (n == 0) return XMOE_OK;
+    if (n > (1 << 22)) return XMOE_ERR_LIMIT;
+    if (!w || !x || !y || !ws || (!logits && !ext_idx)) return XMOE_ERR_ARG;
+    if (!w->w13_packed || !w->w13_sf || !w->w13_gs || !w->w2_q || !w->w2_scale) return XMOE_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(ws) & 1023u) return XMOE_ERR_WORKSPACE;
+    const Layout L = make_layout(cfg, n);
+    if (ws_bytes < L.total) return XMOE_ERR_WORKSPACE;
+    uint8_t* b = (uint8_t*)ws;
+    uint32_t* status = (uint32_t*)(b + L.off_status);
+    uint32_t* amax_scratch = (uint32_t*)(b + L.off_amax);
+    ActScale* scale = (ActScale*)(b + L.off_scale);
+    int32_t* topk_idx = (int32_t*)(b + L.off_topk_idx);
+    void* topk_w = b + L.off_topk_w;
+    int32_t* topk_off = (int32_t*)(b + L.off_topk_off);
+    int32_t* topk_row = (int32_t*)(b + L.off_topk_row);
+    int32_t* counts = (int32_t*)(b + L.off_counts);
+    int32_t* offsets = (int32_t*)(b + L.off_offsets);
+    const int H = cfg->hidden, I = cfg->inter, E = cfg->num_experts;
+
+    if (cudaMemsetAsync(b, 0, 64, stream) != cudaSuccess) return XMOE_ERR_CUDA;
+
+    if (ext_idx) {
+        // caller-supplied routing: widen [N, top_k] to the [N, k_eff] workspace arrays
+        if (cudaMemcpy2DAsync(topk_idx, (size_t)L.k_eff * 4, ext_idx, (size_t)cfg->top_k * 4, (size_t)cfg->top_k * 4, n,
+                              cudaMemcpyDeviceToDevice, stream) != cudaSuccess ||
+            cudaMemcpy2DAsync(topk_w, (size_t)L.k_eff * 2, ext_w, (size_t)cfg->top_k * 2, (size_t)cfg->top_k * 2, n,
+                              cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+            return XMOE_ERR_CUDA;
+    } else {
+        RouterArgs r;
+        r.logits = logits;
+        r.lut = w->sigmoid_lut;
+        r.bias = w->router_bias;
+        r.expert_scale = w->expert_scale;
+        r.topk_idx = topk_idx;
+        r.topk_w = topk_w;
+        r.N = n;
+        r.E = E;
+        r.topk = cfg->top_k;
+        r.idx_stride = L.k_eff;
+        r.scoring = cfg->scoring;
+        r.renorm = cfg->renormalize;
+        r.n_group = cfg->n_group > 0 ? cfg->n_group : 1;
+        r.topk_group = cfg->topk_group;
+        r.routed_scale = cfg->routed_scale;
+        if ((rc = launch_router_topk(r, stream))) return rc;
+    }
+
+    PackArgs p;
+    p.topk_idx = topk_idx;
+    p.topk_w = topk_w;
+    p.N = n;
+    p.E = E;
+    p.topk = cfg->top_k;
+    p.idx_stride = L.k_eff;
+    p.n_shared = cfg->num_shared_experts;
+    p.chunk_hist = (int32_t*)(b + L.off_hist);
+    p.counts = counts;
+    p.offsets = offsets;
+    p.topk_off = topk_off;
+    p.topk_row = topk_row;
+    p.row_token = (int32_t*)(b + L.off_row_token);
+    p.row_weight = b + L.off_row_weight;
+    p.status = status;
+    if ((rc = launch_route_pack(p, stream))) return rc;
+
+    AmaxArgs am;
+    am.x = x;
+    am.n_elems = (size_t)n * H;
+    am.scratch = amax_scratch;
+    am.scale = scale;
+    if ((rc = launch_act_amax(am, stream))) return rc;
+
+    QuantArgs q;
+    q.x = x;
+    q.scale = scale;
+    q.topk_row = topk_row;
+    q.N = n;
+    q.H = H;
+    q.k_eff = L.k_eff;
+    q.idx_stride = L.k_eff;
+    q.xq = b + L.off_xq;
+    q.sfx = b + L.off_sfx;
+    q.kb_pad = L.kb_pad;
+    if ((rc = launch_act_quant(q, stream))) return rc;
+
+    if ((rc = run_ff1(w->w13_packed, w->w13_sf, w->w13_gs, b + L.off_xq, b + L.off_sfx, (const float*)scale, counts,
+                      offsets, b + L.off_row_weight, b + L.off_yact, status, L.e_tot, H, I, L.rows, L.nt,
+                      cfg->activation, cfg->swiglu_alpha, cfg->swiglu_limit, stream)))
+        return rc;
+
+    if (cfg->act_topk_keep > 0 && cfg->act_topk_keep < I) {
+        ActTopkArgs t;
+        t.yact = b + L.off_yact;
+        t.counts = counts;
+        t.offsets = offsets;
+        t.E_tot = L.e_tot;
+        t.I = I;
+        t.keep = cfg->act_topk_keep;
+        t.max_rows = (int)L.rows;
+        if ((rc = launch_act_topk(t, stream))) return rc;
+    }
+
+    if ((rc = run_ff2(w->w2_q, w->w2_scale, b + L.off_yact, counts, offsets, b + L.off_out, status, L.e_tot, H, I,
+                      L.rows, L.nt, stream)))
+        return rc;
+
+    CombineArgs c;
+    c.rows = b + L.off_out;
+    c.topk_row = topk_row;
+    c.y = y;
+    c.N = n;
+    c.H = H;
+    c.k_eff = L.k_eff;
+    c.idx_stride = L.k_eff;
+    return launch_combine(c, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* xmoe_build_info(void) {
+    return "xmoe_b200 fused MoE: sm_100a, tcgen05 NVFP4 W4A4 FF1 + W4A16 FF2, CUDA " XMOE_STR(CUDART_VERSION);
+}
+
+const char* xmoe_status_string(int s) {
+    switch (s) {
+        case XMOE_OK: return "ok";
+        case XMOE_ERR_ARG: return "bad argument (null pointer or non-positive size)";
+        case XMOE_ERR_SHAPE: return "unsupported shape or configuration";
+        case XMOE_ERR_WORKSPACE: return "workspace too small or not 1024-byte aligned";
+        case XMOE_ERR_CUDA: return "CUDA runtime/driver call failed";
+        case XMOE_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+        case XMOE_ERR_LIMIT: return "size beyond the supported maximum";
+        default: return "unknown status";
+    }
+}
+
+size_t xmoe_packed_rows(const xmoe_config* cfg, int32_t n) {
+    if (check_cfg(cfg) || n < 0) return 0;
+    return packed_rows(cfg, n);
+}
+size_t xmoe_workspace_bytes(const xmoe_config* cfg, int32_t n) {
+    if (check_cfg(cfg) || n < 0) return 0;
+    return make_layout(cfg, n).total;
+}
+size_t xmoe_workspace_bytes_host_io(const xmoe_config* cfg, int32_t n) {
+    if (check_cfg(cfg) || n < 0) return 0;
+    return make_layout(cfg, n).total_host_io;
+}
+
+int xmoe_forward(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* router_logits, int32_t n,
+                 void* y, void* workspace, size_t workspace_bytes, xmoe_stream_t stream) {
+    return forward_impl(cfg, w, x, router_logits, nullptr, nullptr, n, y, workspace, workspace_bytes,
+                        (cudaStream_t)stream);
+}
+
+int xmoe_forward_routed(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const int32_t* topk_idx,
+                        const void* topk_w, int32_t n, void* y, void* workspace, size_t workspace_bytes,
+                        xmoe_stream_t stream) {
+    if (!topk_idx || !topk_w) return XMOE_ERR_ARG;
+    return forward_impl(cfg, w, x, nullptr, topk_idx, topk_w, n, y, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int xmoe_forward_host(const xmoe_config* cfg, const xmoe_weights* w, const void* x_host, const void* logits_host,
+                      int32_t n, void* y_host, void* workspace, size_t workspace_bytes, xmoe_stream_t stream) {
+    int rc = check_cfg(cfg);
+    if (rc) return rc;
+    if (n < 0 || !x_host || !logits_host || !y_host || !workspace) return XMOE_ERR_ARG;
+    if (n == 0) return XMOE_OK;
+    const Layout L = make_layout(cfg, n);
+    if (workspace_bytes < L.total_host_io) return XMOE_ERR_WORKSPACE;
+    cudaStream_t s = (cudaStream_t)stream;
+    uint8_t* b = (uint8_t*)workspace;
+    const size_t xb = (size_t)n * cfg->hidden * 2, lb = (size_t)n * cfg->num_experts * 2;
+    if (cudaMemcpyAsync(b + L.off_x_in, x_host, xb, cudaMemcpyHostToDevice, s) != cudaSuccess ||
+        cudaMemcpyAsync(b + L.off_logits_in, logits_host, lb, cudaMemcpyHostToDevice, s) != cudaSuccess)
+        return XMOE_ERR_CUDA;
+    rc = forward_impl(cfg, w, b + L.off_x_in, b + L.off_logits_in, nullptr, nullptr, n, b + L.off_y_out, workspace,
+                      workspace_bytes, s);
+    if (rc) return rc;
+    if (cudaMemcpyAsync(y_host, b + L.off_y_out, xb, cudaMemcpyDeviceToHost, s) != cudaSuccess) return XMOE_ERR_CUDA;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return XMOE_ERR_CUDA;
+    return XMOE_OK;
+}
+
+int xmoe_read_status(const void* workspace, uint32_t* host_out, xmoe_stream_t stream) {
+    if (!workspace || !host_out) return XMOE_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (cudaMemcpyAsync(host_out, workspace, 4, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess)
+        return XMOE_ERR_CUDA;
+    if (*host_out >= 0x100u && *host_out < 0x600u) return XMOE_ERR_TIMEOUT;
+    return XMOE_OK;
+}
+
+int xmoe_workspace_view_get(const xmoe_config* cfg, int32_t n, void* workspace, size_t workspace_bytes,
+                            xmoe_workspace_view* v) {
+    int rc = check_cfg(cfg);
+    if (rc) return rc;
+    if (!workspace || !v || n <= 0) return XMOE_ERR_ARG;
+    const Layout L = make_layout(cfg, n);
+    if (workspace_bytes < L.total) return XMOE_ERR_WORKSPACE;
+    uint8_t* b = (uint8_t*)workspace;
+    v->status = (uint32_t*)(b + L.off_status);
+    v->act_scale = (float*)(b + L.off_scale);
+    v->topk_idx = (int32_t*)(b + L.off_topk_idx);
+    v->topk_w = b + L.off_topk_w;
+    v->topk_off = (int32_t*)(b + L.off_topk_off);
+    v->topk_row = (int32_t*)(b + L.off_topk_row);
+    v->counts = (int32_t*)(b + L.off_counts);
+    v->offsets = (int32_t*)(b + L.off_offsets);
+    v->row_token = (int32_t*)(b + L.off_row_token);
+    v->row_weight = b + L.off_row_weight;
+    v->xq = b + L.off_xq;
+    v->sfx = b + L.off_sfx;
+    v->yact = b + L.off_yact;
+    v->out_rows = b + L.off_out;
+    v->k_eff = L.k_eff;
+    v->packed_rows = (int32_t)L.rows;
+    v->kb_pad = L.kb_pad;
+    v->token_tile = L.nt;
+    return XMOE_OK;
+}
+
+int xmoe_router_topk(const void* router_logits, const float* router_bias, const float* sigmoid_lut,
+                     const void* expert_scale, int32_t n, int32_t E, int32_t top_k, int32_t idx_stride, int32_t scoring,
+                     int32_t renormalize, int32_t n_group, int32_t topk_group, float routed_scale, int32_t* topk_idx,
+                     void* topk_w, xmoe_stream_t stream) {
+    if (n < 0 || !router_logits || !topk_idx || !topk_w) return XMOE_ERR_ARG;
+    if (E <= 0 || E > 1024 || top_k <= 0 || top_k > 8 || top_k > E || idx_stride < top_k) return XMOE_ERR_SHAPE;
+    RouterArgs r;
+    r.logits = router_logits;
+    r.lut = sigmoid_lut;
+    r.bias = router_bias;
+    r.expert_scale = expert_scale;
+    r.topk_idx = topk_idx;
+    r.topk_w = topk_w;
+    r.N = n;
+    r.E = E;
+    r.topk = top_k;
+    r.idx_stride = idx_stride;
+    r.scoring = scoring;
+    r.renorm = renormalize;
+    r.n_group = n_group > 0 ? n_group : 1;
+    r.topk_group = topk_group;
+    r.routed_scale = routed_scale;
+    return launch_router_topk(r, (cudaStream_t)stream);
+}
+
+size_t xmoe_route_pack_scratch_bytes(int32_t n, int32_t E, int32_t n_shared) {
+    return (size_t)route_pack_chunks(n > 0 ? n : 1) * (size_t)(E + n_shared) * 4;
+}
+
+int xmoe_route_pack(int32_t* topk_idx, void* topk_w, int32_t n, int32_t E, int32_t top_k, int32_t idx_stride,
+                    int32_t n_shared, void* scratch, int32_t* counts, int32_t* offsets, int32_t* topk_off,
+                    int32_t* topk_row, int32_t* row_token, void* row_weight, uint32_t* status, xmoe_stream_t stream) {
+    if (n < 0 || !topk_idx || !topk_w || !scratch || !counts || !offsets || !topk_off || !topk_row || !row_token ||
+        !row_weight || !status)
+        return XMOE_ERR_ARG;
+    if (idx_stride < top_k + n_shared) return XMOE_ERR_SHAPE;
+    PackArgs p;
+    p.topk_idx = topk_idx;
+    p.topk_w = topk_w;
+    p.N = n;
+    p.E = E;
+    p.topk = top_k;
+    p.idx_stride = idx_stride;
+    p.n_shared = n_shared;
+    p.chunk_hist = (int32_t*)scratch;
+    p.counts = counts;
+    p.offsets = offsets;
+    p.topk_off = topk_off;
+    p.topk_row = topk_row;
+    p.row_token = row_token;
+    p.row_weight = row_weight;
+    p.status = status;
+    return launch_route_pack(p, (cudaStream_t)stream);
+}
+
+int xmoe_act_amax(const void* x, size_t n_elems, uint32_t* scratch, float* act_scale, xmoe_stream_t stream) {
+    if (!x || !scratch || !act_scale || !n_elems) return XMOE_ERR_ARG;
+    AmaxArgs a;
+    a.x = x;
+    a.n_elems = n_elems;
+    a.scratch = scratch;
+    a.scale = (ActScale*)act_scale;
+    return launch_act_amax(a, (cudaStream_t)stream);
+}
+
+int xmoe_act_quant_pack(const void* x, const float* act_scale, const int32_t* topk_row, int32_t n, int32_t H,
+                        int32_t k_eff, int32_t idx_stride, void* xq, void* sfx, xmoe_stream_t stream) {
+    if (!x || !act_scale || !topk_row || !xq || !sfx || n < 0) return XMOE_ERR_ARG;
+    if (H <= 0 || H % 64 || k_eff <= 0 || idx_stride < k_eff) return XMOE_ERR_SHAPE;
+    QuantArgs q;
+    q.x = x;
+    q.scale = (const ActScale*)act_scale;
+    q.topk_row = topk_row;
+    q.N = n;
+    q.H = H;
+    q.k_eff = k_eff;
+    q.idx_stride = idx_stride;
+    q.xq = xq;
+    q.sfx = sfx;
+    q.kb_pad = (int)align_up((size_t)H / 64, 4);
+    return launch_act_quant(q, (cudaStream_t)stream);
+}
+
+int xmoe_ff1(const void* w13_packed, const void* w13_sf, const float* w13_gs, const void* xq, const void* sfx,
+             const float* act_scale, const int32_t* counts, const int32_t* offsets, const void* row_weight, void* yact,
+             uint32_t* status, int32_t e_tot, int32_t H, int32_t I, int32_t packed_rows_, int32_t token_tile,
+             int32_t activation, float alpha, float limit, xmoe_stream_t stream) {
+    if (!w13_packed || !w13_sf || !w13_gs || !xq || !sfx || !act_scale || !counts || !offsets || !row_weight ||
+        !yact || !status)
+        return XMOE_ERR_ARG;
+    if (e_tot <= 0 || H <= 0 || I <= 0 || packed_rows_ <= 0 || packed_rows_ % 128 || H % 64 || I % 32)
+        return XMOE_ERR_SHAPE;
+    return run_ff1(w13_packed, w13_sf, w13_gs, xq, sfx, act_scale, counts, offsets, row_weight, yact, status, e_tot, H,
+                   I, (size_t)packed_rows_, token_tile, activation, alpha, limit, (cudaStream_t)stream);
+}
+
+int xmoe_act_topk(void* yact, const int32_t* counts, const int32_t* offsets, int32_t e_tot, int32_t I, int32_t keep,
+                  int32_t packed_rows_, xmoe_stream_t stream) {
+    if (!yact || !counts || !offsets) return XMOE_ERR_ARG;
+    ActTopkArgs t;
+    t.yact = yact;
+    t.counts = counts;
+    t.offsets = offsets;
+    t.E_tot = e_tot;
+    t.I = I;
+    t.keep = keep;
+    t.max_rows = packed_rows_;
+    return launch_act_topk(t, (cudaStream_t)stream);
+}
+
+int xmoe_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int32_t* counts, const int32_t* offsets,
+             void* out_rows, uint32_t* status, int32_t e_tot, int32_t H, int32_t I, int32_t packed_rows_,
+             int32_t token_tile, xmoe_stream_t stream) {
+    if (!w2_q || !w2_scale || !yact || !counts || !offsets || !out_rows || !status) return XMOE_ERR_ARG;
+    if (e_tot <= 0 || H <= 0 || I <= 0 || packed_rows_ <= 0 || packed_rows_ % 128 || H % 8 || I % 32)
+        return XMOE_ERR_SHAPE;
+    return run_ff2(w2_q, w2_scale, yact, counts, offsets, out_rows, status, e_tot, H, I, (size_t)packed_rows_,
+                   token_tile, (cudaStream_t)stream);
+}
+
+int xmoe_combine(const void* out_rows, const int32_t* topk_row, int32_t n, int32_t H, int32_t k_eff, int32_t idx_stride,
+                 void* y, xmoe_stream_t stream) {
+    if (!out_rows || !topk_row || !y || n < 0) return XMOE_ERR_ARG;
+    CombineArgs c;
+    c.rows = out_rows;
+    c.topk_row = topk_row;
+    c.y = y;
+    c.N = n;
+    c.H = H;
+    c.k_eff = k_eff;
+    c.idx_stride = idx_stride;
+    return launch_combine(c, (cudaStream_t)stream);
+}
+
+size_t xmoe_nvfp4_sf_bytes(int32_t n_mats, int32_t rows, int32_t k) {
+    if (n_mats <= 0 || rows <= 0 || k <= 0) return 0;
+    return (size_t)n_mats * ((rows + 127) / 128) * align_up((size_t)k / 64, 4) * 512;
+}
+
+int xmoe_prep_nvfp4_sf(const void* sf_in, void* sf_out, int32_t n_mats, int32_t rows, int32_t k, xmoe_stream_t stream) {
+    if (!sf_in || !sf_out) return XMOE_ERR_ARG;
+    if (n_mats <= 0 || rows <= 0 || k <= 0 || k % 64) return XMOE_ERR_SHAPE;
+    return launch_prep_nvfp4_sf(sf_in, sf_out, n_mats, rows, k / 16, (rows + 127) / 128,
+                                (int)align_up((size_t)k / 64, 4), (cudaStream_t)stream);
+}
+
+int xmoe_repack_gptq(const void* qweight, void* out, int32_t num_mats, int32_t k, int32_t o, xmoe_stream_t stream) {
+    if (!qweight || !out) return XMOE_ERR_ARG;
+    if (num_mats <= 0 || k <= 0 || o <= 0) return XMOE_ERR_SHAPE;
+    return launch_repack_gptq(qweight, out, num_mats, k, o, (cudaStream_t)stream);
+}
+
+int xmoe_repack_int4_kmajor(const void* w_in, void* out, size_t n_words, xmoe_stream_t stream) {
+    if (!w_in || !out) return XMOE_ERR_ARG;
+    return launch_repack_kmajor_int4(w_in, out, n_words, (cudaStream_t)stream);
+}
+
+void xmoe_fill_sigmoid_lut(float* host_out) {
+    if (!host_out) return;
+    for (uint32_t i = 0; i < 65536u; ++i) {
+        const uint32_t bits = i << 16;
+        float x;
+        memcpy(&x, &bits, 4);
+        host_out[i] = (float)(1.0 / (1.0 + std::exp(-(double)x)));
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,316 @@
+// FF1: grouped NVFP4 W4A4 gate/up GEMM with a fused SwiGLU * routing-weight epilogue.
+//
+// Math follows the reference FF1 (xFused-NVFP4-Kernels/xMoE/xW4A16/sm120a/xR64FF1FF2/
+// xR64FF1.cu:65-651 and co-design.md:75-90): G = W1 x, U = W3 x with fp32 accumulation
+// over NVFP4 x NVFP4 products, both scaled by weight_global_scale * act_inverse_scale,
+// silu(G) * U in fp32, times the routing weight, rounded to bf16. The weight tensors keep
+// the checkpoint layout the reference documents at xR64FF1.cu:17-20
+// (W13 u8 [E, 2I, H/2], low nibble = lower K). The intermediate stays bf16 because the
+// down projection here is W4A16.
+//
+// B200 design (nothing of the reference's mma.sync structure is kept):
+//   * swap-AB: 128 weight rows are the MMA M operand, NT tokens the N operand, so decode
+//     batches do not pad to 128 rows; gate and up tiles of the same I-range accumulate
+//     into two TMEM accumulators and meet in the same epilogue thread (TMEM lane = I row).
+//   * persistent CTAs, one per SM, walk a tile list (expert, I-tile, token-tile) derived
+//     on the device from the expert histogram.
+//   * warp 0 issues TMA (2-D tiled loads with the 128-byte swizzle for W and X, bulk
+//     copies for the pre-ordered scale factors) into a multi-stage ring; warp 1 copies the
+//     scale factors into TMEM (tcgen05.cp) and issues tcgen05.mma kind::mxf4nvf4
+//     (K = 64 per instruction, 4 per stage); warps 2-5 drain the accumulators with
+//     tcgen05.ld and run the epilogue.
+//   * every mbarrier wait is bounded; on a timeout the CTA flags the status word and
+//     all roles fall through to the common exit, where TMEM is released.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace xmoe {
+
+namespace {
+
+constexpr int kBlockM = 128;          // weight rows per tile (per projection)
+constexpr int kStageKBytes = 128;     // packed bytes along K per stage = 256 K elements
+constexpr int kKPerStage = 256;
+constexpr int kSfStageBytes = 2048;   // 4 K-blocks of 64 x 512-byte scale tiles
+constexpr int kThreads = 192;         // producer warp, MMA warp, 4 epilogue warps
+constexpr int kMaxExperts = 1024 + 8;
+constexpr int kTmemCols = 512;
+
+template <int NT>
+struct Ff1Cfg {
+    static constexpr int kABytes = kBlockM * kStageKBytes;  // 16 KiB per projection
+    static constexpr int kBBytes = NT * kStageKBytes;
+    static constexpr int kStageBytes = 2 * kABytes + kBBytes + 3 * kSfStageBytes;
+    static constexpr int kStages = NT >= 128 ? 4 : (NT >= 64 ? 4 : 5);
+    static constexpr int kAccStages = NT >= 128 ? 1 : 2;
+    static constexpr int kAccCols = 2 * NT;                 // gate + up
+    static constexpr int kSfColsBase = kAccStages * kAccCols;
+    static constexpr int kSfColsPerSlot = 48;               // 4 K-blocks x (gate 4 + up 4 + tokens 4)
+    static_assert(kSfColsBase + 2 * kSfColsPerSlot <= kTmemCols, "TMEM budget");
+    static constexpr int kTxBytes = kStageBytes;
+    static constexpr size_t kSmemBytes = 1024 /*align slack*/ + (size_t)kStages * kStageBytes + 8192;
+};
+
+struct TileInfo {
+    int e, mt, nt_idx, count, row0;
+};
+
+// prefix[e] = number of tiles of experts < e; built once per CTA in shared memory.
+__device__ __forceinline__ void build_tile_prefix(int* prefix, const int32_t* counts, int e_tot, int mt_tiles, int NT) {
+    // one warp, 32 experts per step with a running carry
+    const int lane = threadIdx.x & 31;
+    int carry = 0;
+    for (int base = 0; base < e_tot; base += 32) {
+        const int e = base + lane;
+        const int v = e < e_tot ? ((counts[e] + NT - 1) / NT) * mt_tiles : 0;
+        int incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += o;
+        }
+        if (e < e_tot) prefix[e] = carry + incl - v;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) prefix[e_tot] = carry;
+}
+
+__device__ __forceinline__ TileInfo decode_tile(int item, const int* prefix, const int32_t* counts,
+                                                const int32_t* offsets, int e_tot, int mt_tiles, int NT) {
+    int lo = 0, hi = e_tot;  // largest e with prefix[e] <= item
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (prefix[mid] <= item) lo = mid; else hi = mid;
+    }
+    TileInfo t;
+    t.e = lo;
+    const int local = item - prefix[lo];
+    t.count = counts[lo];
+    const int n_tiles = (t.count + NT - 1) / NT;
+    // token tiles innermost: CTAs of one wave share the weight tile through L2
+    t.mt = local / n_tiles;
+    t.nt_idx = local % n_tiles;
+    t.row0 = offsets[lo] + t.nt_idx * NT;
+    return t;
+}
+
+__device__ __forceinline__ float glu_act(float g, float u, int activation, float alpha, float limit) {
+    if (activation == 1) {  // clamped SwiGLU: (min(g,limit) * sigmoid(alpha*g')) * (clamp(u) + 1)
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        const float s = rcp_approx(1.0f + ex2_approx(-alpha * g * 1.4426950408889634f));
+        return g * s * (u + 1.0f);
+    }
+    if (activation == 2) {  // tanh-approximated GELU gate
+        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        const float t = 1.0f - 2.0f * rcp_approx(1.0f + ex2_approx(2.0f * inner * 1.4426950408889634f));
+        return 0.5f * g * (1.0f + t) * u;
+    }
+    return g * u * rcp_approx(1.0f + ex2_approx(-g * 1.4426950408889634f));
+}
+
+template <int NT>
+__global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_constant__ Ff1Args a) {
+    using Cfg = Ff1Cfg<NT>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* stage_base = smem;
+    uint8_t* tail = smem + (size_t)Cfg::kStages * Cfg::kStageBytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);             // [kStages]
+    uint64_t* empty_bar = full_bar + 8;                                 // [kStages]
+    uint64_t* acc_full = empty_bar + 8;                                 // [2]
+    uint64_t* acc_empty = acc_full + 2;                                 // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    int* prefix = reinterpret_cast<int*>(tail + 256);                   // [e_tot + 1]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int mt_tiles = a.mb;
+    const int k_stages = (a.H + kKPerStage - 1) / kKPerStage;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], 4);
+        }
+        *abort_flag = 0u;
+        mbar_fence_init();
+        prefetch_tmap(&a.tm_w);
+        prefetch_tmap(&a.tm_x);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == 2) build_tile_prefix(prefix, a.counts, a.E_tot, mt_tiles, NT);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = prefix[a.E_tot];
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+                const TileInfo t = decode_tile(item, prefix, a.counts, a.offsets, a.E_tot, mt_tiles, NT);
+                const int gate_row = t.e * 2 * a.I + t.mt * kBlockM;
+                const int up_row = gate_row + a.I;
+                const uint8_t* sfw_g = a.sfw + ((size_t)(t.e * 2 + 0) * a.mb + t.mt) * a.kb_pad * 512;
+                const uint8_t* sfw_u = a.sfw + ((size_t)(t.e * 2 + 1) * a.mb + t.mt) * a.kb_pad * 512;
+                const uint8_t* sfx = a.sfx + (size_t)(t.row0 >> 7) * a.kb_pad * 512;
+                for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                    const int s = it % Cfg::kStages;
+                    const uint32_t ph = (it / Cfg::kStages) & 1u;
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* st = stage_base + (size_t)s * Cfg::kStageBytes;
+                    mbar_expect_tx(&full_bar[s], Cfg::kTxBytes);
+                    tma_load_2d(st, &a.tm_w, ks * kStageKBytes, gate_row, &full_bar[s]);
+                    tma_load_2d(st + Cfg::kABytes, &a.tm_w, ks * kStageKBytes, up_row, &full_bar[s]);
+                    tma_load_2d(st + 2 * Cfg::kABytes, &a.tm_x, ks * kStageKBytes, t.row0, &full_bar[s]);
+                    uint8_t* sf = st + 2 * Cfg::kABytes + Cfg::kBBytes;
+                    tma_load_1d(sf, sfw_g + (size_t)ks * kSfStageBytes, kSfStageBytes, &full_bar[s]);
+                    tma_load_1d(sf + kSfStageBytes, sfw_u + (size_t)ks * kSfStageBytes, kSfStageBytes, &full_bar[s]);
+                    tma_load_1d(sf + 2 * kSfStageBytes, sfx + (size_t)ks * kSfStageBytes, kSfStageBytes, &full_bar[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_nvfp4(kBlockM, NT);
+            uint32_t it = 0, tile_n = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tile_n) {
+                const TileInfo t = decode_tile(item, prefix, a.counts, a.offsets, a.E_tot, mt_tiles, NT);
+                const uint32_t as = tile_n % Cfg::kAccStages;
+                const uint32_t aph = (tile_n / Cfg::kAccStages) & 1u;
+                if (!mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
+                tc_fence_after();
+                const uint32_t acc_gate = tmem_base + as * Cfg::kAccCols;
+                const uint32_t acc_up = acc_gate + NT;
+                const uint32_t sfb_col_off = (uint32_t)(t.row0 & 127) >> 5;  // token rows inside the 128-row SF tile
+                for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                    const int s = it % Cfg::kStages;
+                    const uint32_t ph = (it / Cfg::kStages) & 1u;
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t st = smem_u32(stage_base + (size_t)s * Cfg::kStageBytes);
+                    const uint32_t sf_smem = st + 2 * Cfg::kABytes + Cfg::kBBytes;
+                    const uint32_t sf_tmem = tmem_base + Cfg::kSfColsBase + (it & 1u) * Cfg::kSfColsPerSlot;
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) {
+                        tmem_cp_sf(sf_tmem + kb * 4, umma_desc_sf(sf_smem + kb * 512));
+                        tmem_cp_sf(sf_tmem + 16 + kb * 4, umma_desc_sf(sf_smem + kSfStageBytes + kb * 512));
+                        tmem_cp_sf(sf_tmem + 32 + kb * 4, umma_desc_sf(sf_smem + 2 * kSfStageBytes + kb * 512));
+                    }
+                    const uint64_t da_g = umma_desc_sw128(st);
+                    const uint64_t da_u = umma_desc_sw128(st + Cfg::kABytes);
+                    const uint64_t db = umma_desc_sw128(st + 2 * Cfg::kABytes);
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) {
+                        const uint32_t acc = (ks | kb) ? 1u : 0u;
+                        const uint64_t koff = (uint64_t)(kb * 32 >> 4);  // 32 bytes of packed K per MMA
+                        mma_nvfp4(acc_gate, da_g + koff, db + koff, idesc, sf_tmem + kb * 4,
+                                  sf_tmem + 32 + kb * 4 + sfb_col_off, acc);
+                        mma_nvfp4(acc_up, da_u + koff, db + koff, idesc, sf_tmem + 16 + kb * 4,
+                                  sf_tmem + 32 + kb * 4 + sfb_col_off, acc);
+                    }
+                    tc_commit(&empty_bar[s]);
+                }
+                if (ok) tc_commit(&acc_full[as]);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue -----------------------------------
+        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        const float xgs_inv = a.scale->xgs_inv;
+        uint32_t tile_n = 0;
+        uint16_t* yact = reinterpret_cast<uint16_t*>(a.yact);
+        const uint16_t* row_w = reinterpret_cast<const uint16_t*>(a.row_weight);
+        for (int item = blockIdx.x; item < total_tiles; item += gridDim.x, ++tile_n) {
+            const TileInfo t = decode_tile(item, prefix, a.counts, a.offsets, a.E_tot, mt_tiles, NT);
+            const uint32_t as = tile_n % Cfg::kAccStages;
+            const uint32_t aph = (tile_n / Cfg::kAccStages) & 1u;
+            if (!mbar_wait(&acc_full[as], aph, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
+            tc_fence_after();
+            const float sg = a.w13_gs[t.e * 2 + 0] * xgs_inv;
+            const float su = a.w13_gs[t.e * 2 + 1] * xgs_inv;
+            const int i_idx = t.mt * kBlockM + q * 32 + lane;
+            const bool i_ok = i_idx < a.I;
+            const int n_valid = min(NT, t.count - t.nt_idx * NT);
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + as * Cfg::kAccCols;
+            for (int c0 = 0; c0 < NT; c0 += 32) {
+                if (c0 >= n_valid) break;
+                uint32_t g[32], u[32];
+                tmem_ld32(lane_addr + c0, g);
+                tmem_ld32(lane_addr + NT + c0, u);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int n = c0 + j;
+                    if (n < n_valid && i_ok) {
+                        const int r = t.row0 + n;
+                        const float w = bf16_bits_to_f32(row_w[r]);
+                        const float y = glu_act(__uint_as_float(g[j]) * sg, __uint_as_float(u[j]) * su, a.activation,
+                                                a.alpha, a.limit) * w;
+                        yact[(size_t)r * a.I + i_idx] = (uint16_t)f32_to_bf16_bits(y);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[as]);
+        }
+    }
+
+    // common exit: after an abort give in-flight copies / MMAs a bounded moment to land
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+template <int NT>
+int launch_ff1_nt(const Ff1Args& a, cudaStream_t stream) {
+    using Cfg = Ff1Cfg<NT>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(ff1_nvfp4_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)Cfg::kSmemBytes) != cudaSuccess)
+            return XMOE_ERR_CUDA;
+        attr_set = true;
+    }
+    ff1_nvfp4_kernel<NT><<<a.num_sms, kThreads, Cfg::kSmemBytes, stream>>>(a);
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+}  // namespace
+
+int launch_ff1(const Ff1Args& a, cudaStream_t stream) {
+    if (a.E_tot + 1 > kMaxExperts || a.H % 64 || a.I % 16) return XMOE_ERR_SHAPE;
+    switch (a.nt) {
+        case 32: return launch_ff1_nt<32>(a, stream);
+        case 64: return launch_ff1_nt<64>(a, stream);
+        case 128: return launch_ff1_nt<128>(a, stream);
+        default: return XMOE_ERR_SHAPE;
+    }
+}
+
+}  // namespace xmoe

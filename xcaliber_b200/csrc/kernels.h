@@ -1,0 +1,124 @@
+// Internal launcher interface between the C ABI (api.cu) and the kernel translation
+// units. Plain structs of device pointers and sizes; every launcher enqueues on the
+// given stream and returns an XMOE_* status without synchronising.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+namespace xmoe {
+
+struct RouterArgs {
+    const void* logits;        // bf16 [N, E]
+    const float* lut;          // fp32 [65536] sigmoid table (grouped mode only)
+    const float* bias;         // fp32 [E] selection bias or null
+    const void* expert_scale;  // bf16 [E] or null
+    int32_t* topk_idx;         // [N, idx_stride]
+    void* topk_w;              // bf16 [N, idx_stride]
+    int N, E, topk, idx_stride;
+    int scoring;               // 0 softmax, 1 sigmoid
+    int renorm;
+    int n_group, topk_group;
+    float routed_scale;
+};
+
+struct PackArgs {
+    int32_t* topk_idx;   // [N, idx_stride]; shared-expert slots are filled in here
+    void* topk_w;        // bf16 [N, idx_stride]
+    int N, E, topk, idx_stride, n_shared;
+    int32_t* chunk_hist; // [chunks, E + n_shared]
+    int32_t* counts;     // [E + n_shared]
+    int32_t* offsets;    // [E + n_shared + 1], multiples of 128
+    int32_t* topk_off;   // [N, idx_stride] rank inside the expert
+    int32_t* topk_row;   // [N, idx_stride] absolute packed row
+    int32_t* row_token;  // [R_cap]
+    void* row_weight;    // bf16 [R_cap]
+    uint32_t* status;
+};
+
+struct ActScale {  // same meaning as the reference's MoeActScale (preamble.cuh:12-15)
+    float xgs;      // 2688 / amax
+    float xgs_inv;  // bf16(amax / 2688) widened to fp32
+};
+
+struct AmaxArgs {
+    const void* x;  // bf16 [N, H]
+    size_t n_elems;
+    uint32_t* scratch;  // [2]: running max, ticket (both zero on entry, zero on exit)
+    ActScale* scale;
+};
+
+struct QuantArgs {
+    const void* x;  // bf16 [N, H]
+    const ActScale* scale;
+    const int32_t* topk_row;  // [N, idx_stride]
+    int N, H, k_eff, idx_stride;
+    void* xq;   // u8 [R_cap, H/2]
+    void* sfx;  // u8 [R_cap/128, KB, 512]
+    int kb_pad; // K blocks of 64 per row, rounded up to a multiple of 4
+};
+
+struct Ff1Args {
+    CUtensorMap tm_w;  // u8 [E_tot*2I, H/2], box 128 B x 128 rows, 128-byte swizzle
+    CUtensorMap tm_x;  // u8 [R_cap, H/2], box 128 B x NT rows
+    const uint8_t* sfw;      // [E_tot, 2, MB, KB, 512]
+    const uint8_t* sfx;      // [R_cap/128, KB, 512]
+    const float* w13_gs;     // [E_tot, 2]
+    const ActScale* scale;
+    const int32_t* counts;
+    const int32_t* offsets;
+    const void* row_weight;  // bf16 [R_cap]
+    void* yact;              // bf16 [R_cap, I]
+    uint32_t* status;
+    int E_tot, H, I, kb_pad, mb;  // mb = ceil(I / 128)
+    int nt;                       // token tile: 32, 64 or 128
+    int activation;               // 0 silu*up, 1 clamped swiglu, 2 gelu_tanh*up
+    float alpha, limit;
+    int num_sms;
+};
+
+struct Ff2Args {
+    CUtensorMap tm_w;  // u8 [E_tot*H, I/2], box 64 B x 128 rows, no swizzle
+    CUtensorMap tm_y;  // bf16 [R_cap, I], box 64 elems x NT rows, 128-byte swizzle
+    const void* w2_scale;  // bf16 [E_tot, G, H]
+    const int32_t* counts;
+    const int32_t* offsets;
+    void* out;  // bf16 [R_cap, H]
+    uint32_t* status;
+    int E_tot, H, I, groups;  // groups = ceil(I / 128)
+    int nt;
+    int num_sms;
+};
+
+struct CombineArgs {
+    const void* rows;         // bf16 [R_cap, H]
+    const int32_t* topk_row;  // [N, idx_stride]
+    void* y;                  // bf16 [N, H]
+    int N, H, k_eff, idx_stride;
+};
+
+struct ActTopkArgs {
+    void* yact;  // bf16 [R_cap, I], sparsified in place
+    const int32_t* counts;
+    const int32_t* offsets;
+    int E_tot, I, keep;
+    int max_rows;  // grid bound (R_cap)
+};
+
+int launch_router_topk(const RouterArgs& a, cudaStream_t stream);
+int route_pack_chunks(int N);
+int launch_route_pack(const PackArgs& a, cudaStream_t stream);
+int launch_act_amax(const AmaxArgs& a, cudaStream_t stream);
+int launch_act_quant(const QuantArgs& a, cudaStream_t stream);
+int launch_ff1(const Ff1Args& a, cudaStream_t stream);
+int launch_ff2(const Ff2Args& a, cudaStream_t stream);
+int launch_combine(const CombineArgs& a, cudaStream_t stream);
+int launch_act_topk(const ActTopkArgs& a, cudaStream_t stream);
+int launch_prep_nvfp4_sf(const void* sf_in, void* sf_out, int n_mats, int rows, int kblocks16, int mb, int kb_pad,
+                         cudaStream_t stream);
+int launch_repack_gptq(const void* qweight, void* out, int E, int K, int O, cudaStream_t stream);
+int launch_repack_kmajor_int4(const void* w_in, void* out, size_t n_words, cudaStream_t stream);
+
+}  // namespace xmoe

@@ -1,0 +1,421 @@
+// Router (top-k selection + gate weights) and the deterministic expert-contiguous
+// permutation ("route pack").
+//
+// Semantics follow the reference router xFused-NVFP4-Kernels/xMoE/xW4A16/sm120a/topk.cuh:25-142
+// (selection on the ordered bf16 bit pattern, ties to the lower expert id, slots in
+// descending logit order, weights normalised over the selected k) and the reference
+// permutation .../sm120a/preamble.cuh:466-535 (per expert, rows in ascending token
+// order). The permutation here costs O(N*k) instead of the reference's O(E*N*k): a
+// per-chunk histogram, a scan, and an in-order rank assignment per warp.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace xmoe {
+
+// ------------------------------------------------------------------------------------
+// Flat top-k on bf16 logits (softmax or sigmoid weights). One warp per token, lane l
+// owns experts l + 32*j; every composite key lives in a register, so logits are read
+// from HBM exactly once.
+// ------------------------------------------------------------------------------------
+template <bool SIGMOID>
+__global__ __launch_bounds__(256) void router_topk_flat_kernel(
+    const uint16_t* __restrict__ logits, const uint16_t* __restrict__ expert_scale,
+    int32_t* __restrict__ topk_idx, uint16_t* __restrict__ topk_w,
+    int N, int E, int topk, int idx_stride, float routed_scale, int renorm) {
+    const uint32_t lane = lane_id();
+    const uint32_t token = blockIdx.x * 8u + (threadIdx.x >> 5);
+    if (token >= (uint32_t)N) return;
+    const uint16_t* row = logits + (size_t)token * E;
+
+    uint32_t keys[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const uint32_t e = lane + 32u * j;
+        uint32_t key = 0u;
+        if (e < (uint32_t)E) {
+            const uint32_t raw = row[e];
+            // monotone map of the bf16 bits to unsigned: negatives flip all bits,
+            // non-negatives set the sign bit (+0 ranks above -0).
+            const uint32_t ord = raw ^ ((0u - (raw >> 15)) | 0x8000u);
+            key = (ord << 16) | (0xffffu - e);
+        }
+        keys[j] = key;
+    }
+
+    // Without renormalisation the softmax denominator runs over all E experts.
+    float all_sum = 0.f;
+    if (!SIGMOID && !renorm) {
+        uint32_t best = 0u;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) best = max(best, keys[j]);
+        const uint32_t o1 = __reduce_max_sync(0xffffffffu, best) >> 16;
+        const float x1 = bf16_bits_to_f32((o1 & 0x8000u) ? (o1 & 0x7fffu) : (~o1 & 0xffffu));
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (lane + 32u * j < (uint32_t)E) {
+                const uint32_t o = keys[j] >> 16;
+                const float xe = bf16_bits_to_f32((o & 0x8000u) ? (o & 0x7fffu) : (~o & 0xffffu));
+                all_sum += ex2_approx((xe - x1) * 1.4426950408889634f);
+            }
+        }
+#pragma unroll
+        for (int d = 16; d; d >>= 1) all_sum += __shfl_xor_sync(0xffffffffu, all_sum, d);
+    }
+
+    uint32_t selected = 0u;
+    for (int r = 0; r < topk; ++r) {
+        uint32_t best = 0u;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) best = max(best, keys[j]);
+        const uint32_t winner = __reduce_max_sync(0xffffffffu, best);
+        const uint32_t e = 0xffffu - (winner & 0xffffu);
+        if ((e & 31u) == lane) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if ((uint32_t)j == (e >> 5)) keys[j] = 0u;
+        }
+        if (lane == (uint32_t)r) selected = winner;
+    }
+
+    float x = 0.f;
+    uint32_t expert = 0u;
+    if (lane < (uint32_t)topk) {
+        expert = 0xffffu - (selected & 0xffffu);
+        const uint32_t ord = selected >> 16;
+        const uint32_t raw = (ord & 0x8000u) ? (ord & 0x7fffu) : (~ord & 0xffffu);
+        x = bf16_bits_to_f32(raw);
+    }
+    const float top1 = __shfl_sync(0xffffffffu, x, 0);
+    float w = 0.f;
+    if (lane < (uint32_t)topk) {
+        if (SIGMOID) {
+            w = rcp_approx(1.0f + ex2_approx(-x * 1.4426950408889634f));
+        } else {
+            w = ex2_approx((x - top1) * 1.4426950408889634f);
+        }
+    }
+    float denom = w;
+#pragma unroll
+    for (int d = 16; d; d >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, d);
+    if (lane < (uint32_t)topk) {
+        if (renorm) w *= rcp_approx(denom);
+        else if (!SIGMOID) w *= rcp_approx(all_sum);
+        w *= routed_scale;
+        if (expert_scale) w *= bf16_bits_to_f32(expert_scale[expert]);
+        topk_idx[(size_t)token * idx_stride + lane] = (int32_t)expert;
+        topk_w[(size_t)token * idx_stride + lane] = (uint16_t)f32_to_bf16_bits(w);
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Group-limited sigmoid routing with a selection bias (DeepSeek-V3 style). Not in the
+// reference (its sigmoid mode is flat): score = lut[bf16 logit] (a 65536-entry fp32
+// table of sigmoid, so selection is reproducible bit for bit on any machine), choice
+// score = score + bias[e]; a group's score is the sum of its two best choice scores;
+// the best `topk_group` groups stay; top-k over the choice scores of the remaining
+// experts; ties always go to the lower index. Weights are the unbiased scores of the
+// winners, normalised over k, times routed_scale.
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t warp_max_u64(uint64_t v) {
+#pragma unroll
+    for (int d = 16; d; d >>= 1) {
+        const uint64_t o = __shfl_xor_sync(0xffffffffu, v, d);
+        v = o > v ? o : v;
+    }
+    return v;
+}
+__device__ __forceinline__ uint32_t ordered_f32(float f) {
+    const uint32_t b = __float_as_uint(f);
+    return b ^ ((0u - (b >> 31)) | 0x80000000u);
+}
+__device__ __forceinline__ float unordered_f32(uint32_t o) {
+    const uint32_t b = (o & 0x80000000u) ? (o & 0x7fffffffu) : ~o;
+    return __uint_as_float(b);
+}
+
+__global__ __launch_bounds__(256) void router_topk_grouped_kernel(
+    const uint16_t* __restrict__ logits, const float* __restrict__ lut, const float* __restrict__ bias,
+    const uint16_t* __restrict__ expert_scale, int32_t* __restrict__ topk_idx, uint16_t* __restrict__ topk_w,
+    int N, int E, int topk, int idx_stride, int n_group, int topk_group, float routed_scale, int renorm) {
+    const uint32_t lane = lane_id();
+    const uint32_t token = blockIdx.x * 8u + (threadIdx.x >> 5);
+    if (token >= (uint32_t)N) return;
+    const uint16_t* row = logits + (size_t)token * E;
+    const uint32_t gs = (uint32_t)E / (uint32_t)n_group;
+
+    // key = {ordered choice score, ~expert}; 0 = absent / dead.
+    uint64_t keys[32];
+    float score[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const uint32_t e = lane + 32u * j;
+        keys[j] = 0ull;
+        score[j] = 0.f;
+        if (e < (uint32_t)E) {
+            const float s = lut[row[e]];
+            score[j] = s;
+            const float c = bias ? __fadd_rn(s, bias[e]) : s;
+            keys[j] = ((uint64_t)ordered_f32(c) << 32) | (uint64_t)(0xffffffffu - e);
+        }
+    }
+
+    // group scores -> allowed-group mask (n_group <= 32)
+    uint32_t allowed = 0xffffffffu;
+    if (n_group > 1) {
+        float gscore = 0.f;  // lane g keeps group g's score
+        for (int g = 0; g < n_group; ++g) {
+            uint64_t b1 = 0ull;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const uint32_t e = lane + 32u * j;
+                if (e < (uint32_t)E && e / gs == (uint32_t)g) b1 = keys[j] > b1 ? keys[j] : b1;
+            }
+            const uint64_t w1 = warp_max_u64(b1);
+            uint64_t b2 = 0ull;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const uint32_t e = lane + 32u * j;
+                if (e < (uint32_t)E && e / gs == (uint32_t)g && keys[j] != w1) b2 = keys[j] > b2 ? keys[j] : b2;
+            }
+            const uint64_t w2 = warp_max_u64(b2);
+            const float sum = __fadd_rn(unordered_f32((uint32_t)(w1 >> 32)), unordered_f32((uint32_t)(w2 >> 32)));
+            if (lane == (uint32_t)g) gscore = sum;
+        }
+        allowed = 0u;
+        uint64_t gkey = lane < (uint32_t)n_group
+                            ? (((uint64_t)ordered_f32(gscore) << 32) | (uint64_t)(0xffffffffu - lane))
+                            : 0ull;
+        for (int r = 0; r < topk_group; ++r) {
+            const uint64_t wg = warp_max_u64(gkey);
+            const uint32_t g = 0xffffffffu - (uint32_t)wg;
+            allowed |= 1u << g;
+            if (lane == g) gkey = 0ull;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const uint32_t e = lane + 32u * j;
+            if (e < (uint32_t)E && !((allowed >> (e / gs)) & 1u)) keys[j] = 0ull;
+        }
+    }
+
+    float my_score = 0.f;
+    uint32_t my_expert = 0u;
+    for (int r = 0; r < topk; ++r) {
+        uint64_t best = 0ull;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) best = keys[j] > best ? keys[j] : best;
+        const uint64_t winner = warp_max_u64(best);
+        const uint32_t e = 0xffffffffu - (uint32_t)winner;
+        float s = 0.f;
+        if ((e & 31u) == lane) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if ((uint32_t)j == (e >> 5)) {
+                    keys[j] = 0ull;
+                    s = score[j];
+                }
+        }
+        s = __shfl_sync(0xffffffffu, s, e & 31u);
+        if (lane == (uint32_t)r) {
+            my_score = s;
+            my_expert = e;
+        }
+    }
+    // fixed-order sum over the k slots (slot 0 first) so that the host restatement
+    // can reproduce it with plain fp32 adds.
+    float denom = 0.f;
+    for (int r = 0; r < topk; ++r) denom = __fadd_rn(denom, __shfl_sync(0xffffffffu, my_score, r));
+    if (lane < (uint32_t)topk) {
+        float w = my_score;
+        if (renorm) w = __fdiv_rn(w, denom);
+        w = __fmul_rn(w, routed_scale);
+        if (expert_scale) w *= bf16_bits_to_f32(expert_scale[my_expert]);
+        topk_idx[(size_t)token * idx_stride + lane] = (int32_t)my_expert;
+        topk_w[(size_t)token * idx_stride + lane] = (uint16_t)f32_to_bf16_bits(w);
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Route pack. Chunk = 256 tokens per CTA (8 warps x 32 tokens).
+//   pass A: per-chunk expert histogram -> chunk_hist[chunk][E_tot]
+//   pass B: every CTA rebuilds totals, the 128-row-aligned expert offsets and its own
+//           chunk base, then each warp walks its 32 tokens in order handing out ranks.
+// Shared experts (ids E .. E+n_shared-1) take every token with weight 1.0 in the extra
+// slots topk .. topk+n_shared-1.
+// ------------------------------------------------------------------------------------
+constexpr int kPackChunk = 256;
+constexpr int kMaxEtot = 1024 + 8;
+
+__global__ __launch_bounds__(256) void route_hist_kernel(const int32_t* __restrict__ topk_idx, int N, int E,
+                                                         int topk, int idx_stride, int n_shared,
+                                                         int32_t* __restrict__ chunk_hist) {
+    __shared__ int hist[kMaxEtot];
+    const int e_tot = E + n_shared;
+    for (int e = threadIdx.x; e < e_tot; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    const int t = blockIdx.x * kPackChunk + threadIdx.x;
+    if (t < N) {
+        for (int k = 0; k < topk; ++k) {
+            const int e = topk_idx[(size_t)t * idx_stride + k];
+            if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+        }
+        for (int s = 0; s < n_shared; ++s) atomicAdd(&hist[E + s], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < e_tot; e += blockDim.x) chunk_hist[(size_t)blockIdx.x * e_tot + e] = hist[e];
+}
+
+__global__ __launch_bounds__(256) void route_scatter_kernel(
+    int32_t* __restrict__ topk_idx, uint16_t* __restrict__ topk_w, int N, int E, int topk, int idx_stride,
+    int n_shared, const int32_t* __restrict__ chunk_hist, int n_chunks, int32_t* __restrict__ counts,
+    int32_t* __restrict__ offsets, int32_t* __restrict__ topk_off, int32_t* __restrict__ topk_row,
+    int32_t* __restrict__ row_token, uint16_t* __restrict__ row_weight, uint32_t* __restrict__ status) {
+    __shared__ int total[kMaxEtot];
+    __shared__ int before_chunk[kMaxEtot];
+    __shared__ int start[kMaxEtot + 1];
+    __shared__ int warp_base[8][kMaxEtot];
+    __shared__ int carry;
+    const int e_tot = E + n_shared;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunk = blockIdx.x;
+
+    // totals and this chunk's base (tokens of earlier chunks come first)
+    for (int e = threadIdx.x; e < e_tot; e += blockDim.x) {
+        int tot = 0, before = 0;
+        for (int c = 0; c < n_chunks; ++c) {
+            const int h = chunk_hist[(size_t)c * e_tot + e];
+            tot += h;
+            if (c < chunk) before += h;
+        }
+        total[e] = tot;
+        before_chunk[e] = before;
+        for (int w = 0; w < 8; ++w) warp_base[w][e] = 0;
+    }
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+
+    // exclusive scan of round_up(total, 128) -> start[]
+    if (warp == 0) {
+        for (int base = 0; base < e_tot; base += 32) {
+            const int e = base + lane;
+            const int v = e < e_tot ? ((total[e] + 127) & ~127) : 0;
+            int incl = v;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += o;
+            }
+            const int c = carry;
+            if (e < e_tot) start[e] = c + incl - v;
+            __syncwarp();
+            if (lane == 31) carry = c + incl;
+            __syncwarp();
+        }
+        if (lane == 0) start[e_tot] = carry;
+    }
+    __syncthreads();
+    if (chunk == 0) {
+        for (int e = threadIdx.x; e < e_tot; e += blockDim.x) {
+            counts[e] = total[e];
+            offsets[e] = start[e];
+        }
+        if (threadIdx.x == 0) offsets[e_tot] = start[e_tot];
+    }
+
+    // per-warp histograms of this chunk (built in place, then turned into bases)
+    const int t_mine = chunk * kPackChunk + threadIdx.x;
+    if (t_mine < N) {
+        for (int k = 0; k < topk; ++k) {
+            const int e = topk_idx[(size_t)t_mine * idx_stride + k];
+            if (e >= 0 && e < E) atomicAdd(&warp_base[warp][e], 1);
+            else atomicExch(status, 0x600u);  // expert id outside [0, E)
+        }
+        for (int s = 0; s < n_shared; ++s) atomicAdd(&warp_base[warp][E + s], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < e_tot; e += blockDim.x) {
+        int run = before_chunk[e];  // rows of earlier chunks
+        for (int w = 0; w < 8; ++w) {
+            const int h = warp_base[w][e];
+            warp_base[w][e] = run;
+            run += h;
+        }
+    }
+    __syncthreads();
+
+    // in-order rank assignment: a warp walks its 32 tokens; lane k owns slot k.
+    const int k_eff = topk + n_shared;
+    for (int i = 0; i < 32; ++i) {
+        const int t = chunk * kPackChunk + warp * 32 + i;
+        if (t >= N) break;
+        if (lane < k_eff) {
+            int e;
+            uint16_t w;
+            if (lane < topk) {
+                e = topk_idx[(size_t)t * idx_stride + lane];
+                w = topk_w[(size_t)t * idx_stride + lane];
+            } else {
+                e = E + (lane - topk);
+                w = 0x3f80u;  // 1.0 in bf16
+                topk_idx[(size_t)t * idx_stride + lane] = e;
+                topk_w[(size_t)t * idx_stride + lane] = w;
+            }
+            if (e >= 0 && e < e_tot) {
+                const int p = warp_base[warp][e];
+                warp_base[warp][e] = p + 1;
+                const int r = start[e] + p;
+                topk_off[(size_t)t * idx_stride + lane] = p;
+                topk_row[(size_t)t * idx_stride + lane] = r;
+                row_token[r] = t;
+                row_weight[r] = w;
+            } else {
+                topk_off[(size_t)t * idx_stride + lane] = -1;
+                topk_row[(size_t)t * idx_stride + lane] = -1;
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// ---- host launchers ---------------------------------------------------------------
+int launch_router_topk(const RouterArgs& a, cudaStream_t stream) {
+    if (a.N <= 0) return XMOE_OK;
+    const int k_eff = a.idx_stride;
+    dim3 grid((a.N + 7) / 8), block(256);
+    const uint16_t* logits = (const uint16_t*)a.logits;
+    const uint16_t* es = (const uint16_t*)a.expert_scale;
+    if (a.n_group > 1 || a.bias != nullptr) {
+        if (a.scoring != 1 || a.lut == nullptr) return XMOE_ERR_SHAPE;
+        if (a.n_group < 1 || a.n_group > 32 || a.E % a.n_group) return XMOE_ERR_SHAPE;
+        if (a.n_group > 1 && (a.E / a.n_group < 2 || a.topk_group < 1 || a.topk_group > a.n_group ||
+                              a.topk > a.topk_group * (a.E / a.n_group)))
+            return XMOE_ERR_SHAPE;
+        router_topk_grouped_kernel<<<grid, block, 0, stream>>>(logits, a.lut, a.bias, es, a.topk_idx,
+                                                               (uint16_t*)a.topk_w, a.N, a.E, a.topk, k_eff,
+                                                               a.n_group, a.topk_group, a.routed_scale, a.renorm);
+    } else if (a.scoring == 1) {
+        router_topk_flat_kernel<true><<<grid, block, 0, stream>>>(logits, es, a.topk_idx, (uint16_t*)a.topk_w,
+                                                                  a.N, a.E, a.topk, k_eff, a.routed_scale, a.renorm);
+    } else {
+        router_topk_flat_kernel<false><<<grid, block, 0, stream>>>(logits, es, a.topk_idx, (uint16_t*)a.topk_w,
+                                                                   a.N, a.E, a.topk, k_eff, a.routed_scale, a.renorm);
+    }
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+int route_pack_chunks(int N) { return (N + kPackChunk - 1) / kPackChunk; }
+
+int launch_route_pack(const PackArgs& a, cudaStream_t stream) {
+    if (a.N <= 0) return XMOE_OK;
+    if (a.E + a.n_shared > kMaxEtot || a.topk + a.n_shared > 32) return XMOE_ERR_SHAPE;
+    const int chunks = route_pack_chunks(a.N);
+    route_hist_kernel<<<chunks, 256, 0, stream>>>(a.topk_idx, a.N, a.E, a.topk, a.idx_stride, a.n_shared,
+                                                  a.chunk_hist);
+    route_scatter_kernel<<<chunks, 256, 0, stream>>>(a.topk_idx, (uint16_t*)a.topk_w, a.N, a.E, a.topk,
+                                                     a.idx_stride, a.n_shared, a.chunk_hist, chunks, a.counts,
+                                                     a.offsets, a.topk_off, a.topk_row, a.row_token,
+                                                     (uint16_t*)a.row_weight, a.status);
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+}  // namespace xmoe
