@@ -1,0 +1,360 @@
+"""Benchmark of the fused MoE layer (one "step" = one layer call over one batch of tokens).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload mixtral|qwen3|gptoss|dsv3|toy] [--tokens T]
+
+Default workload: the Mixtral-8x7B-shaped layer (H 4096, I 14336, 8 experts, top-2) at 4096
+tokens per GPU, synthetic seeded inputs, weights quantised to NVFP4 (FF1) / int4-g128 (FF2).
+With N > 1 (launched by torch.distributed.run, one rank per GPU) experts are sharded
+expert-parallel and every rank brings its own 4096 tokens (weak scaling).
+
+Prints ONE JSON line on rank 0: tokens/s with inputs resident in HBM (`value`), the same
+through the host-buffer API with copies inside the timed region (`e2e`), a roofline object
+for the dominant kernel (per-stage CUDA-event times recorded on the launching stream during
+the timed steps), clocks sampled during the timed region, and - at N = 1 - the CPU oracle
+timed on the host cores on a bounded sample (`cpu_baseline`). `--impl reference` times only
+that CPU path (the reference project has no CPU or B200 implementation of its own).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from xcaliber_b200 import synth  # noqa: E402
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+NVFP4_NOMINAL_TFLOPS = 9000.0  # dense NVFP4 spec figure; there is no measured FP4 peak on this pool
+SMI_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+def measured_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        d["source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi polled every 100 ms while the timed region runs (read-only query)."""
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = ROOT / "gpurun_out" / f"clocks_rank{gpu_index}.csv"
+
+    def start(self):
+        try:
+            self.path.parent.mkdir(exist_ok=True)
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={SMI_QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.fh,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.fh.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.path.read_text().splitlines():
+            f = [c.strip() for c in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_oracle_tokens_per_s(shape, weights_cpu, sample_tokens: int, steps: int, warmup: int):
+    """The dequantise-then-bf16-matmul CPU path on a bounded sample of the workload."""
+    from oracle import moe_oracle as O  # the checker, used here only as the timed CPU baseline
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    x, logits = synth.make_inputs(shape, weights_cpu, sample_tokens, seed=0)
+    for _ in range(warmup):
+        O.layer_forward(x, logits, weights_cpu, shape, precision="bf16")
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        O.layer_forward(x, logits, weights_cpu, shape, precision="bf16")
+        times.append(time.perf_counter() - t0)
+    return sample_tokens / statistics.median(times), cores, statistics.median(times)
+
+
+def to_cpu_weights(w):
+    return synth.LayerWeights(*[None if t is None else t.cpu() for t in (
+        w.w13_packed, w.w13_scale, w.w13_gs, w.w2_qweight, w.w2_scales, w.router_weight, w.router_bias, w.logit_bias)])
+
+
+def router_on_cpu(w):
+    """Only the router parts (what make_inputs needs), on the CPU."""
+    return synth.LayerWeights(None, None, None, None, None, w.router_weight.cpu(), None,
+                              None if w.logit_bias is None else w.logit_bias.cpu())
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="mixtral", choices=sorted(synth.SHAPES))
+    ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU per step")
+    ap.add_argument("--cpu-sample-tokens", type=int, default=128)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    shape = synth.SHAPES[args.workload]
+    n = args.tokens
+    workload = f"{shape.name}-shaped MoE layer H{shape.hidden} I{shape.inter} E{shape.num_experts} top{shape.top_k}"
+    config = {"workload": workload, "tokens_per_gpu": n, "global_tokens": n * max(world, 1),
+              "parallelism": f"ep{world}" if world > 1 else "single",
+              "l2": "inputs larger than L2 (expert weights re-streamed from HBM every step)"}
+
+    # ------------------------------------------------------------------ reference arm
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        w_cpu = synth.make_weights(shape, seed=0, device="cpu")
+        sample = min(args.cpu_sample_tokens, n)
+        tps, cores, med = cpu_oracle_tokens_per_s(shape, w_cpu, sample, max(1, min(args.steps, 3)), 1)
+        line = {"metric": METRIC, "value": tps, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": med * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 x nvfp4 (FF1), int4 x bf16 (FF2), fp32 accumulate",
+                "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
+                                 "sample": f"{sample} tokens of the same workload, dequantise-then-bf16-matmul, "
+                                           f"median of {max(1, min(args.steps, 3))} runs after 1 warm-up"},
+                "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "note": "the reference project has no CPU path and its GPU kernels do not assemble for sm_100a; "
+                        "this arm times the CPU restatement of its algorithm (oracle/) on the host cores"}
+        print(json.dumps(line))
+        return 0
+
+    # ------------------------------------------------------------------ native arm
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: the native arm has no CPU fallback"}))
+        return 1
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    from xcaliber_b200 import ops
+
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    ckpt = synth.make_weights(shape, seed=0, device=dev)
+    x_cpu, logits_cpu = synth.make_inputs(shape, router_on_cpu(ckpt), n, seed=rank)
+    x, logits = x_cpu.to(dev), logits_cpu.to(dev)
+
+    if world > 1:
+        from xcaliber_b200.ep import ExpertParallelMoE
+
+        layer = ExpertParallelMoE(shape, ckpt, device=dev)
+        fwd = lambda: layer.forward(x, logits)  # noqa: E731
+        launches_per_step = layer.local.kernel_launches_per_forward + 4
+    else:
+        pw = ops.PreparedWeights.from_checkpoint(shape, ckpt.w13_packed, ckpt.w13_scale, ckpt.w13_gs,
+                                                 ckpt.w2_qweight, ckpt.w2_scales, router_bias=ckpt.router_bias,
+                                                 device=dev)
+        layer = ops.FusedMoE(shape, pw)
+        y_buf = torch.empty_like(x)
+        fwd = lambda: layer.forward(x, logits, out=y_buf)  # noqa: E731
+        launches_per_step = layer.kernel_launches_per_forward
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        fwd()
+    sync_all()
+
+    ops.profile_begin(args.steps)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    sync_all()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        fwd()
+    ev1.record()
+    sync_all()
+    clocks = sampler.stop()
+    ms_total = ev0.elapsed_time(ev1)
+    stage_ms, prof_steps = ops.profile_read()
+    ops.profile_begin(0)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = n * world / (ms_step * 1e-3)
+
+    # ---- end to end: host buffers in, host buffer out, copies inside the timed region
+    xh, lh = x_cpu.pin_memory(), logits_cpu.pin_memory()
+    yh = torch.empty_like(x_cpu).pin_memory()
+    if world > 1:
+        def e2e_step():
+            x.copy_(xh, non_blocking=True)
+            logits.copy_(lh, non_blocking=True)
+            yh.copy_(layer.forward(x, logits), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+    else:
+        def e2e_step():
+            layer.forward_host(xh, lh, yh)
+    for _ in range(3):
+        e2e_step()
+    sync_all()
+    t0 = time.perf_counter()
+    ev0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    ev1.record()
+    sync_all()
+    e2e_ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = n * world / (e2e_ms / args.steps * 1e-3)
+    h2d = x_cpu.numel() * 2 + logits_cpu.numel() * 2
+    d2h = x_cpu.numel() * 2
+
+    # ---- roofline of the dominant kernel (local pipeline stages, this rank)
+    peaks = measured_peaks()
+    per_stage = {k: v / max(prof_steps, 1) for k, v in stage_ms.items()}
+    dominant = max(("ff1", "ff2"), key=lambda k: per_stage.get(k, 0.0))
+    rows_local = n * shape.k_eff  # assignments processed per rank per step (uniform in expectation under EP)
+    e_local = shape.e_tot if world == 1 else shape.num_experts // world + shape.num_shared_experts
+    flops_ff1 = 4.0 * rows_local * shape.hidden * shape.inter
+    flops_ff2 = 2.0 * rows_local * shape.hidden * shape.inter
+    w_bytes_ff1 = e_local * (2 * shape.inter * shape.hidden // 2 + 2 * shape.inter * shape.hidden // 16 + 8)
+    w_bytes_ff2 = e_local * (shape.hidden * shape.inter // 2 + 2 * shape.hidden * ((shape.inter + 127) // 128))
+    avg_rows_per_expert = rows_local / max(e_local, 1)
+    tensor_bound = avg_rows_per_expert >= 256
+    dom_ms = per_stage.get(dominant, 0.0)
+    if tensor_bound:
+        fl = flops_ff1 if dominant == "ff1" else flops_ff2
+        achieved = fl / (dom_ms * 1e-3) / 1e12 if dom_ms else 0.0
+        peak = NVFP4_NOMINAL_TFLOPS if dominant == "ff1" else peaks["bf16_tflops_sustained"]
+        roofline = {"kernel": dominant, "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                    "frac": achieved / peak if peak else None, "traffic": None,
+                    "peak_source": ("nominal dense NVFP4 (no measured FP4 figure)" if dominant == "ff1"
+                                    else f"{peaks['source']} bf16 sustained")}
+    else:
+        by = (w_bytes_ff1 + rows_local * (shape.hidden // 2 + shape.hidden // 16 + 2 * shape.inter)) if dominant == "ff1" \
+            else (w_bytes_ff2 + rows_local * 2 * (shape.inter + shape.hidden))
+        achieved = by / (dom_ms * 1e-3) / 1e9 if dom_ms else 0.0
+        roofline = {"kernel": dominant, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": f"{peaks['source']} copy"}
+    traffic_file = ROOT / "profiles" / "traffic.json"
+    if traffic_file.exists():
+        tr = json.loads(traffic_file.read_text()).get(f"{args.workload}:{n}:{dominant}")
+        if tr is not None:
+            roofline["traffic"] = tr
+    ff1_ms, ff2_ms = per_stage.get("ff1", 0.0), per_stage.get("ff2", 0.0)
+    extra = {
+        "stage_ms": {k: round(v, 5) for k, v in per_stage.items()},
+        "ff1_tflops": flops_ff1 / (ff1_ms * 1e-3) / 1e12 if ff1_ms else None,
+        "ff1_frac_of_nominal_nvfp4": flops_ff1 / (ff1_ms * 1e-3) / 1e12 / NVFP4_NOMINAL_TFLOPS if ff1_ms else None,
+        "ff2_tflops": flops_ff2 / (ff2_ms * 1e-3) / 1e12 if ff2_ms else None,
+        "ff2_frac_of_bf16_sustained": flops_ff2 / (ff2_ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"] if ff2_ms else None,
+        "layer_useful_tflops": synth.algorithmic_flops(shape, n) / (ms_step * 1e-3) / 1e12,
+    }
+
+    # ---- decode point of the same layer (N = 16 per GPU), CUDA-graph replay, HBM roofline
+    decode = None
+    if world == 1:
+        nd = 16
+        xd, ld = x[:nd].contiguous(), logits[:nd].contiguous()
+        yd = torch.empty_like(xd)
+        for _ in range(3):
+            layer.forward(xd, ld, out=yd)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            layer.forward(xd, ld, out=yd)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        ev0.record()
+        reps = 50
+        for _ in range(reps):
+            g.replay()
+        ev1.record()
+        torch.cuda.synchronize()
+        dms = ev0.elapsed_time(ev1) / reps
+        live = int((layer.view(nd)["counts"] > 0).sum().item())
+        by = synth.algorithmic_bytes(shape, nd, live)
+        decode = {"tokens": nd, "ms_per_step": dms, "tokens_per_s": nd / (dms * 1e-3), "live_experts": live,
+                  "algorithmic_gb": by / 1e9, "hbm_gbs": by / (dms * 1e-3) / 1e9,
+                  "hbm_frac_of_measured": by / (dms * 1e-3) / 1e9 / peaks["hbm_gbs"], "launch": "cuda graph replay"}
+
+    cpu_baseline = None
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        sample = min(args.cpu_sample_tokens, n)
+        tps, cores, med = cpu_oracle_tokens_per_s(shape, to_cpu_weights(ckpt), sample, 1, 0)
+        cpu_baseline = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
+                        "sample": f"{sample} tokens of the same workload (all experts dequantised once), "
+                                  f"dequantise-then-bf16-matmul oracle, 1 run, {med:.1f} s"}
+
+    if world > 1:
+        statuses = [layer.local.status(m) for (m, _h) in list(layer.local._ws)[:1]]
+    else:
+        statuses = [layer.status(n)]
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "nvfp4 x nvfp4 (FF1), int4 x bf16 (FF2), fp32 accumulate",
+                "data": "synthetic", "config": config, "clocks": clocks,
+                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline,
+                "device_status": statuses, **extra}
+        if decode is not None:
+            line["decode"] = decode
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

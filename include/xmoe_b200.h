@@ -101,15 +101,26 @@ int xmoe_forward_host(const xmoe_config* cfg, const xmoe_weights* w, const void*
 int xmoe_read_status(const void* workspace, uint32_t* host_out, xmoe_stream_t stream);
 
 /* Variant of _C.forward with routing supplied by the caller, as in the reference's
- * operator(...) (xR64ABSBinding.cu:8-121): topk_idx i32 / topk_w bf16, both [N, top_k]. */
+ * operator(...) (xR64ABSBinding.cu:8-121): topk_idx i32 / topk_w bf16, both [N, top_k].
+ * act_scale (device, 3 x f32: XGS, XGSINV, amax) replaces the internal amax pass when not NULL;
+ * expert-parallel ranks pass the scale agreed across ranks. */
 int xmoe_forward_routed(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const int32_t* topk_idx,
-                        const void* topk_w, int32_t n_tokens, void* y, void* workspace, size_t workspace_bytes,
-                        xmoe_stream_t stream);
+                        const void* topk_w, const float* act_scale, int32_t n_tokens, void* y, void* workspace,
+                        size_t workspace_bytes, xmoe_stream_t stream);
+
+/* Per-stage device timing of xmoe_forward* calls, the counterpart of the reference harness's
+ * per-kernel timing (sm120a/benchmarks/benchmark.cu:381-399). begin(max_steps > 0) makes every
+ * forward record CUDA events between its stages on the caller's stream; read() synchronises
+ * the device and returns the summed milliseconds of the 8 stages (router, route pack, amax,
+ * quantise, FF1, activation top-k, FF2, combine) over the recorded steps; begin(0) turns it off.
+ * Not thread-safe; meant for benchmarks. */
+int xmoe_profile_begin(int32_t max_steps);
+int xmoe_profile_read(float* stage_ms_sum, int32_t* steps_out);
 
 /* Device pointers into a workspace after a forward, for inspection and tests. */
 typedef struct xmoe_workspace_view {
     uint32_t* status;
-    float* act_scale;      /* [2]: XGS, XGSINV */
+    float* act_scale;      /* [3]: XGS, XGSINV, amax */
     int32_t* topk_idx;     /* [N, k_eff] */
     void* topk_w;          /* bf16 [N, k_eff] */
     int32_t* topk_off;     /* [N, k_eff] */
@@ -119,7 +130,7 @@ typedef struct xmoe_workspace_view {
     int32_t* row_token;    /* [R] */
     void* row_weight;      /* bf16 [R] */
     void* xq;              /* u8 [R, H/2] */
-    void* sfx;             /* u8 [R/128, KB, 512] */
+    void* sfx;             /* u8 [R/token_tile, KB, 512] */
     void* yact;            /* bf16 [R, I] */
     void* out_rows;        /* bf16 [R, H] */
     int32_t k_eff;
@@ -148,13 +159,16 @@ int xmoe_route_pack(int32_t* topk_idx, void* topk_w, int32_t n_tokens, int32_t n
                     xmoe_stream_t stream);
 
 /* Replaces moe_act_absmax_partial + moe_act_scale_finalize (sm120a/preamble.cuh:69-128).
- * scratch: 2 x u32, zero on entry (left zero on exit). act_scale: 2 x f32. */
+ * scratch: 2 x u32, zero on entry (left zero on exit). act_scale: 4 x f32 = XGS, XGSINV, amax, unused. */
 int xmoe_act_amax(const void* x, size_t n_elems, uint32_t* scratch, float* act_scale, xmoe_stream_t stream);
+/* The finalize half alone (preamble.cuh:98-128): amax (device f32, e.g. after a max all-reduce
+ * over expert-parallel ranks) -> act_scale {XGS, XGSINV, amax}. */
+int xmoe_act_scale_from_amax(const float* amax, float* act_scale, xmoe_stream_t stream);
 
 /* Replaces launch_xr64_abs_preamble (xR64ABS.cuh:129-139) / moe_act_pack_expert_contiguous
  * (sm120a/preamble.cuh:549-630). */
 int xmoe_act_quant_pack(const void* x, const float* act_scale, const int32_t* topk_row, int32_t n_tokens,
-                        int32_t hidden, int32_t k_eff, int32_t idx_stride, void* xq, void* sfx,
+                        int32_t hidden, int32_t k_eff, int32_t idx_stride, int32_t token_tile, void* xq, void* sfx,
                         xmoe_stream_t stream);
 
 /* Replaces launch_xr64_abs_ff1 (xR64ABS.cuh:162-176) / xR64FF1 (xR64FF1FF2/xR64FF1.cu:65). */

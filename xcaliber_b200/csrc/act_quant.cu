@@ -7,8 +7,10 @@
 //   :45-66    bf16x2 * bf16 scale (rounded to bf16) -> RN-satfinite E2M1 pair
 //   :567-599  per token, per 16 K: s = ue4m3_ceil(amax16 * XGS / 6), q = e2m1(x * bf16(XGS/dec(s)))
 // The layout is new: packed rows [R, H/2] (low nibble = lower K) that TMA can stage
-// with a 128-byte swizzle, and scale factors in 512-byte blocks of 128 rows x 4 K-blocks
-// in exactly the order the tcgen05 scale-factor copy consumes.
+// with a 128-byte swizzle, and scale factors in 512-byte tiles (one per token tile of NT
+// rows and 64 K) in exactly the order the tcgen05 scale-factor copy consumes: byte
+// (row%32)*16 + (row%NT / 32)*4 + (k16 % 4). A tile always starts at TMEM column 0 of the
+// token operand, whatever NT is; for NT < 128 the unused 4-byte groups are never read.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -47,8 +49,27 @@ __global__ __launch_bounds__(256) void act_amax_kernel(const uint4* __restrict__
                 scale->xgs = 0.f;
                 scale->xgs_inv = 0.f;
             }
+            reinterpret_cast<float*>(scale)[2] = amax;  // third word: the raw maximum
         }
     }
+}
+
+// amax (e.g. after a max all-reduce across expert-parallel ranks) -> {XGS, XGSINV, amax}
+__global__ void act_scale_from_amax_kernel(const float* __restrict__ amax_in, float* __restrict__ scale) {
+    const float amax = *amax_in;
+    if (amax > 0.f) {
+        scale[0] = 2688.0f / amax;
+        scale[1] = bf16_bits_to_f32(f32_to_bf16_bits(amax * (1.0f / 2688.0f)));
+    } else {
+        scale[0] = 0.f;
+        scale[1] = 0.f;
+    }
+    scale[2] = amax;
+}
+
+int launch_act_scale_from_amax(const float* amax, float* scale, cudaStream_t stream) {
+    act_scale_from_amax_kernel<<<1, 1, 0, stream>>>(amax, scale);
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 
 __device__ __forceinline__ uint32_t ue4m3_ceil(float x) {
@@ -99,7 +120,7 @@ __device__ __forceinline__ uint32_t e2m1x2(uint32_t x2, uint32_t scale2) {
 __global__ __launch_bounds__(256) void act_quant_pack_kernel(
     const uint16_t* __restrict__ x, const ActScale* __restrict__ scale, const int32_t* __restrict__ topk_row,
     int N, int H, int k_eff, int idx_stride, uint8_t* __restrict__ xq, uint8_t* __restrict__ sfx, int kb_pad,
-    int units_per_token) {
+    int units_per_token, int nt) {
     const float xgs = scale->xgs;
     const uint32_t lane = lane_id();
     const size_t total_units = (size_t)N * units_per_token;
@@ -138,8 +159,8 @@ __global__ __launch_bounds__(256) void act_quant_pack_kernel(
             if (r < 0) continue;
             if (h0 < H) *reinterpret_cast<uint2*>(xq + (size_t)r * (H / 2) + h0 / 2) = make_uint2(q_lo, q_hi);
             if ((lane & 3u) == 0u && h0 < h_pad) {
-                const size_t blk = (size_t)(r >> 7) * kb_pad + kb;
-                *reinterpret_cast<uint32_t*>(sfx + blk * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4) = s4;
+                const size_t blk = (size_t)(r / nt) * kb_pad + kb;
+                *reinterpret_cast<uint32_t*>(sfx + blk * 512 + (r & 31) * 16 + ((r % nt) >> 5) * 4) = s4;
             }
         }
     }
@@ -157,14 +178,14 @@ int launch_act_amax(const AmaxArgs& a, cudaStream_t stream) {
 
 int launch_act_quant(const QuantArgs& a, cudaStream_t stream) {
     if (a.N <= 0) return XMOE_OK;
-    if (a.H % 16) return XMOE_ERR_SHAPE;
+    if (a.H % 16 || (a.nt != 32 && a.nt != 64 && a.nt != 128)) return XMOE_ERR_SHAPE;
     const int units_per_token = (a.kb_pad * 64 + 511) / 512;
     const size_t total = (size_t)a.N * units_per_token;
     size_t blocks = (total + 7) / 8;
     if (blocks > 148 * 16) blocks = 148 * 16;
     act_quant_pack_kernel<<<(int)blocks, 256, 0, stream>>>((const uint16_t*)a.x, a.scale, a.topk_row, a.N, a.H,
                                                            a.k_eff, a.idx_stride, (uint8_t*)a.xq, (uint8_t*)a.sfx,
-                                                           a.kb_pad, units_per_token);
+                                                           a.kb_pad, units_per_token, a.nt);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 

@@ -62,6 +62,19 @@ int num_sms() {
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// ---- optional per-stage timing (CUDA events recorded on the caller's stream) -----------
+constexpr int kProfStages = 8;  // router, pack, amax, quant, ff1, act_topk, ff2, combine
+struct Profiler {
+    cudaEvent_t* ev = nullptr;  // [max_steps][kProfStages + 1]
+    int max_steps = 0;
+    int step = 0;
+} g_prof;
+
+inline void prof_mark(int stage_boundary, cudaStream_t s) {
+    if (g_prof.ev && g_prof.step < g_prof.max_steps)
+        cudaEventRecord(g_prof.ev[(size_t)g_prof.step * (kProfStages + 1) + stage_boundary], s);
+}
+
 int check_cfg(const xmoe_config* c) {
     if (!c) return XMOE_ERR_ARG;
     if (c->hidden <= 0 || c->inter <= 0 || c->num_experts <= 0 || c->top_k <= 0) return XMOE_ERR_ARG;
@@ -131,7 +144,7 @@ Layout make_layout(const xmoe_config* c, int n) {
     L.off_row_token = take(L.rows * 4);
     L.off_row_weight = take(L.rows * 2);
     L.off_xq = take(L.rows * (size_t)(c->hidden / 2));
-    L.off_sfx = take((L.rows / 128) * (size_t)L.kb_pad * 512);
+    L.off_sfx = take((L.rows / L.nt) * (size_t)L.kb_pad * 512);
     L.off_yact = take(L.rows * (size_t)c->inter * 2);
     L.off_out = take(L.rows * (size_t)c->hidden * 2);
     L.total = o;
@@ -201,8 +214,8 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
 }
 
 int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* logits,
-                 const int32_t* ext_idx, const void* ext_w, int n, void* y, void* ws, size_t ws_bytes,
-                 cudaStream_t stream) {
+                 const int32_t* ext_idx, const void* ext_w, const float* ext_scale, int n, void* y, void* ws,
+                 size_t ws_bytes, cudaStream_t stream) {
     int rc = check_cfg(cfg);
     if (rc) return rc;
     if (n < 0) return XMOE_ERR_ARG;
@@ -226,6 +239,7 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     const int H = cfg->hidden, I = cfg->inter, E = cfg->num_experts;
 
     if (cudaMemsetAsync(b, 0, 64, stream) != cudaSuccess) return XMOE_ERR_CUDA;
+    prof_mark(0, stream);
 
     if (ext_idx) {
         // caller-supplied routing: widen [N, top_k] to the [N, k_eff] workspace arrays
@@ -270,14 +284,22 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     p.row_token = (int32_t*)(b + L.off_row_token);
     p.row_weight = b + L.off_row_weight;
     p.status = status;
+    prof_mark(1, stream);
     if ((rc = launch_route_pack(p, stream))) return rc;
+    prof_mark(2, stream);
 
     AmaxArgs am;
     am.x = x;
     am.n_elems = (size_t)n * H;
     am.scratch = amax_scratch;
     am.scale = scale;
-    if ((rc = launch_act_amax(am, stream))) return rc;
+    if (ext_scale) {
+        if (cudaMemcpyAsync(scale, ext_scale, 12, cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+            return XMOE_ERR_CUDA;
+    } else if ((rc = launch_act_amax(am, stream))) {
+        return rc;
+    }
+    prof_mark(3, stream);
 
     QuantArgs q;
     q.x = x;
@@ -290,12 +312,15 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     q.xq = b + L.off_xq;
     q.sfx = b + L.off_sfx;
     q.kb_pad = L.kb_pad;
+    q.nt = L.nt;
     if ((rc = launch_act_quant(q, stream))) return rc;
+    prof_mark(4, stream);
 
     if ((rc = run_ff1(w->w13_packed, w->w13_sf, w->w13_gs, b + L.off_xq, b + L.off_sfx, (const float*)scale, counts,
                       offsets, b + L.off_row_weight, b + L.off_yact, status, L.e_tot, H, I, L.rows, L.nt,
                       cfg->activation, cfg->swiglu_alpha, cfg->swiglu_limit, stream)))
         return rc;
+    prof_mark(5, stream);
 
     if (cfg->act_topk_keep > 0 && cfg->act_topk_keep < I) {
         ActTopkArgs t;
@@ -308,10 +333,12 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
         t.max_rows = (int)L.rows;
         if ((rc = launch_act_topk(t, stream))) return rc;
     }
+    prof_mark(6, stream);
 
     if ((rc = run_ff2(w->w2_q, w->w2_scale, b + L.off_yact, counts, offsets, b + L.off_out, status, L.e_tot, H, I,
                       L.rows, L.nt, stream)))
         return rc;
+    prof_mark(7, stream);
 
     CombineArgs c;
     c.rows = b + L.off_out;
@@ -321,7 +348,10 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     c.H = H;
     c.k_eff = L.k_eff;
     c.idx_stride = L.k_eff;
-    return launch_combine(c, stream);
+    rc = launch_combine(c, stream);
+    prof_mark(8, stream);
+    if (g_prof.ev && g_prof.step < g_prof.max_steps) ++g_prof.step;
+    return rc;
 }
 
 }  // namespace
@@ -360,15 +390,51 @@ size_t xmoe_workspace_bytes_host_io(const xmoe_config* cfg, int32_t n) {
 
 int xmoe_forward(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* router_logits, int32_t n,
                  void* y, void* workspace, size_t workspace_bytes, xmoe_stream_t stream) {
-    return forward_impl(cfg, w, x, router_logits, nullptr, nullptr, n, y, workspace, workspace_bytes,
+    return forward_impl(cfg, w, x, router_logits, nullptr, nullptr, nullptr, n, y, workspace, workspace_bytes,
                         (cudaStream_t)stream);
 }
 
 int xmoe_forward_routed(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const int32_t* topk_idx,
-                        const void* topk_w, int32_t n, void* y, void* workspace, size_t workspace_bytes,
-                        xmoe_stream_t stream) {
+                        const void* topk_w, const float* act_scale, int32_t n, void* y, void* workspace,
+                        size_t workspace_bytes, xmoe_stream_t stream) {
     if (!topk_idx || !topk_w) return XMOE_ERR_ARG;
-    return forward_impl(cfg, w, x, nullptr, topk_idx, topk_w, n, y, workspace, workspace_bytes, (cudaStream_t)stream);
+    return forward_impl(cfg, w, x, nullptr, topk_idx, topk_w, act_scale, n, y, workspace, workspace_bytes,
+                        (cudaStream_t)stream);
+}
+
+int xmoe_profile_begin(int32_t max_steps) {
+    if (g_prof.ev) {
+        for (size_t i = 0; i < (size_t)g_prof.max_steps * (kProfStages + 1); ++i) cudaEventDestroy(g_prof.ev[i]);
+        delete[] g_prof.ev;
+        g_prof = Profiler();
+    }
+    if (max_steps <= 0) return XMOE_OK;
+    if (max_steps > 4096) return XMOE_ERR_LIMIT;
+    const size_t n = (size_t)max_steps * (kProfStages + 1);
+    g_prof.ev = new cudaEvent_t[n];
+    for (size_t i = 0; i < n; ++i)
+        if (cudaEventCreate(&g_prof.ev[i]) != cudaSuccess) return XMOE_ERR_CUDA;
+    g_prof.max_steps = max_steps;
+    g_prof.step = 0;
+    return XMOE_OK;
+}
+
+int xmoe_profile_read(float* stage_ms_sum, int32_t* steps_out) {
+    if (!stage_ms_sum || !steps_out) return XMOE_ERR_ARG;
+    for (int i = 0; i < kProfStages; ++i) stage_ms_sum[i] = 0.f;
+    *steps_out = g_prof.step;
+    if (!g_prof.ev) return XMOE_OK;
+    if (cudaDeviceSynchronize() != cudaSuccess) return XMOE_ERR_CUDA;
+    for (int s = 0; s < g_prof.step; ++s) {
+        cudaEvent_t* e = g_prof.ev + (size_t)s * (kProfStages + 1);
+        for (int i = 0; i < kProfStages; ++i) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, e[i], e[i + 1]) != cudaSuccess) return XMOE_ERR_CUDA;
+            stage_ms_sum[i] += ms;
+        }
+    }
+    g_prof.step = 0;
+    return XMOE_OK;
 }
 
 int xmoe_forward_host(const xmoe_config* cfg, const xmoe_weights* w, const void* x_host, const void* logits_host,
@@ -385,8 +451,8 @@ int xmoe_forward_host(const xmoe_config* cfg, const xmoe_weights* w, const void*
     if (cudaMemcpyAsync(b + L.off_x_in, x_host, xb, cudaMemcpyHostToDevice, s) != cudaSuccess ||
         cudaMemcpyAsync(b + L.off_logits_in, logits_host, lb, cudaMemcpyHostToDevice, s) != cudaSuccess)
         return XMOE_ERR_CUDA;
-    rc = forward_impl(cfg, w, b + L.off_x_in, b + L.off_logits_in, nullptr, nullptr, n, b + L.off_y_out, workspace,
-                      workspace_bytes, s);
+    rc = forward_impl(cfg, w, b + L.off_x_in, b + L.off_logits_in, nullptr, nullptr, nullptr, n, b + L.off_y_out,
+                      workspace, workspace_bytes, s);
     if (rc) return rc;
     if (cudaMemcpyAsync(y_host, b + L.off_y_out, xb, cudaMemcpyDeviceToHost, s) != cudaSuccess) return XMOE_ERR_CUDA;
     if (cudaStreamSynchronize(s) != cudaSuccess) return XMOE_ERR_CUDA;
@@ -497,8 +563,14 @@ int xmoe_act_amax(const void* x, size_t n_elems, uint32_t* scratch, float* act_s
     return launch_act_amax(a, (cudaStream_t)stream);
 }
 
+int xmoe_act_scale_from_amax(const float* amax, float* act_scale, xmoe_stream_t stream) {
+    if (!amax || !act_scale) return XMOE_ERR_ARG;
+    return launch_act_scale_from_amax(amax, act_scale, (cudaStream_t)stream);
+}
+
 int xmoe_act_quant_pack(const void* x, const float* act_scale, const int32_t* topk_row, int32_t n, int32_t H,
-                        int32_t k_eff, int32_t idx_stride, void* xq, void* sfx, xmoe_stream_t stream) {
+                        int32_t k_eff, int32_t idx_stride, int32_t token_tile, void* xq, void* sfx,
+                        xmoe_stream_t stream) {
     if (!x || !act_scale || !topk_row || !xq || !sfx || n < 0) return XMOE_ERR_ARG;
     if (H <= 0 || H % 64 || k_eff <= 0 || idx_stride < k_eff) return XMOE_ERR_SHAPE;
     QuantArgs q;
@@ -512,6 +584,7 @@ int xmoe_act_quant_pack(const void* x, const float* act_scale, const int32_t* to
     q.xq = xq;
     q.sfx = sfx;
     q.kb_pad = (int)align_up((size_t)H / 64, 4);
+    q.nt = token_tile;
     return launch_act_quant(q, (cudaStream_t)stream);
 }
 

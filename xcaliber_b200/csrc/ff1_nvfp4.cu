@@ -165,7 +165,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
                 const int up_row = gate_row + a.I;
                 const uint8_t* sfw_g = a.sfw + ((size_t)(t.e * 2 + 0) * a.mb + t.mt) * a.kb_pad * 512;
                 const uint8_t* sfw_u = a.sfw + ((size_t)(t.e * 2 + 1) * a.mb + t.mt) * a.kb_pad * 512;
-                const uint8_t* sfx = a.sfx + (size_t)(t.row0 >> 7) * a.kb_pad * 512;
+                const uint8_t* sfx = a.sfx + (size_t)(t.row0 / NT) * a.kb_pad * 512;
                 for (int ks = 0; ks < k_stages; ++ks, ++it) {
                     const int s = it % Cfg::kStages;
                     const uint32_t ph = (it / Cfg::kStages) & 1u;
@@ -192,14 +192,12 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
             uint32_t it = 0, tile_n = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tile_n) {
-                const TileInfo t = decode_tile(item, prefix, a.counts, a.offsets, a.E_tot, mt_tiles, NT);
                 const uint32_t as = tile_n % Cfg::kAccStages;
                 const uint32_t aph = (tile_n / Cfg::kAccStages) & 1u;
                 if (!mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
                 tc_fence_after();
                 const uint32_t acc_gate = tmem_base + as * Cfg::kAccCols;
                 const uint32_t acc_up = acc_gate + NT;
-                const uint32_t sfb_col_off = (uint32_t)(t.row0 & 127) >> 5;  // token rows inside the 128-row SF tile
                 for (int ks = 0; ks < k_stages; ++ks, ++it) {
                     const int s = it % Cfg::kStages;
                     const uint32_t ph = (it / Cfg::kStages) & 1u;
@@ -225,9 +223,9 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
                         const uint32_t acc = (ks | kb) ? 1u : 0u;
                         const uint64_t koff = (uint64_t)(kb * 32 >> 4);  // 32 bytes of packed K per MMA
                         mma_nvfp4(acc_gate, da_g + koff, db + koff, idesc, sf_tmem + kb * 4,
-                                  sf_tmem + 32 + kb * 4 + sfb_col_off, acc);
+                                  sf_tmem + 32 + kb * 4, acc);
                         mma_nvfp4(acc_up, da_u + koff, db + koff, idesc, sf_tmem + 16 + kb * 4,
-                                  sf_tmem + 32 + kb * 4 + sfb_col_off, acc);
+                                  sf_tmem + 32 + kb * 4, acc);
                     }
                     tc_commit(&empty_bar[s]);
                 }

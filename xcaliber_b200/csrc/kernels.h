@@ -47,7 +47,7 @@ struct AmaxArgs {
     const void* x;  // bf16 [N, H]
     size_t n_elems;
     uint32_t* scratch;  // [2]: running max, ticket (both zero on entry, zero on exit)
-    ActScale* scale;
+    ActScale* scale;  // 4 floats of room: xgs, xgs_inv, amax, unused
 };
 
 struct QuantArgs {
@@ -56,15 +56,16 @@ struct QuantArgs {
     const int32_t* topk_row;  // [N, idx_stride]
     int N, H, k_eff, idx_stride;
     void* xq;   // u8 [R_cap, H/2]
-    void* sfx;  // u8 [R_cap/128, KB, 512]
+    void* sfx;  // u8 [R_cap/nt, KB, 512]
     int kb_pad; // K blocks of 64 per row, rounded up to a multiple of 4
+    int nt;     // token tile the scale-factor tiles are laid out for: 32, 64 or 128
 };
 
 struct Ff1Args {
     CUtensorMap tm_w;  // u8 [E_tot*2I, H/2], box 128 B x 128 rows, 128-byte swizzle
     CUtensorMap tm_x;  // u8 [R_cap, H/2], box 128 B x NT rows
     const uint8_t* sfw;      // [E_tot, 2, MB, KB, 512]
-    const uint8_t* sfx;      // [R_cap/128, KB, 512]
+    const uint8_t* sfx;      // [R_cap/nt, KB, 512]
     const float* w13_gs;     // [E_tot, 2]
     const ActScale* scale;
     const int32_t* counts;
@@ -111,6 +112,7 @@ int launch_router_topk(const RouterArgs& a, cudaStream_t stream);
 int route_pack_chunks(int N);
 int launch_route_pack(const PackArgs& a, cudaStream_t stream);
 int launch_act_amax(const AmaxArgs& a, cudaStream_t stream);
+int launch_act_scale_from_amax(const float* amax, float* scale, cudaStream_t stream);
 int launch_act_quant(const QuantArgs& a, cudaStream_t stream);
 int launch_ff1(const Ff1Args& a, cudaStream_t stream);
 int launch_ff2(const Ff2Args& a, cudaStream_t stream);
