@@ -39,7 +39,7 @@ def test_workspace_sizes(built_lib):
     assert big >= rows * (14336 * 2 + 4096 * 2 + 2048)
     assert built_lib.xmoe_workspace_bytes_host_io(C.byref(cfg), 4096) > big
     # decode batches only reserve rows for experts that can be live
-    assert built_lib.xmoe_packed_rows(C.byref(ops.make_config(synth.SHAPES["qwen3"])), 1) == 1024 + 128
+    assert built_lib.xmoe_packed_rows(C.byref(ops.make_config(synth.SHAPES["qwen3"])), 1) == 1024
 
 
 @pytest.mark.parametrize("field,value", [("hidden", 1000), ("inter", 100), ("num_experts", 2048), ("top_k", 9),

@@ -220,7 +220,8 @@ def test_quantisers_roundtrip():
     for m in range(3):
         deq = O.int4_dequant_gptq(q[m].numpy(), O.bf16_bits(sc[m]))
         step = O.bits_to_f32(O.bf16_bits(sc[m])).T.repeat(128, axis=1)
-        assert (np.abs(deq - w2[m].float().numpy()) <= step * 0.51 + 1e-7).all()
+        # half a step, plus the bf16 rounding of the scale (clamp at +7) and of the product
+        assert (np.abs(deq - w2[m].float().numpy()) <= step * 0.58 + 1e-7).all()
     # the reference's own repack target holds the same integers (xR64ABSRepack.cu:3-24)
     ref = O.repack_gptq_reference_layout(q[0].numpy())
     s4 = ((ref[:, 0] >> 0) & 0xF).astype(np.int64)
