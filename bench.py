@@ -127,13 +127,16 @@ def router_on_cpu(w):
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="mixtral", choices=sorted(synth.SHAPES))
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU per step")
     ap.add_argument("--cpu-sample-tokens", type=int, default=128)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for short profiler captures)")
+    ap.add_argument("--no-decode", action="store_true", help="skip the supplementary decode point")
+    ap.add_argument("--decode-tokens", type=int, default=16)
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -240,21 +243,21 @@ def main() -> int:
     else:
         def e2e_step():
             layer.forward_host(xh, lh, yh)
-    for _ in range(3):
+    e2e_steps = 0 if args.no_e2e else args.steps
+    for _ in range(3 if e2e_steps else 0):
         e2e_step()
     sync_all()
-    t0 = time.perf_counter()
     ev0.record()
-    for _ in range(args.steps):
+    for _ in range(e2e_steps):
         e2e_step()
     ev1.record()
     sync_all()
-    e2e_ms = ev0.elapsed_time(ev1)
+    e2e_ms = ev0.elapsed_time(ev1) if e2e_steps else float("nan")
     if world > 1:
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    e2e_value = n * world / (e2e_ms / args.steps * 1e-3)
+    e2e_value = n * world / (e2e_ms / args.steps * 1e-3) if e2e_steps else None
     h2d = x_cpu.numel() * 2 + logits_cpu.numel() * 2
     d2h = x_cpu.numel() * 2
 
@@ -302,8 +305,8 @@ def main() -> int:
 
     # ---- decode point of the same layer (N = 16 per GPU), CUDA-graph replay, HBM roofline
     decode = None
-    if world == 1:
-        nd = 16
+    if world == 1 and not args.no_decode:
+        nd = args.decode_tokens
         xd, ld = x[:nd].contiguous(), logits[:nd].contiguous()
         yd = torch.empty_like(xd)
         for _ in range(3):
@@ -322,11 +325,17 @@ def main() -> int:
         ev1.record()
         torch.cuda.synchronize()
         dms = ev0.elapsed_time(ev1) / reps
+        ops.profile_begin(10)
+        for _ in range(10):
+            layer.forward(xd, ld, out=yd)
+        dstage, dsteps = ops.profile_read()
+        ops.profile_begin(0)
         live = int((layer.view(nd)["counts"] > 0).sum().item())
         by = synth.algorithmic_bytes(shape, nd, live)
         decode = {"tokens": nd, "ms_per_step": dms, "tokens_per_s": nd / (dms * 1e-3), "live_experts": live,
                   "algorithmic_gb": by / 1e9, "hbm_gbs": by / (dms * 1e-3) / 1e9,
-                  "hbm_frac_of_measured": by / (dms * 1e-3) / 1e9 / peaks["hbm_gbs"], "launch": "cuda graph replay"}
+                  "hbm_frac_of_measured": by / (dms * 1e-3) / 1e9 / peaks["hbm_gbs"], "launch": "cuda graph replay",
+                  "stage_ms_stream_launch": {k: round(v / max(dsteps, 1), 5) for k, v in dstage.items()}}
 
     cpu_baseline = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
