@@ -306,7 +306,7 @@ int launch_ff1(const Ff1Args& a, cudaStream_t stream) {
     switch (a.nt) {
         case 32: return launch_ff1_nt<32>(a, stream);
         case 64: return launch_ff1_nt<64>(a, stream);
-        case 128: return launch_ff1_nt<128>(a, stream);
+        case 128: return launch_ff1_prefill(a, stream);  // token-major variant, ff1_nvfp4_prefill.cu
         default: return XMOE_ERR_SHAPE;
     }
 }

@@ -41,13 +41,13 @@ template <int NT>
 struct Ff2Cfg {
     static constexpr int kBBytes = NT * kStageK * 2;        // two slabs of NT x 128 B
     static constexpr int kStageBytes = kRawBytes + 1024 /*scales, padded*/ + kBBytes;
-    static constexpr int kStages = NT >= 128 ? 3 : (NT >= 64 ? 4 : 6);
-    static constexpr int kADqStages = 2;
+    static constexpr int kStages = NT >= 128 ? 3 : (NT >= 64 ? 3 : 5);
+    static constexpr int kADqStages = NT >= 128 ? 3 : 4;  // bf16 weight tiles in flight between dequant and MMA
     static constexpr int kAccStages = 2;
     static_assert(kAccStages * NT <= kTmemCols, "TMEM budget");
     static constexpr int kTxBytes = kRawBytes + kScaleBytes + kBBytes;
     static constexpr size_t kSmemBytes =
-        1024 + (size_t)kStages * kStageBytes + (size_t)kADqStages * kADqBytes + 8192;
+        1024 + (size_t)kStages * kStageBytes + (size_t)kADqStages * kADqBytes + 5120;
 };
 
 struct TileInfo {
@@ -111,9 +111,9 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_kernel(const __grid_con
     uint8_t* tail = adq_base + (size_t)Cfg::kADqStages * kADqBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // [kStages]   TMA landed
     uint64_t* empty_bar = full_bar + 8;                      // [kStages]   dequant warps + MMA done with the stage
-    uint64_t* adq_full = empty_bar + 8;                      // [2]         bf16 weight tile ready
-    uint64_t* adq_empty = adq_full + 2;                      // [2]         MMAs reading it retired
-    uint64_t* acc_full = adq_empty + 2;                      // [2]
+    uint64_t* adq_full = empty_bar + 8;                      // [4]         bf16 weight tile ready
+    uint64_t* adq_empty = adq_full + 4;                      // [4]         MMAs reading it retired
+    uint64_t* acc_full = adq_empty + 4;                      // [2]
     uint64_t* acc_empty = acc_full + 2;                      // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -129,9 +129,11 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_kernel(const __grid_con
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], kDqWarps + 1);
         }
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < Cfg::kADqStages; ++s) {
             mbar_init(&adq_full[s], kDqWarps);
             mbar_init(&adq_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
             mbar_init(&acc_full[s], 1);
             mbar_init(&acc_empty[s], 4);
         }
@@ -196,8 +198,8 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_kernel(const __grid_con
                 for (int ks = 0; ks < k_stages; ++ks, ++it) {
                     const int s = it % Cfg::kStages;
                     const uint32_t ph = (it / Cfg::kStages) & 1u;
-                    const int d = it & 1u;
-                    const uint32_t dph = (it >> 1) & 1u;
+                    const int d = it % Cfg::kADqStages;
+                    const uint32_t dph = (it / Cfg::kADqStages) & 1u;
                     if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
                         !mbar_wait(&adq_full[d], dph, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) {
                         ok = false;
@@ -260,8 +262,8 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_kernel(const __grid_con
             for (int ks = 0; ks < k_stages; ++ks, ++it) {
                 const int s = it % Cfg::kStages;
                 const uint32_t ph = (it / Cfg::kStages) & 1u;
-                const int d = it & 1u;
-                const uint32_t dph = (it >> 1) & 1u;
+                const int d = it % Cfg::kADqStages;
+                const uint32_t dph = (it / Cfg::kADqStages) & 1u;
                 if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
                     !mbar_wait(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) {
                     ok = false;

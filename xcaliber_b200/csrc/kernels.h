@@ -115,6 +115,7 @@ int launch_act_amax(const AmaxArgs& a, cudaStream_t stream);
 int launch_act_scale_from_amax(const float* amax, float* scale, cudaStream_t stream);
 int launch_act_quant(const QuantArgs& a, cudaStream_t stream);
 int launch_ff1(const Ff1Args& a, cudaStream_t stream);
+int launch_ff1_prefill(const Ff1Args& a, cudaStream_t stream);
 int launch_ff2(const Ff2Args& a, cudaStream_t stream);
 int launch_combine(const CombineArgs& a, cudaStream_t stream);
 int launch_act_topk(const ActTopkArgs& a, cudaStream_t stream);

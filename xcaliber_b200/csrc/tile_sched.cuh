@@ -1,0 +1,79 @@
+// Device-side tile list for the grouped GEMMs, and the gated activation shared by the FF1
+// epilogues. A work item is (expert, weight tile, token tile); the list is never written to
+// memory: every CTA rebuilds the per-expert prefix of tile counts from the expert histogram
+// and decodes item numbers with a binary search.
+#pragma once
+
+#include "common.cuh"
+
+namespace xmoe {
+
+struct TileInfo {
+    int e, wt, nt_idx, count, row0;  // expert, weight-tile index, token-tile index, expert rows, first packed row
+};
+
+// prefix[e] = number of tiles of experts < e (one warp, 32 experts per step, running carry).
+__device__ __forceinline__ void tile_prefix_build(int* prefix, const int32_t* counts, int e_tot, int w_tiles,
+                                                  int token_tile) {
+    const int lane = threadIdx.x & 31;
+    int carry = 0;
+    for (int base = 0; base < e_tot; base += 32) {
+        const int e = base + lane;
+        const int v = e < e_tot ? ((counts[e] + token_tile - 1) / token_tile) * w_tiles : 0;
+        int incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += o;
+        }
+        if (e < e_tot) prefix[e] = carry + incl - v;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) prefix[e_tot] = carry;
+}
+
+// Token tiles are innermost, so the CTAs of one wave work on the same weight tile and share
+// it through L2.
+__device__ __forceinline__ TileInfo tile_decode(int item, const int* prefix, const int32_t* counts,
+                                                const int32_t* offsets, int e_tot, int token_tile) {
+    int lo = 0, hi = e_tot;  // largest e with prefix[e] <= item
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (prefix[mid] <= item) lo = mid; else hi = mid;
+    }
+    TileInfo t;
+    t.e = lo;
+    const int local = item - prefix[lo];
+    t.count = counts[lo];
+    const int n_tiles = (t.count + token_tile - 1) / token_tile;
+    t.wt = local / n_tiles;
+    t.nt_idx = local % n_tiles;
+    t.row0 = offsets[lo] + t.nt_idx * token_tile;
+    return t;
+}
+
+// activation 0: silu(g)*u; 1: clamped SwiGLU (min(g,limit) * sigmoid(alpha*g)) * (clamp(u)+1);
+// 2: tanh-GELU(g)*u. fp32 with the approximate ex2 / rcp units, like the reference epilogue
+// (xR64FF1.cu:356-386).
+__device__ __forceinline__ float glu_act(float g, float u, int activation, float alpha, float limit) {
+    if (activation == 1) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        const float s = rcp_approx(1.0f + ex2_approx(-alpha * g * 1.4426950408889634f));
+        return g * s * (u + 1.0f);
+    }
+    if (activation == 2) {
+        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        const float t = 1.0f - 2.0f * rcp_approx(1.0f + ex2_approx(2.0f * inner * 1.4426950408889634f));
+        return 0.5f * g * (1.0f + t) * u;
+    }
+    return g * u * rcp_approx(1.0f + ex2_approx(-g * 1.4426950408889634f));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+}  // namespace xmoe
