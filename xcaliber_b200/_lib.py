@@ -7,7 +7,10 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-_LIB_PATH = Path(__file__).resolve().parent / "libxmoe_b200.so"
+import os
+
+# XMOE_B200_LIB selects another build of the library (e.g. one compiled with debug defines).
+_LIB_PATH = Path(os.environ.get("XMOE_B200_LIB") or Path(__file__).resolve().parent / "libxmoe_b200.so")
 _lib = None
 
 STATUS_NAMES = {0: "OK", 1: "ERR_ARG", 2: "ERR_SHAPE", 3: "ERR_WORKSPACE", 4: "ERR_CUDA", 5: "ERR_TIMEOUT",

@@ -194,7 +194,7 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
     Ff2Args a;
     memset(&a, 0, sizeof(a));
     int rc = make_tmap_2d(&a.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2_q, (uint64_t)I / 2, (uint64_t)e_tot * H, 64,
-                          128, CU_TENSOR_MAP_SWIZZLE_NONE);
+                          128, CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc) return rc;
     rc = make_tmap_2d(&a.tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64, (uint32_t)nt,
                       CU_TENSOR_MAP_SWIZZLE_128B);

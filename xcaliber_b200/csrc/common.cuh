@@ -28,8 +28,14 @@
 #define XMOE_DEV_TIMEOUT_EPI 0x400u   // MMA warp never saw a drained accumulator
 #define XMOE_DEV_TIMEOUT_DQ 0x500u    // dequant / MMA hand-off wait gave up
 
+// A waiting thread parks inside mbarrier.try_wait for up to XMOE_WAIT_HINT_NS (it wakes as soon
+// as the phase completes), so idle roles do not compete for issue slots with the working warps.
+// The number of such parked polls is bounded: worst case ~ XMOE_SPIN_LIMIT * hint = 2.6 s.
+#ifndef XMOE_WAIT_HINT_NS
+#define XMOE_WAIT_HINT_NS 20000u
+#endif
 #ifndef XMOE_SPIN_LIMIT
-#define XMOE_SPIN_LIMIT (1u << 22)    // each poll suspends up to ~1 us => seconds worst case
+#define XMOE_SPIN_LIMIT (1u << 17)
 #endif
 
 namespace xmoe {
@@ -68,10 +74,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(XMOE_WAIT_HINT_NS)
         : "memory");
     return ok != 0;
 }
@@ -81,7 +87,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
                                           uint32_t* status, uint32_t code) {
     for (uint32_t spin = 0; spin < XMOE_SPIN_LIMIT; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 63u) == 63u && *abort_flag) return false;
+        if (*abort_flag) return false;
     }
     *abort_flag = 1u;
     if (status) atomicCAS(status, XMOE_DEV_OK, code | (blockIdx.x & 0xffu));
@@ -212,6 +218,50 @@ __host__ __device__ constexpr uint32_t umma_idesc_nvfp4(uint32_t m, uint32_t n) 
 // Instruction descriptor, kind::f16: accumulator format [4,6) (1 = fp32), a/b format (1 = bf16).
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(uint32_t m, uint32_t n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// ---- lean issue path -------------------------------------------------------------------
+// One thread issues every MMA of a CTA, so the instructions it spends per MMA bound the
+// tensor pipe from above (a K=16 bf16 MMA with N=32 lasts ~17 cycles). The helpers below keep
+// the 64-bit descriptors as (low word, constant high word): per MMA the issuing thread adds a
+// compile-time offset to a 32-bit register and nothing else.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, 128-byte swizzle
+constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);                   // SBO 128 B, version 1, no swizzle
+__device__ __forceinline__ uint32_t umma_desc_lo_sw128(uint32_t smem_addr) {
+    return ((smem_addr & 0x3ffffu) >> 4) | (1u << 16);
+}
+__device__ __forceinline__ uint32_t umma_desc_lo_sf(uint32_t smem_addr) { return (smem_addr & 0x3ffffu) >> 4; }
+
+__device__ __forceinline__ void mma_nvfp4_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %7};\n\t"
+        "mov.b64 db, {%2, %7};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem),
+          "r"(kDescHiSw128)
+        : "memory");
+}
+// A from tensor memory (lane = row, 8 columns per K16), B from shared memory.
+__device__ __forceinline__ void mma_bf16_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_cp_sf_lo(uint32_t taddr, uint32_t s_lo) {
+    asm volatile(
+        "{\n\t.reg .b64 ds;\n\t"
+        "mov.b64 ds, {%1, %2};\n\t"
+        "tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], ds;\n\t}"
+        ::"r"(taddr), "r"(s_lo), "r"(kDescHiSf)
+        : "memory");
 }
 
 // ---- small numeric helpers ------------------------------------------------------------

@@ -189,7 +189,12 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_nvfp4(kBlockM, NT);
-            uint32_t it = 0, tile_n = 0;
+            constexpr uint32_t kStage16 = Cfg::kStageBytes >> 4;
+            const uint32_t ag_lo0 = umma_desc_lo_sw128(smem_u32(stage_base));
+            const uint32_t au_lo0 = umma_desc_lo_sw128(smem_u32(stage_base + Cfg::kABytes));
+            const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(stage_base + 2 * Cfg::kABytes));
+            const uint32_t sf_lo0 = umma_desc_lo_sf(smem_u32(stage_base + 2 * Cfg::kABytes + Cfg::kBBytes));
+            uint32_t tile_n = 0, s = 0, ph = 0, slot = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tile_n) {
                 const uint32_t as = tile_n % Cfg::kAccStages;
@@ -198,36 +203,33 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
                 tc_fence_after();
                 const uint32_t acc_gate = tmem_base + as * Cfg::kAccCols;
                 const uint32_t acc_up = acc_gate + NT;
-                for (int ks = 0; ks < k_stages; ++ks, ++it) {
-                    const int s = it % Cfg::kStages;
-                    const uint32_t ph = (it / Cfg::kStages) & 1u;
+                for (int ks = 0; ks < k_stages; ++ks) {
                     if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t st = smem_u32(stage_base + (size_t)s * Cfg::kStageBytes);
-                    const uint32_t sf_smem = st + 2 * Cfg::kABytes + Cfg::kBBytes;
-                    const uint32_t sf_tmem = tmem_base + Cfg::kSfColsBase + (it & 1u) * Cfg::kSfColsPerSlot;
+                    const uint32_t sf_lo = sf_lo0 + s * kStage16;
+                    const uint32_t sf_tmem = tmem_base + Cfg::kSfColsBase + slot * Cfg::kSfColsPerSlot;
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
-                        tmem_cp_sf(sf_tmem + kb * 4, umma_desc_sf(sf_smem + kb * 512));
-                        tmem_cp_sf(sf_tmem + 16 + kb * 4, umma_desc_sf(sf_smem + kSfStageBytes + kb * 512));
-                        tmem_cp_sf(sf_tmem + 32 + kb * 4, umma_desc_sf(sf_smem + 2 * kSfStageBytes + kb * 512));
+                        tmem_cp_sf_lo(sf_tmem + kb * 4, sf_lo + kb * 32);
+                        tmem_cp_sf_lo(sf_tmem + 16 + kb * 4, sf_lo + (kSfStageBytes >> 4) + kb * 32);
+                        tmem_cp_sf_lo(sf_tmem + 32 + kb * 4, sf_lo + 2 * (kSfStageBytes >> 4) + kb * 32);
                     }
-                    const uint64_t da_g = umma_desc_sw128(st);
-                    const uint64_t da_u = umma_desc_sw128(st + Cfg::kABytes);
-                    const uint64_t db = umma_desc_sw128(st + 2 * Cfg::kABytes);
+                    const uint32_t ag_lo = ag_lo0 + s * kStage16, au_lo = au_lo0 + s * kStage16;
+                    const uint32_t b_lo = b_lo0 + s * kStage16;
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
-                        const uint32_t acc = (ks | kb) ? 1u : 0u;
-                        const uint64_t koff = (uint64_t)(kb * 32 >> 4);  // 32 bytes of packed K per MMA
-                        mma_nvfp4(acc_gate, da_g + koff, db + koff, idesc, sf_tmem + kb * 4,
-                                  sf_tmem + 32 + kb * 4, acc);
-                        mma_nvfp4(acc_up, da_u + koff, db + koff, idesc, sf_tmem + 16 + kb * 4,
-                                  sf_tmem + 32 + kb * 4, acc);
+                        const uint32_t acc = (ks | kb) ? 1u : 0u;  // 32 bytes of packed K per MMA: +2 descriptor units
+                        mma_nvfp4_lo(acc_gate, ag_lo + kb * 2, b_lo + kb * 2, idesc, sf_tmem + kb * 4,
+                                     sf_tmem + 32 + kb * 4, acc);
+                        mma_nvfp4_lo(acc_up, au_lo + kb * 2, b_lo + kb * 2, idesc, sf_tmem + 16 + kb * 4,
+                                     sf_tmem + 32 + kb * 4, acc);
                     }
                     tc_commit(&empty_bar[s]);
+                    if (++s == (uint32_t)Cfg::kStages) { s = 0; ph ^= 1u; }
+                    slot ^= 1u;
                 }
                 if (ok) tc_commit(&acc_full[as]);
             }

@@ -8,12 +8,23 @@
 // exchange between threads, the routing weight is one register per thread, and a thread
 // writes 64 contiguous bytes of its own output row per 32 columns (16-byte stores).
 //
-// Roles: warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps 2-5 epilogue.
+// Roles: warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps 2-9 epilogue.
 #include "common.cuh"
 #include "kernels.h"
 #include "tile_sched.cuh"
 
 namespace xmoe {
+
+#ifdef XMOE_TRACE
+// Debug build only: per-CTA, per-tile clock stamps {mma start, mma issued, acc full, epilogue done}.
+__device__ unsigned long long g_ff1_trace[148 * 64 * 4];
+#define XMOE_TRACE_STAMP(tile, k)                                                              \
+    do {                                                                                       \
+        if ((tile) < 64u && blockIdx.x < 148u) g_ff1_trace[(blockIdx.x * 64u + (tile)) * 4u + (k)] = clock64(); \
+    } while (0)
+#else
+#define XMOE_TRACE_STAMP(tile, k) do {} while (0)
+#endif
 
 namespace {
 
@@ -26,12 +37,13 @@ constexpr int kABytes = kTokTile * kStageKBytes;      // 16 KiB activations
 constexpr int kBBytes = 2 * kWTile * kStageKBytes;    // 32 KiB gate|up weights
 constexpr int kStageBytes = kABytes + kBBytes + 3 * kSfBytes;   // 54 KiB
 constexpr int kStages = 4;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;        // producer warp, MMA warp, 8 epilogue warps
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = 256;
 constexpr int kSfSlotCols = 48;        // per slot: 4 K-blocks x (tokens 4 + gate 4 + up 4)
 constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + 8192;
 
+template <int ACT>
 __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __grid_constant__ Ff1Args a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -55,7 +67,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(acc_full, 1);
-        mbar_init(acc_empty, 4);
+        mbar_init(acc_empty, 8);
         *abort_flag = 0u;
         mbar_fence_init();
         prefetch_tmap(&a.tm_w);
@@ -105,43 +117,50 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_nvfp4(kTokTile, 2 * kWTile);
-            uint32_t it = 0, tile_n = 0;
+            constexpr uint32_t kStage16 = kStageBytes >> 4;
+            const uint32_t a_lo0 = umma_desc_lo_sw128(smem_u32(smem));
+            const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(smem + kABytes));
+            const uint32_t sf_lo0 = umma_desc_lo_sf(smem_u32(smem + kABytes + kBBytes));
+            uint32_t tile_n = 0, s = 0, ph = 0, slot = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tile_n) {
                 if (!mbar_wait(acc_empty, (tile_n & 1u) ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
                 tc_fence_after();
-                for (int ks = 0; ks < k_stages; ++ks, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1u;
+                XMOE_TRACE_STAMP(tile_n, 0);
+                for (int ks = 0; ks < k_stages; ++ks) {
                     if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t st = smem_u32(smem + (size_t)s * kStageBytes);
-                    const uint32_t sf_smem = st + kABytes + kBBytes;
-                    const uint32_t sf_tmem = tmem_base + kAccCols + (it & 1u) * kSfSlotCols;
+                    const uint32_t sf_lo = sf_lo0 + s * kStage16;
+                    const uint32_t sf_tmem = tmem_base + kAccCols + slot * kSfSlotCols;
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
-                        tmem_cp_sf(sf_tmem + kb * 4, umma_desc_sf(sf_smem + kb * 512));                         // tokens
-                        tmem_cp_sf(sf_tmem + 16 + kb * 8, umma_desc_sf(sf_smem + kSfBytes + kb * 512));         // gate
-                        tmem_cp_sf(sf_tmem + 16 + kb * 8 + 4, umma_desc_sf(sf_smem + 2 * kSfBytes + kb * 512)); // up
+                        tmem_cp_sf_lo(sf_tmem + kb * 4, sf_lo + kb * 32);                                // tokens
+                        tmem_cp_sf_lo(sf_tmem + 16 + kb * 8, sf_lo + (kSfBytes >> 4) + kb * 32);         // gate
+                        tmem_cp_sf_lo(sf_tmem + 16 + kb * 8 + 4, sf_lo + 2 * (kSfBytes >> 4) + kb * 32); // up
                     }
-                    const uint64_t da = umma_desc_sw128(st);
-                    const uint64_t db = umma_desc_sw128(st + kABytes);
+                    const uint32_t a_lo = a_lo0 + s * kStage16;
+                    const uint32_t b_lo = b_lo0 + s * kStage16;
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
-                        const uint64_t koff = (uint64_t)((kb * 32) >> 4);
-                        mma_nvfp4(tmem_base, da + koff, db + koff, idesc, sf_tmem + kb * 4, sf_tmem + 16 + kb * 8,
-                                  (ks | kb) ? 1u : 0u);
+                        mma_nvfp4_lo(tmem_base, a_lo + kb * 2, b_lo + kb * 2, idesc, sf_tmem + kb * 4,
+                                     sf_tmem + 16 + kb * 8, (ks | kb) ? 1u : 0u);
                     }
                     tc_commit(&empty_bar[s]);
+                    if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+                    slot ^= 1u;
                 }
                 if (ok) tc_commit(acc_full);
+                XMOE_TRACE_STAMP(tile_n, 1);
             }
         }
     } else {
+        // 8 epilogue warps: two per lane quadrant, each draining half of the 128 I columns, so
+        // every scheduler has two warps to interleave around the transcendental unit.
         const int q = warp & 3;
+        const int col_half = (warp - 2) >> 2;
         const float xgs_inv = a.scale->xgs_inv;
         uint16_t* yact = reinterpret_cast<uint16_t*>(a.yact);
         const uint16_t* row_w = reinterpret_cast<const uint16_t*>(a.row_weight);
@@ -153,13 +172,14 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
             const int r = t.row0 + n_local;
             const float w = row_ok ? bf16_bits_to_f32(row_w[r]) : 0.f;
             const float sg = a.w13_gs[t.e * 2 + 0] * xgs_inv;
-            const float su = a.w13_gs[t.e * 2 + 1] * xgs_inv;
-            const int i0 = t.wt * kWTile;
+            const float su = a.w13_gs[t.e * 2 + 1] * xgs_inv * w;  // routing weight folded into the up scale
+            const int i0 = t.wt * kWTile + col_half * 64;
             if (!mbar_wait(acc_full, tile_n & 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
             tc_fence_after();
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+            if (threadIdx.x == 64) XMOE_TRACE_STAMP(tile_n, 2);
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + col_half * 64;
 #pragma unroll 1
-            for (int c0 = 0; c0 < kWTile; c0 += 32) {
+            for (int c0 = 0; c0 < 64; c0 += 32) {
                 if (i0 + c0 >= a.I) break;
                 uint32_t g[32], u[32];
                 tmem_ld32(lane_addr + c0, g);
@@ -169,10 +189,10 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
                     uint32_t o[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const float y0 = glu_act(__uint_as_float(g[2 * j]) * sg, __uint_as_float(u[2 * j]) * su,
-                                                 a.activation, a.alpha, a.limit) * w;
-                        const float y1 = glu_act(__uint_as_float(g[2 * j + 1]) * sg, __uint_as_float(u[2 * j + 1]) * su,
-                                                 a.activation, a.alpha, a.limit) * w;
+                        const float y0 = glu_act_t<ACT>(__uint_as_float(g[2 * j]) * sg, __uint_as_float(u[2 * j]) * su,
+                                                        a.alpha, a.limit, w);
+                        const float y1 = glu_act_t<ACT>(__uint_as_float(g[2 * j + 1]) * sg,
+                                                        __uint_as_float(u[2 * j + 1]) * su, a.alpha, a.limit, w);
                         o[j] = pack_bf16x2(y0, y1);
                     }
                     uint4* dst = reinterpret_cast<uint4*>(yact + (size_t)r * a.I + i0 + c0);
@@ -183,6 +203,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
             }
             tc_fence_before();
             __syncwarp();
+            if (threadIdx.x == 64) XMOE_TRACE_STAMP(tile_n, 3);
             if (lane == 0) mbar_arrive(acc_empty);
         }
     }
@@ -196,18 +217,34 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
     if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
-}  // namespace
-
-int launch_ff1_prefill(const Ff1Args& a, cudaStream_t stream) {
+template <int ACT>
+int launch_prefill_act(const Ff1Args& a, cudaStream_t stream) {
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(ff1_nvfp4_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(ff1_nvfp4_prefill_kernel<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kSmemBytes) != cudaSuccess)
             return XMOE_ERR_CUDA;
         attr_set = true;
     }
-    ff1_nvfp4_prefill_kernel<<<a.num_sms, kThreads, kSmemBytes, stream>>>(a);
+    ff1_nvfp4_prefill_kernel<ACT><<<a.num_sms, kThreads, kSmemBytes, stream>>>(a);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+}  // namespace
+
+#ifdef XMOE_TRACE
+extern "C" int xmoe_ff1_trace_dump(unsigned long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_ff1_trace, sizeof(g_ff1_trace));
+}
+#endif
+
+int launch_ff1_prefill(const Ff1Args& a, cudaStream_t stream) {
+    switch (a.activation) {
+        case 0: return launch_prefill_act<0>(a, stream);
+        case 1: return launch_prefill_act<1>(a, stream);
+        case 2: return launch_prefill_act<2>(a, stream);
+        default: return XMOE_ERR_SHAPE;
+    }
 }
 
 }  // namespace xmoe

@@ -1,57 +1,62 @@
-// FF2: grouped W4A16 down projection. int4 group-128 weights are expanded to bf16 in
-// shared memory ahead of a bf16 tcgen05 MMA; activations are the bf16 FF1 output.
+// FF2: grouped W4A16 down projection. int4 group-128 weights are expanded to bf16 on the
+// way into TENSOR MEMORY (the MMA's A operand), activations are the bf16 FF1 output staged
+// by TMA; accumulation is bf16 x bf16 -> fp32 on tcgen05.
 //
 // Weight contract: symmetric int4, group 128 along K, w = (u4 - 8) * scale[k/128] -- the
 // GPTQ / compressed-tensors contract of the reference's INT4 lane
 // (xFused-XXXX-Kernels/xMoE/xW4A16/sm75/xR64/xR64ABSRepack.cu:3-24, xR64ABS.cuh:30-34,
-// vllm/xcaliber_int4_vllm/method.py:188-203). The "expand 4-bit weights with a few
-// logic ops, then use the 16-bit tensor path" idea is the one the reference sketches in
-// xFused-NVFP4-Kernels/ptx.cuh:1-83; the expansion here is the integer flavour:
-// (nibble | 0x4300) is the bf16 value 128 + nibble, minus 136 gives nibble - 8 exactly,
-// one bf16x2 multiply applies the group scale (one rounding, same as bf16(w * s)).
+// vllm/xcaliber_int4_vllm/method.py:188-203). The "expand 4-bit weights with a few logic
+// ops, then use the 16-bit tensor path" idea is the one the reference sketches in
+// xFused-NVFP4-Kernels/ptx.cuh:1-83; here the expansion is the integer flavour:
+// (nibble | 0x4300) is the bf16 value 128 + nibble, minus 136 gives nibble - 8 exactly, one
+// bf16x2 multiply applies the group scale (a single rounding, i.e. bf16((u4 - 8) * s)).
 //
-// Structure (swap-AB like FF1: 128 output features = MMA M, NT tokens = MMA N):
-//   warp 0      TMA producer: raw int4 tile (128 rows x 64 B = K 128), its 128 bf16 group
-//               scales, and the bf16 activation tile (NT rows x K 128, 128-byte swizzle)
-//   warps 6-13  dequantise the raw tile into a K-major 128-byte-swizzled bf16 tile
-//               (two 64-K slabs), fence to the async proxy, signal the MMA warp
-//   warp 1      tcgen05.mma kind::f16 (bf16 x bf16 -> fp32 in TMEM), K = 16 per instruction
-//   warps 2-5   epilogue: tcgen05.ld -> bf16 rows [packed row, H]
+// Structure (128 output features = MMA M, NT packed token rows = MMA N):
+//   warp 0       TMA producer: raw int4 tile (128 rows x 64 B = K 128, 64-byte swizzle so
+//                that one thread per row reads without bank conflicts), the 128 bf16 group
+//                scales of the tile, and the bf16 activation tile (NT x K 128, 128-byte swizzle)
+//   warps 6-21   dequantise (4 groups of 4 warps, stages round-robin): thread = weight row,
+//                128 K; the bf16 pairs go straight to
+//                tensor memory with tcgen05.st (lane = row, column = K pair). The expanded
+//                weights never touch shared memory, which was the bottleneck of a first
+//                version that wrote a bf16 tile to shared memory (10 B of shared-memory
+//                traffic per weight byte).
+//   warp 1       tcgen05.mma kind::f16 with A from tensor memory, B from shared memory
+//   warps 2-5    epilogue: tcgen05.ld, transpose 32x32 blocks through shared memory so that
+//                each lane owns one token row, 16-byte stores to [packed row, H]
 // One K stage is exactly one quantisation group, so a row needs one scale per stage.
+// All mbarrier waits are bounded (see common.cuh).
 #include <cuda_bf16.h>
 
 #include "common.cuh"
 #include "kernels.h"
+#include "tile_sched.cuh"
 
 namespace xmoe {
 
 namespace {
 
 constexpr int kBlockM = 128;
-constexpr int kStageK = 128;                     // one int4 group
-constexpr int kRawBytes = kBlockM * kStageK / 2; // 8 KiB
-constexpr int kScaleBytes = kBlockM * 2;         // 256 B
-constexpr int kADqBytes = kBlockM * kStageK * 2; // 32 KiB = two 16 KiB slabs
-constexpr int kDqWarps = 8;
-constexpr int kThreads = 32 * (6 + kDqWarps);    // 448
+constexpr int kStageK = 128;                      // one int4 group
+constexpr int kRawBytes = kBlockM * kStageK / 2;  // 8 KiB
+constexpr int kMaxThreads = 32 * (6 + 4 * 6);
 constexpr int kMaxExperts = 1024 + 8;
-constexpr int kTmemCols = 256;
+constexpr int kTmemCols = 512;
+constexpr int kACols = kStageK / 2;               // 64 columns hold 128 bf16 of one row
+constexpr int kTailBytes = 5120 + 8192;           // barriers + tile prefix + epilogue transpose
 
 template <int NT>
 struct Ff2Cfg {
     static constexpr int kBBytes = NT * kStageK * 2;        // two slabs of NT x 128 B
     static constexpr int kStageBytes = kRawBytes + 1024 /*scales, padded*/ + kBBytes;
-    static constexpr int kStages = NT >= 128 ? 3 : (NT >= 64 ? 3 : 5);
-    static constexpr int kADqStages = NT >= 128 ? 3 : 4;  // bf16 weight tiles in flight between dequant and MMA
-    static constexpr int kAccStages = 2;
-    static_assert(kAccStages * NT <= kTmemCols, "TMEM budget");
-    static constexpr int kTxBytes = kRawBytes + kScaleBytes + kBBytes;
-    static constexpr size_t kSmemBytes =
-        1024 + (size_t)kStages * kStageBytes + (size_t)kADqStages * kADqBytes + 5120;
-};
-
-struct TileInfo {
-    int e, mt, nt_idx, count, row0;
+    static constexpr int kStages = NT >= 128 ? 5 : (NT >= 64 ? 8 : 12);
+    // expanded-weight buffers in tensor memory == independent dequant groups of 4 warps
+    static constexpr int kARing = NT >= 128 ? 4 : 6;
+    static constexpr int kDqGroups = kARing;
+    static constexpr int kThreads = 32 * (6 + 4 * kDqGroups);
+    static constexpr int kAccBase = kARing * kACols;   // accumulators follow the A ring
+    static_assert(kAccBase + 2 * NT <= kTmemCols, "TMEM budget");
+    static constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kTailBytes;
 };
 
 __device__ __forceinline__ __nv_bfloat162 bf162_from_bits(uint32_t bits) {
@@ -65,59 +70,48 @@ __device__ __forceinline__ uint32_t bits_from_bf162(__nv_bfloat162 v) {
     return bits;
 }
 
-__device__ __forceinline__ void build_tile_prefix(int* prefix, const int32_t* counts, int e_tot, int mt_tiles, int NT) {
-    const int lane = threadIdx.x & 31;
-    int carry = 0;
-    for (int base = 0; base < e_tot; base += 32) {
-        const int e = base + lane;
-        const int v = e < e_tot ? ((counts[e] + NT - 1) / NT) * mt_tiles : 0;
-        int incl = v;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const int o = __shfl_up_sync(0xffffffffu, incl, d);
-            if (lane >= d) incl += o;
-        }
-        if (e < e_tot) prefix[e] = carry + incl - v;
-        carry += __shfl_sync(0xffffffffu, incl, 31);
-    }
-    if (lane == 0) prefix[e_tot] = carry;
+// D[tmem] (+)= A[tmem] * B[smem], bf16 x bf16 -> fp32, K = 16 (A: lane = row, 8 columns).
+__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 
-__device__ __forceinline__ TileInfo decode_tile(int item, const int* prefix, const int32_t* counts,
-                                                const int32_t* offsets, int e_tot, int NT) {
-    int lo = 0, hi = e_tot;
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (prefix[mid] <= item) lo = mid; else hi = mid;
-    }
-    TileInfo t;
-    t.e = lo;
-    const int local = item - prefix[lo];
-    t.count = counts[lo];
-    const int n_tiles = (t.count + NT - 1) / NT;
-    t.mt = local / n_tiles;
-    t.nt_idx = local % n_tiles;
-    t.row0 = offsets[lo] + t.nt_idx * NT;
-    return t;
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
 }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 template <int NT>
-__global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_kernel(const __grid_constant__ Ff2Args a) {
+__global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(const __grid_constant__ Ff2Args a) {
     using Cfg = Ff2Cfg<NT>;
+    constexpr int kARing = Cfg::kARing, kDqGroups = Cfg::kDqGroups, kAccBase = Cfg::kAccBase;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* stage_base = smem;
-    uint8_t* adq_base = smem + (size_t)Cfg::kStages * Cfg::kStageBytes;
-    uint8_t* tail = adq_base + (size_t)Cfg::kADqStages * kADqBytes;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // [kStages]   TMA landed
-    uint64_t* empty_bar = full_bar + 8;                      // [kStages]   dequant warps + MMA done with the stage
-    uint64_t* adq_full = empty_bar + 8;                      // [4]         bf16 weight tile ready
-    uint64_t* adq_empty = adq_full + 4;                      // [4]         MMAs reading it retired
-    uint64_t* acc_full = adq_empty + 4;                      // [2]
+    uint8_t* tail = smem + (size_t)Cfg::kStages * Cfg::kStageBytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // [16] TMA landed
+    uint64_t* empty_bar = full_bar + 16;                     // [16] dequant warps + MMA done with the stage
+    uint64_t* adq_full = empty_bar + 16;                     // [8]  expanded weights are in tensor memory
+    uint64_t* adq_empty = adq_full + 8;                      // [8]  MMAs reading them retired
+    uint64_t* acc_full = adq_empty + 8;                      // [2]
     uint64_t* acc_empty = acc_full + 2;                      // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    int* prefix = reinterpret_cast<int*>(tail + 256);
+    int* prefix = reinterpret_cast<int*>(tail + 512);
+    uint16_t* transpose = reinterpret_cast<uint16_t*>(tail + 5120);  // 4 warps x 32 x 32 bf16
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -127,10 +121,10 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_kernel(const __grid_con
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::kStages; ++s) {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], kDqWarps + 1);
+            mbar_init(&empty_bar[s], 4 + 1);  // the 4 warps of one dequant group + the MMA commit
         }
-        for (int s = 0; s < Cfg::kADqStages; ++s) {
-            mbar_init(&adq_full[s], kDqWarps);
+        for (int s = 0; s < kARing; ++s) {
+            mbar_init(&adq_full[s], 4);
             mbar_init(&adq_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -146,7 +140,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_kernel(const __grid_con
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
-    if (warp == 2) build_tile_prefix(prefix, a.counts, a.E_tot, mt_tiles, NT);
+    if (warp == 2) tile_prefix_build(prefix, a.counts, a.E_tot, mt_tiles, NT);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -160,8 +154,8 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_kernel(const __grid_con
             uint32_t it = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
-                const TileInfo t = decode_tile(item, prefix, a.counts, a.offsets, a.E_tot, NT);
-                const int h0 = t.mt * kBlockM;
+                const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
+                const int h0 = t.wt * kBlockM;
                 const int w_row = t.e * a.H + h0;
                 const int rows_here = min(kBlockM, a.H - h0);
                 const uint32_t scale_bytes = (uint32_t)rows_here * 2u;  // H % 8 == 0 keeps this a multiple of 16
@@ -187,37 +181,36 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_kernel(const __grid_con
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(kBlockM, NT);
-            uint32_t it = 0, tile_n = 0;
+            const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(stage_base + kRawBytes + 1024));
+            uint32_t tile_n = 0;
+            uint32_t s = 0, ph = 0, d = 0, dph = 0;  // smem stage / phase, tensor-memory A buffer / phase
             bool ok = true;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tile_n) {
                 const uint32_t as = tile_n & 1u;
                 const uint32_t aph = (tile_n >> 1) & 1u;
                 if (!mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
                 tc_fence_after();
-                const uint32_t acc = tmem_base + as * NT;
-                for (int ks = 0; ks < k_stages; ++ks, ++it) {
-                    const int s = it % Cfg::kStages;
-                    const uint32_t ph = (it / Cfg::kStages) & 1u;
-                    const int d = it % Cfg::kADqStages;
-                    const uint32_t dph = (it / Cfg::kADqStages) & 1u;
+                const uint32_t acc = tmem_base + kAccBase + as * NT;
+                for (int ks = 0; ks < k_stages; ++ks) {
                     if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
                         !mbar_wait(&adq_full[d], dph, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_smem = smem_u32(adq_base + (size_t)d * kADqBytes);
-                    const uint32_t b_smem = smem_u32(stage_base + (size_t)s * Cfg::kStageBytes + kRawBytes + 1024);
+                    const uint32_t a_tmem = tmem_base + d * kACols;
+                    const uint32_t b_lo = b_lo0 + s * (uint32_t)(Cfg::kStageBytes >> 4);
 #pragma unroll
                     for (int kk = 0; kk < kStageK / 16; ++kk) {
-                        const int slab = kk >> 2;
-                        const uint64_t koff = (uint64_t)(((kk & 3) * 32) >> 4);
-                        const uint64_t da = umma_desc_sw128(a_smem + slab * (kBlockM * 128)) + koff;
-                        const uint64_t db = umma_desc_sw128(b_smem + slab * (NT * 128)) + koff;
-                        mma_bf16(acc, da, db, idesc, (ks | kk) ? 1u : 0u);
+                        // slab kk/4 (64 K each), 32 bytes of K per MMA inside the 128-byte swizzle row
+                        constexpr int kSlab16 = (NT * 128) >> 4;
+                        mma_bf16_ts_lo(acc, a_tmem + kk * 8, b_lo + (kk >> 2) * kSlab16 + (kk & 3) * 2, idesc,
+                                       (ks | kk) ? 1u : 0u);
                     }
                     tc_commit(&empty_bar[s]);
                     tc_commit(&adq_empty[d]);
+                    if (++s == (uint32_t)Cfg::kStages) { s = 0; ph ^= 1u; }
+                    if (++d == (uint32_t)kARing) { d = 0; dph ^= 1u; }
                 }
                 if (ok) tc_commit(&acc_full[as]);
             }
@@ -227,27 +220,36 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_kernel(const __grid_con
         const int q = warp & 3;
         uint32_t tile_n = 0;
         uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
+        uint16_t* tp = transpose + q * 1024;  // this warp's 32 tokens x 32 features
         for (int item = blockIdx.x; item < total_tiles; item += gridDim.x, ++tile_n) {
-            const TileInfo t = decode_tile(item, prefix, a.counts, a.offsets, a.E_tot, NT);
+            const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
             const uint32_t as = tile_n & 1u;
             const uint32_t aph = (tile_n >> 1) & 1u;
             if (!mbar_wait(&acc_full[as], aph, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
             tc_fence_after();
-            const int h_idx = t.mt * kBlockM + q * 32 + lane;
-            const bool h_ok = h_idx < a.H;
+            const int h_base = t.wt * kBlockM + q * 32;  // first feature of this warp's 32 lanes
             const int n_valid = min(NT, t.count - t.nt_idx * NT);
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + as * NT;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAccBase + as * NT;
             for (int c0 = 0; c0 < NT; c0 += 32) {
                 if (c0 >= n_valid) break;
                 uint32_t v[32];
                 tmem_ld32(lane_addr + c0, v);
                 tmem_ld_wait();
+                // lane = feature, v[j] = token c0+j  ->  shared [token][feature]
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int n = c0 + j;
-                    if (n < n_valid && h_ok)
-                        out[(size_t)(t.row0 + n) * a.H + h_idx] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
+                for (int j = 0; j < 32; ++j) tp[j * 32 + lane] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
+                __syncwarp();
+                // lane = token: 32 features = 64 contiguous bytes of its output row
+                const uint4* src = reinterpret_cast<const uint4*>(tp + lane * 32);
+                const uint4 r0 = src[0], r1 = src[1], r2 = src[2], r3 = src[3];
+                if (c0 + lane < n_valid) {
+                    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(t.row0 + c0 + lane) * a.H + h_base);
+                    if (h_base < a.H) dst[0] = r0;
+                    if (h_base + 8 < a.H) dst[1] = r1;
+                    if (h_base + 16 < a.H) dst[2] = r2;
+                    if (h_base + 24 < a.H) dst[3] = r3;
                 }
+                __syncwarp();
             }
             tc_fence_before();
             __syncwarp();
@@ -255,47 +257,56 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_kernel(const __grid_con
         }
     } else {
         // ------------------------------ dequantiser --------------------------------
-        const int dq_tid = threadIdx.x - 6 * 32;  // 0..255
+        // Tensor memory lanes are reachable per warp quadrant (warp index mod 4), so four
+        // consecutive warps cover the 128 rows of a tile. kDqGroups such groups take the K
+        // stages round-robin: expanding one stage is a serial chain of ~300 instructions per
+        // thread, and independent groups are what keeps several stages in flight.
+        const int quadrant = warp & 3;
+        const int group = (warp - 6) >> 2;
+        const int row = quadrant * 32 + lane;
+        const uint32_t swz = (uint32_t)(row >> 1) & 3u;  // 64-byte TMA swizzle: 16-byte chunk ^= (row / 2) % 4
+        const __nv_bfloat162 bias = bf162_from_bits(0x43084308u);  // 136.0 twice
         uint32_t it = 0;
         bool ok = true;
         for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
             for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                if ((int)(it % kDqGroups) != group) continue;
                 const int s = it % Cfg::kStages;
                 const uint32_t ph = (it / Cfg::kStages) & 1u;
-                const int d = it % Cfg::kADqStages;
-                const uint32_t dph = (it / Cfg::kADqStages) & 1u;
+                const int d = it % kARing;
+                const uint32_t dph = (it / kARing) & 1u;
                 if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
                     !mbar_wait(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) {
                     ok = false;
                     break;
                 }
+                tc_fence_after();
                 const uint8_t* st = stage_base + (size_t)s * Cfg::kStageBytes;
-                const uint4* raw = reinterpret_cast<const uint4*>(st);
-                const uint16_t* sc = reinterpret_cast<const uint16_t*>(st + kRawBytes);
-                uint8_t* dst = adq_base + (size_t)d * kADqBytes;
+                const uint32_t sraw = reinterpret_cast<const uint16_t*>(st + kRawBytes)[row];
+                const __nv_bfloat162 s2 = bf162_from_bits(sraw | (sraw << 16));
+                const uint32_t a_lane = tmem_base + ((uint32_t)(quadrant * 32) << 16) + d * kACols;
 #pragma unroll
-                for (int rep = 0; rep < 2; ++rep) {
-                    const int c = dq_tid + rep * 256;  // 16-byte chunk of the raw tile
-                    const int row = c >> 2, part = c & 3;
-                    const uint4 r4 = raw[c];
-                    const uint32_t words[4] = {r4.x, r4.y, r4.z, r4.w};
-                    const uint32_t sraw = sc[row];
-                    const __nv_bfloat162 s2 = bf162_from_bits(sraw | (sraw << 16));
-                    const __nv_bfloat162 bias = bf162_from_bits(0x43084308u);  // 136.0 twice
-                    uint8_t* slab = dst + (part >> 1) * (kBlockM * 128) + (row >> 3) * 1024 + (row & 7) * 128;
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t o[32];
 #pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        uint32_t o[4];
+                    for (int c = 0; c < 2; ++c) {
+                        const uint32_t chunk = (uint32_t)(half * 2 + c) ^ swz;
+                        const uint4 r4 = *reinterpret_cast<const uint4*>(st + row * 64 + chunk * 16);
+                        const uint32_t words[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint32_t bits = ((words[w] >> (4 * j)) & 0x000f000fu) | 0x43004300u;
-                            o[j] = bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(bits), bias), s2));
+                        for (int w = 0; w < 4; ++w) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t bits = ((words[w] >> (4 * j)) & 0x000f000fu) | 0x43004300u;
+                                o[(c * 4 + w) * 4 + j] =
+                                    bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(bits), bias), s2));
+                            }
                         }
-                        const int chunk = (part & 1) * 4 + w;  // 16-byte chunk inside the 128-byte row
-                        *reinterpret_cast<uint4*>(slab + ((chunk ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                     }
+                    tmem_st32(a_lane + half * 32, o);
                 }
-                fence_proxy_async_smem();
+                tmem_st_wait();
+                tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(&adq_full[d]);
@@ -324,7 +335,7 @@ int launch_ff2_nt(const Ff2Args& a, cudaStream_t stream) {
             return XMOE_ERR_CUDA;
         attr_set = true;
     }
-    ff2_w4a16_kernel<NT><<<a.num_sms, kThreads, Cfg::kSmemBytes, stream>>>(a);
+    ff2_w4a16_kernel<NT><<<a.num_sms, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(a);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 

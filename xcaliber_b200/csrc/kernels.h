@@ -81,7 +81,7 @@ struct Ff1Args {
 };
 
 struct Ff2Args {
-    CUtensorMap tm_w;  // u8 [E_tot*H, I/2], box 64 B x 128 rows, no swizzle
+    CUtensorMap tm_w;  // u8 [E_tot*H, I/2], box 64 B x 128 rows, 64-byte swizzle
     CUtensorMap tm_y;  // bf16 [R_cap, I], box 64 elems x NT rows, 128-byte swizzle
     const void* w2_scale;  // bf16 [E_tot, G, H]
     const int32_t* counts;

@@ -70,6 +70,25 @@ __device__ __forceinline__ float glu_act(float g, float u, int activation, float
     return g * u * rcp_approx(1.0f + ex2_approx(-g * 1.4426950408889634f));
 }
 
+// Compile-time flavour for the prefill epilogue. `u_w` already carries the routing weight
+// (u * w); `w` is needed separately only where the activation adds a constant to u.
+template <int ACT>
+__device__ __forceinline__ float glu_act_t(float g, float u_w, float alpha, float limit, float w) {
+    if (ACT == 1) {
+        g = fminf(g, limit);
+        const float lw = limit * fabsf(w);
+        u_w = fminf(fmaxf(u_w, -lw), lw);  // clamp(u) * w == clamp(u * w, -limit|w|, limit|w|)
+        const float s = rcp_approx(1.0f + ex2_approx(-alpha * g * 1.4426950408889634f));
+        return g * s * (u_w + w);
+    }
+    if (ACT == 2) {
+        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        const float t = 1.0f - 2.0f * rcp_approx(1.0f + ex2_approx(2.0f * inner * 1.4426950408889634f));
+        return 0.5f * g * (1.0f + t) * u_w;
+    }
+    return g * u_w * rcp_approx(1.0f + ex2_approx(-g * 1.4426950408889634f));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
