@@ -158,6 +158,25 @@ int xmoe_route_pack(int32_t* topk_idx, void* topk_w, int32_t n_tokens, int32_t n
                     int32_t* topk_off, int32_t* topk_row, int32_t* row_token, void* row_weight, uint32_t* status,
                     xmoe_stream_t stream);
 
+/* No counterpart in the reference. xmoe_route_pack for callers that cannot hand over scratch
+ * because they cannot allocate device memory at this point: e.g. a serving engine whose memory
+ * pool already owns all free HBM, or a call site where cudaMalloc is unwelcome because it can
+ * synchronise the device. The chunk histograms live in a fixed array inside the library
+ * (264,192 bytes held by every GPU that loads it, until process exit), so the call allocates
+ * nothing: no cudaMalloc / cudaFree and no allocating library routine.
+ * Limits: n_tokens <= xmoe_route_pack_static_max_tokens() (16384) and num_experts + num_shared
+ * <= 1032; anything larger returns XMOE_ERR_LIMIT and launches nothing.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ * with that device current): make that first call before any stream capture begins.
+ * Every call shares the one array, which keeps the previous call's contents; nothing in it
+ * needs clearing (each call rewrites every entry it reads), but two calls that overlap on the
+ * GPU - other streams, other host threads - race on it. Outputs are identical to xmoe_route_pack. */
+int32_t xmoe_route_pack_static_max_tokens(void);
+int xmoe_route_pack_static(int32_t* topk_idx, void* topk_w, int32_t n_tokens, int32_t num_experts, int32_t top_k,
+                           int32_t idx_stride, int32_t num_shared, int32_t* counts, int32_t* offsets,
+                           int32_t* topk_off, int32_t* topk_row, int32_t* row_token, void* row_weight,
+                           uint32_t* status, xmoe_stream_t stream);
+
 /* Replaces moe_act_absmax_partial + moe_act_scale_finalize (sm120a/preamble.cuh:69-128).
  * scratch: 2 x u32, zero on entry (left zero on exit). act_scale: 4 x f32 = XGS, XGSINV, amax, unused. */
 int xmoe_act_amax(const void* x, size_t n_elems, uint32_t* scratch, float* act_scale, xmoe_stream_t stream);

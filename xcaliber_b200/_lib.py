@@ -64,6 +64,8 @@ SIGNATURES = {
     "xmoe_router_topk": (C.c_int, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P]),
     "xmoe_route_pack_scratch_bytes": (_SZ, [_I, _I, _I]),
     "xmoe_route_pack": (C.c_int, [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "xmoe_route_pack_static_max_tokens": (_I, []),
+    "xmoe_route_pack_static": (C.c_int, [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
     "xmoe_act_amax": (C.c_int, [_P, _SZ, _P, _P, _P]),
     "xmoe_act_scale_from_amax": (C.c_int, [_P, _P, _P]),
     "xmoe_act_quant_pack": (C.c_int, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P]),

@@ -370,7 +370,7 @@ const char* xmoe_status_string(int s) {
         case XMOE_ERR_WORKSPACE: return "workspace too small or not 1024-byte aligned";
         case XMOE_ERR_CUDA: return "CUDA runtime/driver call failed";
         case XMOE_ERR_TIMEOUT: return "a bounded device-side wait gave up";
-        case XMOE_ERR_LIMIT: return "size beyond the supported maximum";
+        case XMOE_ERR_LIMIT: return "size beyond the supported maximum (for the *_static entry points: the fixed scratch array)";
         default: return "unknown status";
     }
 }
@@ -551,6 +551,34 @@ int xmoe_route_pack(int32_t* topk_idx, void* topk_w, int32_t n, int32_t E, int32
     p.row_weight = row_weight;
     p.status = status;
     return launch_route_pack(p, (cudaStream_t)stream);
+}
+
+int32_t xmoe_route_pack_static_max_tokens(void) { return route_pack_static_max_tokens(); }
+
+int xmoe_route_pack_static(int32_t* topk_idx, void* topk_w, int32_t n, int32_t E, int32_t top_k, int32_t idx_stride,
+                           int32_t n_shared, int32_t* counts, int32_t* offsets, int32_t* topk_off, int32_t* topk_row,
+                           int32_t* row_token, void* row_weight, uint32_t* status, xmoe_stream_t stream) {
+    if (n < 0 || !topk_idx || !topk_w || !counts || !offsets || !topk_off || !topk_row || !row_token || !row_weight ||
+        !status)
+        return XMOE_ERR_ARG;
+    if (idx_stride < top_k + n_shared) return XMOE_ERR_SHAPE;
+    PackArgs p;
+    p.topk_idx = topk_idx;
+    p.topk_w = topk_w;
+    p.N = n;
+    p.E = E;
+    p.topk = top_k;
+    p.idx_stride = idx_stride;
+    p.n_shared = n_shared;
+    p.chunk_hist = nullptr;  // filled in with the library's own fixed device array
+    p.counts = counts;
+    p.offsets = offsets;
+    p.topk_off = topk_off;
+    p.topk_row = topk_row;
+    p.row_token = row_token;
+    p.row_weight = row_weight;
+    p.status = status;
+    return launch_route_pack_static(p, (cudaStream_t)stream);
 }
 
 int xmoe_act_amax(const void* x, size_t n_elems, uint32_t* scratch, float* act_scale, xmoe_stream_t stream) {

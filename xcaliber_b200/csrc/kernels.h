@@ -111,6 +111,8 @@ struct ActTopkArgs {
 int launch_router_topk(const RouterArgs& a, cudaStream_t stream);
 int route_pack_chunks(int N);
 int launch_route_pack(const PackArgs& a, cudaStream_t stream);
+int route_pack_static_max_tokens();
+int launch_route_pack_static(PackArgs a, cudaStream_t stream);  // scratch = a fixed device array of the library
 int launch_act_amax(const AmaxArgs& a, cudaStream_t stream);
 int launch_act_scale_from_amax(const float* amax, float* scale, cudaStream_t stream);
 int launch_act_quant(const QuantArgs& a, cudaStream_t stream);

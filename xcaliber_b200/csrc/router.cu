@@ -418,4 +418,41 @@ int launch_route_pack(const PackArgs& a, cudaStream_t stream) {
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 
+// ------------------------------------------------------------------------------------
+// Route pack for callers that must not allocate device memory.
+//
+// The per-chunk histograms normally live in caller-provided scratch. Some callers cannot
+// provide any: a serving engine that has already handed every free byte of the GPU to its
+// KV-cache pool, or a runtime that routes between layers where cudaMalloc is off limits
+// because it may synchronise the device. For them the scratch is this fixed array, which
+// every GPU that loads the library holds until the process exits (264,192 bytes).
+// It is sized for at most kStaticPackMaxTokens tokens and kMaxEtot experts; the entry
+// point refuses larger problems. Nothing in it has to start at zero (pass A overwrites
+// every entry pass B reads), but all calls share it: two calls that overlap on the GPU
+// (different streams, or a graph replay racing a direct call) corrupt each other.
+// ------------------------------------------------------------------------------------
+constexpr int kStaticPackMaxTokens = 16384;
+constexpr int kStaticPackChunks = kStaticPackMaxTokens / kPackChunk;  // 64
+static __device__ __align__(256) int32_t g_static_pack_scratch[kStaticPackChunks * kMaxEtot];
+
+int route_pack_static_max_tokens() { return kStaticPackMaxTokens; }
+
+int launch_route_pack_static(PackArgs a, cudaStream_t stream) {
+    if (a.N > kStaticPackMaxTokens) return XMOE_ERR_LIMIT;
+    if (a.E + a.n_shared > kMaxEtot) return XMOE_ERR_LIMIT;
+    // In host code the array's name is not a device address. Ask the runtime for the address
+    // once per device, with that device current, and hand the kernels the result.
+    constexpr int kMaxDevices = 64;
+    static int32_t* device_ptr[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return XMOE_ERR_CUDA;
+    if (device_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_pack_scratch) != cudaSuccess || p == nullptr) return XMOE_ERR_CUDA;
+        device_ptr[dev] = static_cast<int32_t*>(p);
+    }
+    a.chunk_hist = device_ptr[dev];
+    return launch_route_pack(a, stream);
+}
+
 }  // namespace xmoe
