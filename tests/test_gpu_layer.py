@@ -133,3 +133,12 @@ def test_deterministic_run_to_run():
     y1 = layer.forward(xa, la).clone()
     y2 = layer.forward(xa, la).clone()
     assert torch.equal(y1, y2)
+
+
+def test_long_k_prefill_uses_wide_ff2_tile():
+    # inter >= 2048 with prefill-sized experts: FF1 token-major kernel + FF2 with 256-token tiles,
+    # ragged last tiles (counts not multiples of 128 or 256)
+    shape = synth.scaled_shape(synth.SHAPES["mixtral"], hidden=256, inter=2048, num_experts=4)
+    _, _, _, _, y, ref, view = run_case(shape, 700)
+    assert view["token_tile"] == 128
+    check_stages(shape, 700, y, ref, view)

@@ -99,6 +99,10 @@ int pick_token_tile(const xmoe_config* c, int n) {
     return 32;
 }
 
+// FF2 may use a wider token tile than FF1: with a long K (I >= 2048) the 256-token tile keeps the
+// bf16 pipe at its full rate and the un-overlapped epilogue is small against the main loop.
+int ff2_token_tile(const xmoe_config* c, int nt) { return (nt == 128 && c->inter >= 2048) ? 256 : nt; }
+
 struct Layout {
     int k_eff, e_tot, kb_pad, mb, groups, nt, chunks;
     size_t rows;  // packed-row capacity
@@ -193,8 +197,10 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
             void* out_rows, uint32_t* status, int e_tot, int H, int I, size_t rows, int nt, cudaStream_t stream) {
     Ff2Args a;
     memset(&a, 0, sizeof(a));
-    int rc = make_tmap_2d(&a.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2_q, (uint64_t)I / 2, (uint64_t)e_tot * H, 64,
-                          128, CU_TENSOR_MAP_SWIZZLE_64B);
+    // K per stage: 128 (64-byte rows, 64-byte swizzle) up to 128-token tiles, 64 (32-byte rows) for 256
+    const bool wide = nt >= 256;
+    int rc = make_tmap_2d(&a.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2_q, (uint64_t)I / 2, (uint64_t)e_tot * H,
+                          wide ? 32 : 64, 128, wide ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc) return rc;
     rc = make_tmap_2d(&a.tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64, (uint32_t)nt,
                       CU_TENSOR_MAP_SWIZZLE_128B);
@@ -336,7 +342,7 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     prof_mark(6, stream);
 
     if ((rc = run_ff2(w->w2_q, w->w2_scale, b + L.off_yact, counts, offsets, b + L.off_out, status, L.e_tot, H, I,
-                      L.rows, L.nt, stream)))
+                      L.rows, ff2_token_tile(cfg, L.nt), stream)))
         return rc;
     prof_mark(7, stream);
 

@@ -34,28 +34,45 @@
 
 namespace xmoe {
 
+#ifdef XMOE_TRACE
+// Debug build only: per-CTA cycle totals of where each role waits.
+__device__ long long g_ff2_trace[148 * 16];
+#define XMOE_T0() const long long t0__ = clock64()
+#define XMOE_TACC(var) var += clock64() - t0__
+#define XMOE_TDUMP(slot, var) do { if (blockIdx.x < 148) g_ff2_trace[blockIdx.x * 16 + (slot)] = (var); } while (0)
+#else
+#define XMOE_T0() do {} while (0)
+#define XMOE_TACC(var) do {} while (0)
+#define XMOE_TDUMP(slot, var) do {} while (0)
+#endif
+
 namespace {
 
 constexpr int kBlockM = 128;
-constexpr int kStageK = 128;                      // one int4 group
-constexpr int kRawBytes = kBlockM * kStageK / 2;  // 8 KiB
-constexpr int kMaxThreads = 32 * (6 + 4 * 6);
 constexpr int kMaxExperts = 1024 + 8;
 constexpr int kTmemCols = 512;
-constexpr int kACols = kStageK / 2;               // 64 columns hold 128 bf16 of one row
-constexpr int kTailBytes = 5120 + 8192;           // barriers + tile prefix + epilogue transpose
+constexpr int kTailBytes = 5120 + 8192;  // barriers + tile prefix + epilogue transpose
 
+// NT <= 128: one K stage = one int4 group (K 128), two accumulators (epilogue overlaps the next
+// tile). NT = 256 (long-K prefill): a K=16 MMA lasts at least ~130 cycles whatever N is, so only
+// N = 256 runs the bf16 pipe at full rate; the 256-column accumulator is then single and the
+// stages are K 64 to keep a deep ring in shared memory.
 template <int NT>
 struct Ff2Cfg {
-    static constexpr int kBBytes = NT * kStageK * 2;        // two slabs of NT x 128 B
+    static constexpr int kStageK = NT >= 256 ? 64 : 128;
+    static constexpr int kRawBytes = kBlockM * kStageK / 2;   // int4 tile: 128 rows x kStageK/2 bytes
+    static constexpr int kACols = kStageK / 2;                // TMEM columns of one expanded stage
+    static constexpr int kSlabs = kStageK / 64;               // 128-byte-swizzle slabs of the token tile
+    static constexpr int kBBytes = NT * kStageK * 2;
     static constexpr int kStageBytes = kRawBytes + 1024 /*scales, padded*/ + kBBytes;
     static constexpr int kStages = NT >= 128 ? 5 : (NT >= 64 ? 8 : 12);
-    // expanded-weight buffers in tensor memory == independent dequant groups of 4 warps
-    static constexpr int kARing = NT >= 128 ? 4 : 6;
-    static constexpr int kDqGroups = kARing;
+    static constexpr int kARing = NT >= 256 ? 8 : (NT >= 128 ? 4 : 6);  // expanded-weight buffers in tensor memory
+    static constexpr int kDqGroups = NT >= 128 ? 4 : 6;                 // independent dequant groups of 4 warps
+    static constexpr int kAccStages = NT >= 256 ? 1 : 2;
     static constexpr int kThreads = 32 * (6 + 4 * kDqGroups);
-    static constexpr int kAccBase = kARing * kACols;   // accumulators follow the A ring
-    static_assert(kAccBase + 2 * NT <= kTmemCols, "TMEM budget");
+    static constexpr int kAccBase = kARing * kACols;          // accumulators follow the A ring
+    static_assert(kAccBase + kAccStages * NT <= kTmemCols, "TMEM budget");
+    static_assert(kStages <= 16 && kARing <= 8, "barrier arrays");
     static constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kTailBytes;
 };
 
@@ -98,6 +115,7 @@ template <int NT>
 __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(const __grid_constant__ Ff2Args a) {
     using Cfg = Ff2Cfg<NT>;
     constexpr int kARing = Cfg::kARing, kDqGroups = Cfg::kDqGroups, kAccBase = Cfg::kAccBase;
+    constexpr int kStageK = Cfg::kStageK, kRawBytes = Cfg::kRawBytes, kACols = Cfg::kACols, kAccStages = Cfg::kAccStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* stage_base = smem;
@@ -116,7 +134,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int mt_tiles = (a.H + kBlockM - 1) / kBlockM;
-    const int k_stages = a.groups;
+    const int k_stages = (a.I + kStageK - 1) / kStageK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::kStages; ++s) {
@@ -153,6 +171,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             const uint16_t* scales = reinterpret_cast<const uint16_t*>(a.w2_scale);
             uint32_t it = 0;
             bool ok = true;
+            long long tw_prod = 0, t_total = -clock64();
+            (void)tw_prod; (void)t_total;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
                 const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
                 const int h0 = t.wt * kBlockM;
@@ -162,20 +182,27 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 for (int ks = 0; ks < k_stages; ++ks, ++it) {
                     const int s = it % Cfg::kStages;
                     const uint32_t ph = (it / Cfg::kStages) & 1u;
-                    if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
-                        ok = false;
-                        break;
+                    {
+                        XMOE_T0();
+                        if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
+                            ok = false;
+                            break;
+                        }
+                        XMOE_TACC(tw_prod);
                     }
                     uint8_t* st = stage_base + (size_t)s * Cfg::kStageBytes;
                     mbar_expect_tx(&full_bar[s], kRawBytes + scale_bytes + Cfg::kBBytes);
                     tma_load_2d(st, &a.tm_w, ks * (kStageK / 2), w_row, &full_bar[s]);
-                    tma_load_1d(st + kRawBytes, scales + ((size_t)t.e * a.groups + ks) * a.H + h0, scale_bytes,
-                                &full_bar[s]);
+                    tma_load_1d(st + kRawBytes, scales + ((size_t)t.e * a.groups + (ks * kStageK) / 128) * a.H + h0,
+                                scale_bytes, &full_bar[s]);
                     uint8_t* b = st + kRawBytes + 1024;
-                    tma_load_2d(b, &a.tm_y, ks * kStageK, t.row0, &full_bar[s]);
-                    tma_load_2d(b + NT * 128, &a.tm_y, ks * kStageK + 64, t.row0, &full_bar[s]);
+#pragma unroll
+                    for (int slab = 0; slab < Cfg::kSlabs; ++slab)
+                        tma_load_2d(b + slab * NT * 128, &a.tm_y, ks * kStageK + slab * 64, t.row0, &full_bar[s]);
                 }
             }
+            XMOE_TDUMP(0, tw_prod);
+            XMOE_TDUMP(1, t_total + clock64());
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
@@ -185,18 +212,30 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             uint32_t tile_n = 0;
             uint32_t s = 0, ph = 0, d = 0, dph = 0;  // smem stage / phase, tensor-memory A buffer / phase
             bool ok = true;
+            long long tw_full = 0, tw_adq = 0, tw_acc = 0, t_issue = 0;
+            (void)tw_full; (void)tw_adq; (void)tw_acc; (void)t_issue;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tile_n) {
-                const uint32_t as = tile_n & 1u;
-                const uint32_t aph = (tile_n >> 1) & 1u;
-                if (!mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
+                const uint32_t as = tile_n % kAccStages;
+                const uint32_t aph = (tile_n / kAccStages) & 1u;
+                {
+                    XMOE_T0();
+                    if (!mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
+                    XMOE_TACC(tw_acc);
+                }
                 tc_fence_after();
                 const uint32_t acc = tmem_base + kAccBase + as * NT;
                 for (int ks = 0; ks < k_stages; ++ks) {
-                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
-                        !mbar_wait(&adq_full[d], dph, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) {
-                        ok = false;
-                        break;
+                    {
+                        XMOE_T0();
+                        if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
+                        XMOE_TACC(tw_full);
                     }
+                    {
+                        XMOE_T0();
+                        if (!mbar_wait(&adq_full[d], dph, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
+                        XMOE_TACC(tw_adq);
+                    }
+                    XMOE_T0();
                     tc_fence_after();
                     const uint32_t a_tmem = tmem_base + d * kACols;
                     const uint32_t b_lo = b_lo0 + s * (uint32_t)(Cfg::kStageBytes >> 4);
@@ -211,9 +250,14 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     tc_commit(&adq_empty[d]);
                     if (++s == (uint32_t)Cfg::kStages) { s = 0; ph ^= 1u; }
                     if (++d == (uint32_t)kARing) { d = 0; dph ^= 1u; }
+                    XMOE_TACC(t_issue);
                 }
                 if (ok) tc_commit(&acc_full[as]);
             }
+            XMOE_TDUMP(2, tw_full);
+            XMOE_TDUMP(3, tw_adq);
+            XMOE_TDUMP(4, tw_acc);
+            XMOE_TDUMP(5, t_issue);
         }
     } else if (warp < 6) {
         // ------------------------------ epilogue -----------------------------------
@@ -223,8 +267,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         uint16_t* tp = transpose + q * 1024;  // this warp's 32 tokens x 32 features
         for (int item = blockIdx.x; item < total_tiles; item += gridDim.x, ++tile_n) {
             const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
-            const uint32_t as = tile_n & 1u;
-            const uint32_t aph = (tile_n >> 1) & 1u;
+            const uint32_t as = tile_n % kAccStages;
+            const uint32_t aph = (tile_n / kAccStages) & 1u;
             if (!mbar_wait(&acc_full[as], aph, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
             tc_fence_after();
             const int h_base = t.wt * kBlockM + q * 32;  // first feature of this warp's 32 lanes
@@ -264,10 +308,13 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         const int quadrant = warp & 3;
         const int group = (warp - 6) >> 2;
         const int row = quadrant * 32 + lane;
-        const uint32_t swz = (uint32_t)(row >> 1) & 3u;  // 64-byte TMA swizzle: 16-byte chunk ^= (row / 2) % 4
+        // TMA swizzle of the raw tile: 64-byte rows -> chunk ^= (row / 2) % 4; 32-byte rows -> chunk ^= (row / 4) % 2
+        const uint32_t swz = kStageK == 128 ? ((uint32_t)(row >> 1) & 3u) : ((uint32_t)(row >> 2) & 1u);
         const __nv_bfloat162 bias = bf162_from_bits(0x43084308u);  // 136.0 twice
         uint32_t it = 0;
         bool ok = true;
+        long long dq_wfull = 0, dq_wempty = 0, dq_work = 0;
+        (void)dq_wfull; (void)dq_wempty; (void)dq_work;
         for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
             for (int ks = 0; ks < k_stages; ++ks, ++it) {
                 if ((int)(it % kDqGroups) != group) continue;
@@ -275,23 +322,29 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 const uint32_t ph = (it / Cfg::kStages) & 1u;
                 const int d = it % kARing;
                 const uint32_t dph = (it / kARing) & 1u;
-                if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
-                    !mbar_wait(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) {
-                    ok = false;
-                    break;
+                {
+                    XMOE_T0();
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
+                    XMOE_TACC(dq_wfull);
                 }
+                {
+                    XMOE_T0();
+                    if (!mbar_wait(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
+                    XMOE_TACC(dq_wempty);
+                }
+                XMOE_T0();
                 tc_fence_after();
                 const uint8_t* st = stage_base + (size_t)s * Cfg::kStageBytes;
                 const uint32_t sraw = reinterpret_cast<const uint16_t*>(st + kRawBytes)[row];
                 const __nv_bfloat162 s2 = bf162_from_bits(sraw | (sraw << 16));
                 const uint32_t a_lane = tmem_base + ((uint32_t)(quadrant * 32) << 16) + d * kACols;
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
+                for (int half = 0; half < kStageK / 64; ++half) {
                     uint32_t o[32];
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         const uint32_t chunk = (uint32_t)(half * 2 + c) ^ swz;
-                        const uint4 r4 = *reinterpret_cast<const uint4*>(st + row * 64 + chunk * 16);
+                        const uint4 r4 = *reinterpret_cast<const uint4*>(st + row * (kStageK / 2) + chunk * 16);
                         const uint32_t words[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
                         for (int w = 0; w < 4; ++w) {
@@ -312,7 +365,13 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     mbar_arrive(&adq_full[d]);
                     mbar_arrive(&empty_bar[s]);
                 }
+                XMOE_TACC(dq_work);
             }
+        }
+        if (warp == 6 && lane == 0) {
+            XMOE_TDUMP(6, dq_wfull);
+            XMOE_TDUMP(7, dq_wempty);
+            XMOE_TDUMP(8, dq_work);
         }
     }
 
@@ -341,12 +400,19 @@ int launch_ff2_nt(const Ff2Args& a, cudaStream_t stream) {
 
 }  // namespace
 
+#ifdef XMOE_TRACE
+extern "C" int xmoe_ff2_trace_dump(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_ff2_trace, sizeof(g_ff2_trace));
+}
+#endif
+
 int launch_ff2(const Ff2Args& a, cudaStream_t stream) {
     if (a.E_tot + 1 > kMaxExperts || a.H % 8 || a.I % 32) return XMOE_ERR_SHAPE;
     switch (a.nt) {
         case 32: return launch_ff2_nt<32>(a, stream);
         case 64: return launch_ff2_nt<64>(a, stream);
         case 128: return launch_ff2_nt<128>(a, stream);
+        case 256: return launch_ff2_nt<256>(a, stream);
         default: return XMOE_ERR_SHAPE;
     }
 }
