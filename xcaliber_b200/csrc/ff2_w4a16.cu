@@ -12,19 +12,19 @@
 // bf16x2 multiply applies the group scale (a single rounding, i.e. bf16((u4 - 8) * s)).
 //
 // Structure (128 output features = MMA M, NT packed token rows = MMA N):
-//   warp 0       TMA producer: raw int4 tile (128 rows x 64 B = K 128, 64-byte swizzle so
-//                that one thread per row reads without bank conflicts), the 128 bf16 group
-//                scales of the tile, and the bf16 activation tile (NT x K 128, 128-byte swizzle)
-//   warps 6-21   dequantise (4 groups of 4 warps, stages round-robin): thread = weight row,
-//                128 K; the bf16 pairs go straight to
-//                tensor memory with tcgen05.st (lane = row, column = K pair). The expanded
-//                weights never touch shared memory, which was the bottleneck of a first
-//                version that wrote a bf16 tile to shared memory (10 B of shared-memory
-//                traffic per weight byte).
-//   warp 1       tcgen05.mma kind::f16 with A from tensor memory, B from shared memory
-//   warps 2-5    epilogue: tcgen05.ld, transpose 32x32 blocks through shared memory so that
-//                each lane owns one token row, 16-byte stores to [packed row, H]
-// One K stage is exactly one quantisation group, so a row needs one scale per stage.
+//   warp 0      weight producer: TMA of the raw int4 tile (128 rows x K/2 bytes, swizzled so
+//               that one thread per row reads without bank conflicts) + its bf16 group scales
+//               into a DEEP ring (the weights come from HBM)
+//   warp 6      token producer: TMA of the bf16 activation tile (NT x K, 128-byte swizzle) into a
+//               SHORT ring (the activations come from L2)
+//   warps 7..   dequantise (groups of 4 warps, stages round-robin): thread = weight row; the
+//               bf16 pairs go straight to tensor memory with tcgen05.st (lane = row, column =
+//               K pair). Expanded weights never touch shared memory: a first version that
+//               wrote a bf16 tile to shared memory cost 10 B of shared-memory traffic per
+//               weight byte.
+//   warp 1      tcgen05.mma kind::f16 with A from tensor memory, B from shared memory
+//   warps 2-5   epilogue: tcgen05.ld, transpose 32x32 blocks through shared memory so that
+//               each lane owns one token row, 16-byte stores to [packed row, H]
 // All mbarrier waits are bounded (see common.cuh).
 #include <cuda_bf16.h>
 
@@ -52,28 +52,33 @@ constexpr int kBlockM = 128;
 constexpr int kMaxExperts = 1024 + 8;
 constexpr int kTmemCols = 512;
 constexpr int kTailBytes = 5120 + 8192;  // barriers + tile prefix + epilogue transpose
+constexpr int kFirstDqWarp = 7;
 
-// NT <= 128: one K stage = one int4 group (K 128), two accumulators (epilogue overlaps the next
-// tile). NT = 256 (long-K prefill): a K=16 MMA lasts at least ~130 cycles whatever N is, so only
-// N = 256 runs the bf16 pipe at full rate; the 256-column accumulator is then single and the
-// stages are K 64 to keep a deep ring in shared memory.
+// NT <= 128: one K stage = one int4 group (K 128), two accumulators (the epilogue overlaps the
+// next tile). NT = 256 (long-K prefill): a K=16 MMA occupies the tensor pipe for at least ~130
+// cycles whatever N is, so only N = 256 runs the bf16 pipe at full rate; the 256-column
+// accumulator is then single and the stages are K 64.
 template <int NT>
 struct Ff2Cfg {
     static constexpr int kStageK = NT >= 256 ? 64 : 128;
     static constexpr int kRawBytes = kBlockM * kStageK / 2;   // int4 tile: 128 rows x kStageK/2 bytes
+    static constexpr int kWStageBytes = kRawBytes + 512;      // + 128 bf16 scales, padded
     static constexpr int kACols = kStageK / 2;                // TMEM columns of one expanded stage
     static constexpr int kSlabs = kStageK / 64;               // 128-byte-swizzle slabs of the token tile
-    static constexpr int kBBytes = NT * kStageK * 2;
-    static constexpr int kStageBytes = kRawBytes + 1024 /*scales, padded*/ + kBBytes;
-    static constexpr int kStages = NT >= 128 ? 5 : (NT >= 64 ? 8 : 12);
+    static constexpr int kBStageBytes = NT * kStageK * 2;
+    static constexpr int kWStages = NT == 128 ? 12 : 16;      // weight ring (HBM latency)
+    static constexpr int kBStages = NT >= 256 ? 4 : (NT >= 128 ? 3 : (NT >= 64 ? 4 : 6));  // token ring (L2 latency)
     static constexpr int kARing = NT >= 256 ? 8 : (NT >= 128 ? 4 : 6);  // expanded-weight buffers in tensor memory
     static constexpr int kDqGroups = NT >= 128 ? 4 : 6;                 // independent dequant groups of 4 warps
     static constexpr int kAccStages = NT >= 256 ? 1 : 2;
-    static constexpr int kThreads = 32 * (6 + 4 * kDqGroups);
+    static constexpr int kThreads = 32 * (kFirstDqWarp + 4 * kDqGroups);
     static constexpr int kAccBase = kARing * kACols;          // accumulators follow the A ring
     static_assert(kAccBase + kAccStages * NT <= kTmemCols, "TMEM budget");
-    static_assert(kStages <= 16 && kARing <= 8, "barrier arrays");
-    static constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kTailBytes;
+    static_assert(kWStages <= 16 && kBStages <= 8 && kARing <= 8, "barrier arrays");
+    static_assert(kThreads <= 1024, "block size");
+    static constexpr size_t kSmemBytes =
+        1024 + (size_t)kBStages * kBStageBytes + (size_t)kWStages * kWStageBytes + kTailBytes;
+    static_assert(kSmemBytes <= 232448, "shared memory");
 };
 
 __device__ __forceinline__ __nv_bfloat162 bf162_from_bits(uint32_t bits) {
@@ -85,17 +90,6 @@ __device__ __forceinline__ uint32_t bits_from_bf162(__nv_bfloat162 v) {
     uint32_t bits;
     memcpy(&bits, &v, 4);
     return bits;
-}
-
-// D[tmem] (+)= A[tmem] * B[smem], bf16 x bf16 -> fp32, K = 16 (A: lane = row, 8 columns).
-__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
 }
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
@@ -115,20 +109,24 @@ template <int NT>
 __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(const __grid_constant__ Ff2Args a) {
     using Cfg = Ff2Cfg<NT>;
     constexpr int kARing = Cfg::kARing, kDqGroups = Cfg::kDqGroups, kAccBase = Cfg::kAccBase;
-    constexpr int kStageK = Cfg::kStageK, kRawBytes = Cfg::kRawBytes, kACols = Cfg::kACols, kAccStages = Cfg::kAccStages;
+    constexpr int kStageK = Cfg::kStageK, kRawBytes = Cfg::kRawBytes, kACols = Cfg::kACols;
+    constexpr int kAccStages = Cfg::kAccStages, kWStages = Cfg::kWStages, kBStages = Cfg::kBStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* stage_base = smem;
-    uint8_t* tail = smem + (size_t)Cfg::kStages * Cfg::kStageBytes;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // [16] TMA landed
-    uint64_t* empty_bar = full_bar + 16;                     // [16] dequant warps + MMA done with the stage
-    uint64_t* adq_full = empty_bar + 16;                     // [8]  expanded weights are in tensor memory
-    uint64_t* adq_empty = adq_full + 8;                      // [8]  MMAs reading them retired
-    uint64_t* acc_full = adq_empty + 8;                      // [2]
-    uint64_t* acc_empty = acc_full + 2;                      // [2]
+    uint8_t* b_base = smem;                                          // token ring
+    uint8_t* w_base = smem + (size_t)kBStages * Cfg::kBStageBytes;   // weight ring
+    uint8_t* tail = w_base + (size_t)kWStages * Cfg::kWStageBytes;
+    uint64_t* w_full = reinterpret_cast<uint64_t*>(tail);  // [16] raw weights + scales landed
+    uint64_t* w_empty = w_full + 16;                       // [16] the 4 warps of a dequant group are done with them
+    uint64_t* b_full = w_empty + 16;                       // [8]  token tile landed
+    uint64_t* b_empty = b_full + 8;                        // [8]  MMAs reading it retired
+    uint64_t* adq_full = b_empty + 8;                      // [8]  expanded weights are in tensor memory
+    uint64_t* adq_empty = adq_full + 8;                    // [8]  MMAs reading them retired
+    uint64_t* acc_full = adq_empty + 8;                    // [2]
+    uint64_t* acc_empty = acc_full + 2;                    // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    int* prefix = reinterpret_cast<int*>(tail + 512);
+    int* prefix = reinterpret_cast<int*>(tail + 640);
     uint16_t* transpose = reinterpret_cast<uint16_t*>(tail + 5120);  // 4 warps x 32 x 32 bf16
 
     const int warp = threadIdx.x >> 5;
@@ -137,9 +135,13 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
     const int k_stages = (a.I + kStageK - 1) / kStageK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::kStages; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], 4 + 1);  // the 4 warps of one dequant group + the MMA commit
+        for (int s = 0; s < kWStages; ++s) {
+            mbar_init(&w_full[s], 1);
+            mbar_init(&w_empty[s], 4);
+        }
+        for (int s = 0; s < kBStages; ++s) {
+            mbar_init(&b_full[s], 1);
+            mbar_init(&b_empty[s], 1);
         }
         for (int s = 0; s < kARing; ++s) {
             mbar_init(&adq_full[s], 4);
@@ -166,51 +168,74 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
     const int total_tiles = prefix[a.E_tot];
 
     if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
+        // ------------------------------ weight producer ---------------------------
         if (lane == 0) {
             const uint16_t* scales = reinterpret_cast<const uint16_t*>(a.w2_scale);
-            uint32_t it = 0;
+            uint32_t s = 0, ph = 0;
             bool ok = true;
-            long long tw_prod = 0, t_total = -clock64();
-            (void)tw_prod; (void)t_total;
+            long long tw_prod = 0;
+            (void)tw_prod;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
                 const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
                 const int h0 = t.wt * kBlockM;
                 const int w_row = t.e * a.H + h0;
                 const int rows_here = min(kBlockM, a.H - h0);
                 const uint32_t scale_bytes = (uint32_t)rows_here * 2u;  // H % 8 == 0 keeps this a multiple of 16
-                for (int ks = 0; ks < k_stages; ++ks, ++it) {
-                    const int s = it % Cfg::kStages;
-                    const uint32_t ph = (it / Cfg::kStages) & 1u;
+                for (int ks = 0; ks < k_stages; ++ks) {
                     {
                         XMOE_T0();
-                        if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
+                        if (!mbar_wait(&w_empty[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
                             ok = false;
                             break;
                         }
                         XMOE_TACC(tw_prod);
                     }
-                    uint8_t* st = stage_base + (size_t)s * Cfg::kStageBytes;
-                    mbar_expect_tx(&full_bar[s], kRawBytes + scale_bytes + Cfg::kBBytes);
-                    tma_load_2d(st, &a.tm_w, ks * (kStageK / 2), w_row, &full_bar[s]);
+                    uint8_t* st = w_base + (size_t)s * Cfg::kWStageBytes;
+                    mbar_expect_tx(&w_full[s], kRawBytes + scale_bytes);
+                    tma_load_2d(st, &a.tm_w, ks * (kStageK / 2), w_row, &w_full[s]);
                     tma_load_1d(st + kRawBytes, scales + ((size_t)t.e * a.groups + (ks * kStageK) / 128) * a.H + h0,
-                                scale_bytes, &full_bar[s]);
-                    uint8_t* b = st + kRawBytes + 1024;
-#pragma unroll
-                    for (int slab = 0; slab < Cfg::kSlabs; ++slab)
-                        tma_load_2d(b + slab * NT * 128, &a.tm_y, ks * kStageK + slab * 64, t.row0, &full_bar[s]);
+                                scale_bytes, &w_full[s]);
+                    if (++s == (uint32_t)kWStages) { s = 0; ph ^= 1u; }
                 }
             }
             XMOE_TDUMP(0, tw_prod);
-            XMOE_TDUMP(1, t_total + clock64());
+        }
+    } else if (warp == 6) {
+        // ------------------------------ token producer ----------------------------
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            long long tw_bprod = 0;
+            (void)tw_bprod;
+            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+                const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    {
+                        XMOE_T0();
+                        if (!mbar_wait(&b_empty[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
+                            ok = false;
+                            break;
+                        }
+                        XMOE_TACC(tw_bprod);
+                    }
+                    uint8_t* b = b_base + (size_t)s * Cfg::kBStageBytes;
+                    mbar_expect_tx(&b_full[s], Cfg::kBStageBytes);
+#pragma unroll
+                    for (int slab = 0; slab < Cfg::kSlabs; ++slab)
+                        tma_load_2d(b + slab * NT * 128, &a.tm_y, ks * kStageK + slab * 64, t.row0, &b_full[s]);
+                    if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
+                }
+            }
+            XMOE_TDUMP(1, tw_bprod);
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(kBlockM, NT);
-            const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(stage_base + kRawBytes + 1024));
+            constexpr int kSlab16 = (NT * 128) >> 4;
+            const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(b_base));
             uint32_t tile_n = 0;
-            uint32_t s = 0, ph = 0, d = 0, dph = 0;  // smem stage / phase, tensor-memory A buffer / phase
+            uint32_t s = 0, ph = 0, d = 0, dph = 0;  // token stage / phase, tensor-memory A buffer / phase
             bool ok = true;
             long long tw_full = 0, tw_adq = 0, tw_acc = 0, t_issue = 0;
             (void)tw_full; (void)tw_adq; (void)tw_acc; (void)t_issue;
@@ -227,7 +252,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 for (int ks = 0; ks < k_stages; ++ks) {
                     {
                         XMOE_T0();
-                        if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
+                        if (!mbar_wait(&b_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
                         XMOE_TACC(tw_full);
                     }
                     {
@@ -238,17 +263,16 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     XMOE_T0();
                     tc_fence_after();
                     const uint32_t a_tmem = tmem_base + d * kACols;
-                    const uint32_t b_lo = b_lo0 + s * (uint32_t)(Cfg::kStageBytes >> 4);
+                    const uint32_t b_lo = b_lo0 + s * (uint32_t)(Cfg::kBStageBytes >> 4);
 #pragma unroll
                     for (int kk = 0; kk < kStageK / 16; ++kk) {
                         // slab kk/4 (64 K each), 32 bytes of K per MMA inside the 128-byte swizzle row
-                        constexpr int kSlab16 = (NT * 128) >> 4;
                         mma_bf16_ts_lo(acc, a_tmem + kk * 8, b_lo + (kk >> 2) * kSlab16 + (kk & 3) * 2, idesc,
                                        (ks | kk) ? 1u : 0u);
                     }
-                    tc_commit(&empty_bar[s]);
+                    tc_commit(&b_empty[s]);
                     tc_commit(&adq_empty[d]);
-                    if (++s == (uint32_t)Cfg::kStages) { s = 0; ph ^= 1u; }
+                    if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
                     if (++d == (uint32_t)kARing) { d = 0; dph ^= 1u; }
                     XMOE_TACC(t_issue);
                 }
@@ -303,10 +327,10 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         // ------------------------------ dequantiser --------------------------------
         // Tensor memory lanes are reachable per warp quadrant (warp index mod 4), so four
         // consecutive warps cover the 128 rows of a tile. kDqGroups such groups take the K
-        // stages round-robin: expanding one stage is a serial chain of ~300 instructions per
-        // thread, and independent groups are what keeps several stages in flight.
+        // stages round-robin: expanding one stage is a serial chain of a few hundred
+        // instructions per thread, and independent groups keep several stages in flight.
         const int quadrant = warp & 3;
-        const int group = (warp - 6) >> 2;
+        const int group = (warp - kFirstDqWarp) >> 2;
         const int row = quadrant * 32 + lane;
         // TMA swizzle of the raw tile: 64-byte rows -> chunk ^= (row / 2) % 4; 32-byte rows -> chunk ^= (row / 4) % 2
         const uint32_t swz = kStageK == 128 ? ((uint32_t)(row >> 1) & 3u) : ((uint32_t)(row >> 2) & 1u);
@@ -318,13 +342,13 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
             for (int ks = 0; ks < k_stages; ++ks, ++it) {
                 if ((int)(it % kDqGroups) != group) continue;
-                const int s = it % Cfg::kStages;
-                const uint32_t ph = (it / Cfg::kStages) & 1u;
+                const int s = it % kWStages;
+                const uint32_t ph = (it / kWStages) & 1u;
                 const int d = it % kARing;
                 const uint32_t dph = (it / kARing) & 1u;
                 {
                     XMOE_T0();
-                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
+                    if (!mbar_wait(&w_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
                     XMOE_TACC(dq_wfull);
                 }
                 {
@@ -334,7 +358,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 }
                 XMOE_T0();
                 tc_fence_after();
-                const uint8_t* st = stage_base + (size_t)s * Cfg::kStageBytes;
+                const uint8_t* st = w_base + (size_t)s * Cfg::kWStageBytes;
                 const uint32_t sraw = reinterpret_cast<const uint16_t*>(st + kRawBytes)[row];
                 const __nv_bfloat162 s2 = bf162_from_bits(sraw | (sraw << 16));
                 const uint32_t a_lane = tmem_base + ((uint32_t)(quadrant * 32) << 16) + d * kACols;
@@ -363,12 +387,12 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(&adq_full[d]);
-                    mbar_arrive(&empty_bar[s]);
+                    mbar_arrive(&w_empty[s]);
                 }
                 XMOE_TACC(dq_work);
             }
         }
-        if (warp == 6 && lane == 0) {
+        if (warp == kFirstDqWarp && lane == 0) {
             XMOE_TDUMP(6, dq_wfull);
             XMOE_TDUMP(7, dq_wempty);
             XMOE_TDUMP(8, dq_work);
