@@ -1,0 +1,53 @@
+"""Worker for tests/test_gpu_ep.py: run under torch.distributed.run with 2+ ranks (NCCL).
+Every rank runs the expert-parallel layer on its own tokens and compares with the single-GPU
+layer holding all experts: outputs must be bit-identical (same kernels, same activation scale)."""
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+from xcaliber_b200 import ops, synth  # noqa: E402
+from xcaliber_b200.ep import ExpertParallelMoE  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    failures = []
+    for name, kw, n in [("toy", dict(), 96), ("dsv3", dict(hidden=512, inter=256, num_experts=64, act_topk_keep=0), 80)]:
+        shape = synth.scaled_shape(synth.SHAPES[name], **kw)
+        ck = synth.make_weights(shape, seed=0, device="cpu")
+        xs, ls = [], []
+        for r in range(world):
+            x, lg = synth.make_inputs(shape, ck, n + 8 * r, seed=r)
+            xs.append(x)
+            ls.append(lg)
+        ep = ExpertParallelMoE(shape, ck, device=dev)
+        y = ep.forward(xs[rank].to(dev), ls[rank].to(dev))
+        torch.cuda.synchronize()
+        # single-GPU reference on the concatenation of all ranks' tokens (same global amax)
+        pw = ops.PreparedWeights.from_checkpoint(shape, ck.w13_packed, ck.w13_scale, ck.w13_gs, ck.w2_qweight,
+                                                 ck.w2_scales, router_bias=ck.router_bias, device=dev)
+        full = ops.FusedMoE(shape, pw)
+        y_all = full.forward(torch.cat(xs).to(dev), torch.cat(ls).to(dev))
+        off = sum(t.shape[0] for t in xs[:rank])
+        ref = y_all[off:off + xs[rank].shape[0]]
+        if not torch.equal(y, ref):
+            diff = (y.float() - ref.float()).abs().max().item()
+            failures.append(f"{name}: rank {rank} max abs diff {diff}")
+    flag = torch.tensor([len(failures)], device=dev)
+    dist.all_reduce(flag)
+    if rank == 0:
+        print("EP_CHECK", "OK" if flag.item() == 0 else "FAIL", failures)
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()

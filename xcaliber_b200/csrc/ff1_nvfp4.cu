@@ -23,6 +23,7 @@
 //     all roles fall through to the common exit, where TMEM is released.
 #include "common.cuh"
 #include "kernels.h"
+#include "tile_sched.cuh"
 
 namespace xmoe {
 
@@ -92,21 +93,6 @@ __device__ __forceinline__ TileInfo decode_tile(int item, const int* prefix, con
     t.nt_idx = local % n_tiles;
     t.row0 = offsets[lo] + t.nt_idx * NT;
     return t;
-}
-
-__device__ __forceinline__ float glu_act(float g, float u, int activation, float alpha, float limit) {
-    if (activation == 1) {  // clamped SwiGLU: (min(g,limit) * sigmoid(alpha*g')) * (clamp(u) + 1)
-        g = fminf(g, limit);
-        u = fminf(fmaxf(u, -limit), limit);
-        const float s = rcp_approx(1.0f + ex2_approx(-alpha * g * 1.4426950408889634f));
-        return g * s * (u + 1.0f);
-    }
-    if (activation == 2) {  // tanh-approximated GELU gate
-        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
-        const float t = 1.0f - 2.0f * rcp_approx(1.0f + ex2_approx(2.0f * inner * 1.4426950408889634f));
-        return 0.5f * g * (1.0f + t) * u;
-    }
-    return g * u * rcp_approx(1.0f + ex2_approx(-g * 1.4426950408889634f));
 }
 
 template <int NT>
@@ -247,8 +233,8 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
             const uint32_t aph = (tile_n / Cfg::kAccStages) & 1u;
             if (!mbar_wait(&acc_full[as], aph, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
             tc_fence_after();
-            const float sg = a.w13_gs[t.e * 2 + 0] * xgs_inv;
-            const float su = a.w13_gs[t.e * 2 + 1] * xgs_inv;
+            const float sg = __fmul_rn(a.w13_gs[t.e * 2 + 0], xgs_inv);
+            const float su = __fmul_rn(a.w13_gs[t.e * 2 + 1], xgs_inv);
             const int i_idx = t.mt * kBlockM + q * 32 + lane;
             const bool i_ok = i_idx < a.I;
             const int n_valid = min(NT, t.count - t.nt_idx * NT);
@@ -265,8 +251,8 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
                     if (n < n_valid && i_ok) {
                         const int r = t.row0 + n;
                         const float w = bf16_bits_to_f32(row_w[r]);
-                        const float y = glu_act(__uint_as_float(g[j]) * sg, __uint_as_float(u[j]) * su, a.activation,
-                                                a.alpha, a.limit) * w;
+                        const float y = glu_apply(a.activation, __uint_as_float(g[j]), __uint_as_float(u[j]), sg,
+                                                  __fmul_rn(su, w), a.alpha, a.limit, w);
                         yact[(size_t)r * a.I + i_idx] = (uint16_t)f32_to_bf16_bits(y);
                     }
                 }

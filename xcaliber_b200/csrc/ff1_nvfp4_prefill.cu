@@ -171,8 +171,8 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
             const bool row_ok = t.nt_idx * kTokTile + n_local < t.count;
             const int r = t.row0 + n_local;
             const float w = row_ok ? bf16_bits_to_f32(row_w[r]) : 0.f;
-            const float sg = a.w13_gs[t.e * 2 + 0] * xgs_inv;
-            const float su = a.w13_gs[t.e * 2 + 1] * xgs_inv * w;  // routing weight folded into the up scale
+            const float sg = __fmul_rn(a.w13_gs[t.e * 2 + 0], xgs_inv);
+            const float su = __fmul_rn(__fmul_rn(a.w13_gs[t.e * 2 + 1], xgs_inv), w);  // routing weight folded into the up scale
             const int i0 = t.wt * kWTile + col_half * 64;
             if (!mbar_wait(acc_full, tile_n & 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
             tc_fence_after();
@@ -189,10 +189,10 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
                     uint32_t o[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const float y0 = glu_act_t<ACT>(__uint_as_float(g[2 * j]) * sg, __uint_as_float(u[2 * j]) * su,
-                                                        a.alpha, a.limit, w);
-                        const float y1 = glu_act_t<ACT>(__uint_as_float(g[2 * j + 1]) * sg,
-                                                        __uint_as_float(u[2 * j + 1]) * su, a.alpha, a.limit, w);
+                        const float y0 = glu_apply(ACT, __uint_as_float(g[2 * j]), __uint_as_float(u[2 * j]), sg, su,
+                                                   a.alpha, a.limit, w);
+                        const float y1 = glu_apply(ACT, __uint_as_float(g[2 * j + 1]), __uint_as_float(u[2 * j + 1]), sg,
+                                                   su, a.alpha, a.limit, w);
                         o[j] = pack_bf16x2(y0, y1);
                     }
                     uint4* dst = reinterpret_cast<uint4*>(yact + (size_t)r * a.I + i0 + c0);

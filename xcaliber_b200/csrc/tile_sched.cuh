@@ -70,23 +70,33 @@ __device__ __forceinline__ float glu_act(float g, float u, int activation, float
     return g * u * rcp_approx(1.0f + ex2_approx(-g * 1.4426950408889634f));
 }
 
-// Compile-time flavour for the prefill epilogue. `u_w` already carries the routing weight
-// (u * w); `w` is needed separately only where the activation adds a constant to u.
-template <int ACT>
-__device__ __forceinline__ float glu_act_t(float g, float u_w, float alpha, float limit, float w) {
-    if (ACT == 1) {
+// The one GLU epilogue both FF1 kernels use. g_acc / u_acc are the raw fp32 accumulators, sg the
+// gate scale (weight_global_scale * XGSINV), su_w the up scale times the routing weight, w the
+// routing weight (needed on its own only where the activation adds a constant to u). Every
+// operation is an explicit round-to-nearest intrinsic so that the compiler cannot contract or
+// reorder differently in different kernels: the decode and prefill variants, and therefore the
+// single-GPU and expert-parallel paths, produce bit-identical rows.
+__device__ __forceinline__ float glu_apply(int act, float g_acc, float u_acc, float sg, float su_w, float alpha,
+                                           float limit, float w) {
+    float g = __fmul_rn(g_acc, sg);
+    float u_w = __fmul_rn(u_acc, su_w);
+    if (act == 1) {  // clamped SwiGLU: min(g,limit) * sigmoid(alpha*g) * (clamp(u,-limit,limit) + 1) * w
         g = fminf(g, limit);
-        const float lw = limit * fabsf(w);
-        u_w = fminf(fmaxf(u_w, -lw), lw);  // clamp(u) * w == clamp(u * w, -limit|w|, limit|w|)
-        const float s = rcp_approx(1.0f + ex2_approx(-alpha * g * 1.4426950408889634f));
-        return g * s * (u_w + w);
+        const float lw = __fmul_rn(limit, fabsf(w));
+        u_w = fminf(fmaxf(u_w, -lw), lw);
+        const float e = ex2_approx(__fmul_rn(__fmul_rn(g, alpha), -1.4426950408889634f));
+        const float sgm = rcp_approx(__fadd_rn(1.0f, e));
+        return __fmul_rn(__fmul_rn(g, sgm), __fadd_rn(u_w, w));
     }
-    if (ACT == 2) {
-        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
-        const float t = 1.0f - 2.0f * rcp_approx(1.0f + ex2_approx(2.0f * inner * 1.4426950408889634f));
-        return 0.5f * g * (1.0f + t) * u_w;
+    if (act == 2) {  // tanh-GELU(g) * u * w
+        const float g3 = __fmul_rn(__fmul_rn(g, g), g);
+        const float inner = __fmul_rn(0.7978845608028654f, __fmaf_rn(0.044715f, g3, g));
+        const float e = ex2_approx(__fmul_rn(inner, 2.0f * 1.4426950408889634f));
+        const float t = __fmaf_rn(-2.0f, rcp_approx(__fadd_rn(1.0f, e)), 1.0f);
+        return __fmul_rn(__fmul_rn(__fmul_rn(0.5f, g), __fadd_rn(1.0f, t)), u_w);
     }
-    return g * u_w * rcp_approx(1.0f + ex2_approx(-g * 1.4426950408889634f));
+    const float e = ex2_approx(__fmul_rn(g, -1.4426950408889634f));  // silu(g) * u * w
+    return __fmul_rn(__fmul_rn(g, u_w), rcp_approx(__fadd_rn(1.0f, e)));
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
