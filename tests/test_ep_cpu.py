@@ -51,7 +51,7 @@ def _worker(rank, world, port, n_shared, results):
         results[rank] = float((y - exp).abs().max())
         # planning invariants
         plan = ep.plan_dispatch(idx, e_local, world)
-        assert sum(plan.send_counts) == n * k
+        assert int(plan.send_counts.sum()) == n * k
         dest = (idx.reshape(-1)[plan.send_order] // e_local)
         assert (dest[1:] >= dest[:-1]).all()
         assert (plan.send_order[plan.slot_pos.reshape(-1).long()] == torch.arange(n * k)).all()
@@ -80,7 +80,7 @@ def _failing_worker(rank, world, port, results):
             results[rank] = "left before the exchange"
             return  # this rank never joins the all-to-all
         try:
-            ep.exchange_counts([1, 1], device="cpu")
+            ep.exchange_counts(torch.tensor([1, 1]), device="cpu")
             results[rank] = "no error"
         except Exception as exc:  # the survivor must see an error, not hang
             results[rank] = f"error: {type(exc).__name__}"

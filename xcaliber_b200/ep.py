@@ -27,30 +27,38 @@ import torch.distributed as dist
 @dataclasses.dataclass
 class DispatchPlan:
     send_order: torch.Tensor    # i64 [N*k]: flat (token*k + slot) indices sorted by destination rank (stable)
-    send_counts: list[int]      # rows sent to each rank
+    send_counts: torch.Tensor   # i32 [world] rows sent to each rank (device)
     slot_pos: torch.Tensor      # i32 [N, k]: position of (token, slot) in send order
     local_expert: torch.Tensor  # i32 [N*k] in send order: expert id relative to the owner rank
 
 
 def plan_dispatch(topk_idx: torch.Tensor, experts_per_rank: int, world: int) -> DispatchPlan:
-    """topk_idx [N, k] global expert ids -> grouping of the N*k assignments by owner rank."""
+    """topk_idx [N, k] global expert ids -> grouping of the N*k assignments by owner rank.
+    Stable counting sort over the (few) ranks with a one-hot running sum: no device sort."""
     n, k = topk_idx.shape
     flat = topk_idx.reshape(-1).to(torch.int64)
     dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
-    order = torch.argsort(dest, stable=True)
-    counts = torch.bincount(dest, minlength=world)[:world]
-    pos = torch.empty(n * k, dtype=torch.int32, device=topk_idx.device)
-    pos[order] = torch.arange(n * k, dtype=torch.int32, device=topk_idx.device)
+    onehot = (dest.unsqueeze(1) == torch.arange(world, device=flat.device).unsqueeze(0)).to(torch.int32)
+    running = onehot.cumsum(0)                                   # [N*k, world], inclusive
+    counts = running[-1] if n * k else torch.zeros(world, dtype=torch.int32, device=flat.device)
+    starts = counts.cumsum(0) - counts
+    pos = (starts[dest] + running.gather(1, dest.unsqueeze(1)).squeeze(1) - 1).to(torch.int32)
+    order = torch.empty(n * k, dtype=torch.int64, device=flat.device)
+    order[pos.long()] = torch.arange(n * k, dtype=torch.int64, device=flat.device)
     local = (flat - dest * experts_per_rank)[order].to(torch.int32)
-    return DispatchPlan(order, counts.tolist(), pos.reshape(n, k), local)
+    return DispatchPlan(order, counts, pos.reshape(n, k), local)
 
 
-def exchange_counts(send_counts: list[int], group=None, device="cpu") -> list[int]:
+def exchange_counts(send_counts, group=None, device="cpu") -> tuple[list[int], list[int]]:
+    """One collective and one host read: every rank learns the whole send-count matrix.
+    Returns (send_counts, recv_counts) as host lists."""
     world = dist.get_world_size(group)
-    s = torch.tensor(send_counts, dtype=torch.int64, device=device)
-    r = torch.empty(world, dtype=torch.int64, device=device)
-    dist.all_to_all_single(r, s, group=group)
-    return r.tolist()
+    rank = dist.get_rank(group)
+    s = torch.as_tensor(send_counts, dtype=torch.int64, device=device).reshape(world)
+    parts = [torch.empty(world, dtype=torch.int64, device=device) for _ in range(world)]
+    dist.all_gather(parts, s.contiguous(), group=group)
+    host = torch.stack(parts).tolist()
+    return host[rank], [host[r][rank] for r in range(world)]
 
 
 def all_to_all_rows(rows: torch.Tensor, send_counts: list[int], recv_counts: list[int], group=None) -> torch.Tensor:
@@ -66,20 +74,27 @@ def ep_forward(x, topk_idx, topk_w, experts_per_rank, local_experts_fn, combine_
     world = dist.get_world_size(group)
     n, k = topk_idx.shape
     plan = plan_dispatch(topk_idx, experts_per_rank, world)
-    recv_counts = exchange_counts(plan.send_counts, group, device=x.device)
+    send_counts, recv_counts = exchange_counts(plan.send_counts, group, device=x.device)
     tok = torch.div(plan.send_order, k, rounding_mode="floor")
     x_send = x.index_select(0, tok)
+    # (local expert id, gate weight) travel together: one int32 pair per row
     w_send = topk_w.reshape(-1)[plan.send_order]
-    x_recv = all_to_all_rows(x_send, plan.send_counts, recv_counts, group)
-    e_recv = all_to_all_rows(plan.local_expert, plan.send_counts, recv_counts, group)
-    w_recv = all_to_all_rows(w_send, plan.send_counts, recv_counts, group)
+    x_recv = all_to_all_rows(x_send, send_counts, recv_counts, group)
+    if topk_w.element_size() == 2:
+        meta = torch.stack([plan.local_expert, w_send.view(torch.int16).to(torch.int32)], dim=1)
+        meta_recv = all_to_all_rows(meta, send_counts, recv_counts, group)
+        e_recv = meta_recv[:, 0].contiguous()
+        w_recv = meta_recv[:, 1].to(torch.int16).view(topk_w.dtype)
+    else:
+        e_recv = all_to_all_rows(plan.local_expert, send_counts, recv_counts, group)
+        w_recv = all_to_all_rows(w_send, send_counts, recv_counts, group)
     y_recv = local_experts_fn(x_recv, e_recv.reshape(-1, 1), w_recv.reshape(-1, 1))
     n_sh_rows = 0
     y_sh = shared_fn(x) if shared_fn is not None else None
     if y_sh is not None:
         n_sh_rows = y_sh.shape[0]
     rows = torch.empty(n * k + n_sh_rows, x.shape[1], dtype=y_recv.dtype, device=x.device)
-    dist.all_to_all_single(rows[: n * k], y_recv.contiguous(), output_split_sizes=plan.send_counts,
+    dist.all_to_all_single(rows[: n * k], y_recv.contiguous(), output_split_sizes=send_counts,
                            input_split_sizes=recv_counts, group=group)
     topk_row = plan.slot_pos
     if y_sh is not None:
