@@ -5,6 +5,7 @@
 // errors come back as status codes instead of TORCH_CHECK exceptions.
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/xmoe_b200.h"
@@ -197,13 +198,19 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
             void* out_rows, uint32_t* status, int e_tot, int H, int I, size_t rows, int nt, cudaStream_t stream) {
     Ff2Args a;
     memset(&a, 0, sizeof(a));
-    // K per stage: 128 (64-byte rows, 64-byte swizzle) up to 128-token tiles, 64 (32-byte rows) for 256
-    const bool wide = nt >= 256;
+    // 256-token tiles run on CTA pairs (2-SM MMA) unless XMOE_FF2_PAIR=0: each CTA stages 128 token
+    // rows and K 128 (64-byte weight rows). The single-CTA 256 variant uses K 64 (32-byte rows).
+    static const bool pair_enabled = [] {
+        const char* e = getenv("XMOE_FF2_PAIR");
+        return !(e && e[0] == '0');
+    }();
+    const bool pair = nt >= 256 && pair_enabled && num_sms() >= 2 && H > 128;
+    const bool k64 = nt >= 256 && !pair;
     int rc = make_tmap_2d(&a.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2_q, (uint64_t)I / 2, (uint64_t)e_tot * H,
-                          wide ? 32 : 64, 128, wide ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B);
+                          k64 ? 32 : 64, 128, k64 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc) return rc;
-    rc = make_tmap_2d(&a.tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64, (uint32_t)nt,
-                      CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = make_tmap_2d(&a.tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64,
+                      (uint32_t)(pair ? 128 : nt), CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     a.w2_scale = w2_scale;
     a.counts = counts;
@@ -216,7 +223,7 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
     a.groups = (I + 127) / 128;
     a.nt = nt;
     a.num_sms = num_sms();
-    return launch_ff2(a, stream);
+    return pair ? launch_ff2_pair(a, stream) : launch_ff2(a, stream);
 }
 
 int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* logits,

@@ -1,0 +1,439 @@
+// FF2 for long-K prefill on CTA PAIRS: the same W4A16 down projection as ff2_w4a16.cu (weight
+// contract, expansion arithmetic and tensor-memory A operand are identical; reference pointers
+// are listed there), issued as 2-SM MMAs (tcgen05 cta_group::2, M = 256, N = 256).
+//
+// Why: with 128 weight rows per tile the 256-token activation tile is re-read from L2 once per
+// 128 output features, and at ~9 TB/s of L2 delivery that capped the single-CTA kernel near
+// 1.0 PFLOP/s. A cluster of two CTAs works on 256 weight rows: each CTA stages only HALF of the
+// token tile (128 rows), expands its own 128 weight rows into its own tensor memory, and the
+// leader CTA issues one MMA per K16 that reads both halves. Token-tile traffic per SM halves.
+//
+// Cross-CTA protocol (no multicast anywhere; plain TMA loads with local barriers):
+//   * peer -> leader: "my half of the token stage landed" (relay thread, remote mbarrier arrive),
+//     "my expanded weights are in tensor memory" (each dequant warp arrives on the LEADER's
+//     barrier, count 8), "my epilogue drained the accumulator" (count 8 on the leader).
+//   * leader -> peer: tcgen05.commit on the peer's copy of the token-stage / A-buffer /
+//     accumulator barriers (commit takes a shared::cluster address, one per CTA).
+// Both CTAs run every role except MMA issue (leader only); the peer's idle MMA warp is the relay.
+// Every wait is bounded; both CTAs meet at a cluster barrier before tensor memory is released.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "tile_sched.cuh"
+
+namespace xmoe {
+
+namespace {
+
+constexpr int kBlockM = 128;             // weight rows per CTA
+constexpr int kTokHalf = 128;            // token rows staged per CTA
+constexpr int kTokTile = 256;            // token rows per pair tile = MMA N
+constexpr int kStageK = 128;             // one int4 group
+constexpr int kRawBytes = kBlockM * kStageK / 2;
+constexpr int kWStageBytes = kRawBytes + 512;
+constexpr int kBStageBytes = kTokHalf * kStageK * 2;   // 32 KiB: two 128-byte-swizzle slabs
+constexpr int kWStages = 12;
+constexpr int kBStages = 3;
+constexpr int kACols = kStageK / 2;      // 64
+constexpr int kARing = 4;
+constexpr int kDqGroups = 4;
+constexpr int kAccBase = kARing * kACols;  // 256
+constexpr int kTmemCols = 512;
+constexpr int kFirstDqWarp = 7;
+constexpr int kThreads = 32 * (kFirstDqWarp + 4 * kDqGroups);  // 736
+constexpr int kTailBytes = 5120 + 8192;
+constexpr size_t kSmemBytes = 1024 + (size_t)kBStages * kBStageBytes + (size_t)kWStages * kWStageBytes + kTailBytes;
+static_assert(kSmemBytes <= 232448, "shared memory");
+static_assert(kAccBase + kTokTile <= kTmemCols, "TMEM budget");
+
+__device__ __forceinline__ __nv_bfloat162 bf162_from_bits(uint32_t bits) {
+    __nv_bfloat162 v;
+    memcpy(&v, &bits, 4);
+    return v;
+}
+__device__ __forceinline__ uint32_t bits_from_bf162(__nv_bfloat162 v) {
+    uint32_t bits;
+    memcpy(&bits, &v, 4);
+    return bits;
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---- cluster helpers -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `local_smem_addr` in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_smem_addr), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Bounded wait with cluster-scope acquire: for barriers that receive arrivals from the peer CTA.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  uint32_t* status, uint32_t code) {
+    for (uint32_t spin = 0; spin < XMOE_SPIN_LIMIT; ++spin) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity), "r"(XMOE_WAIT_HINT_NS)
+            : "memory");
+        if (ok) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1u;
+    if (status) atomicCAS(status, XMOE_DEV_OK, code | (blockIdx.x & 0xffu));
+    return false;
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Arrive on the barrier at `cluster_addr` (any CTA of the pair) once all MMAs issued so far retire.
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+                 : "memory");
+}
+// 2-SM MMA: D (256 x N, 128 rows in each CTA's tensor memory) (+)= A (each CTA's tensor memory)
+// * B (N/2 rows in each CTA's shared memory at the same offset).
+__device__ __forceinline__ void mma_bf16_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+
+__global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __grid_constant__ Ff2Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* b_base = smem;
+    uint8_t* w_base = smem + (size_t)kBStages * kBStageBytes;
+    uint8_t* tail = w_base + (size_t)kWStages * kWStageBytes;
+    uint64_t* w_full = reinterpret_cast<uint64_t*>(tail);  // [16] local: raw weights + scales landed
+    uint64_t* w_empty = w_full + 16;                       // [16] local: dequant group done with them
+    uint64_t* b_full = w_empty + 16;                       // [8]  local: my token half landed
+    uint64_t* b_peer = b_full + 8;                         // [8]  leader: the peer's token half landed
+    uint64_t* b_empty = b_peer + 8;                        // [8]  each CTA: MMAs reading the stage retired
+    uint64_t* adq_full = b_empty + 8;                      // [8]  leader: both CTAs' expanded weights are in TMEM
+    uint64_t* adq_empty = adq_full + 8;                    // [8]  each CTA: MMAs reading the A buffer retired
+    uint64_t* acc_full = adq_empty + 8;                    // [1]  each CTA
+    uint64_t* acc_empty = acc_full + 1;                    // [1]  leader: both epilogues drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    int* prefix = reinterpret_cast<int*>(tail + 640);
+    uint16_t* transpose = reinterpret_cast<uint16_t*>(tail + 5120);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int cluster_id = blockIdx.x >> 1;
+    const int n_clusters = gridDim.x >> 1;
+    const int mt_tiles = (a.H + kBlockM - 1) / kBlockM;
+    const int h_pairs = (mt_tiles + 1) / 2;
+    const int k_stages = (a.I + kStageK - 1) / kStageK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kWStages; ++s) {
+            mbar_init(&w_full[s], 1);
+            mbar_init(&w_empty[s], 4);
+        }
+        for (int s = 0; s < kBStages; ++s) {
+            mbar_init(&b_full[s], 1);
+            mbar_init(&b_peer[s], 1);
+            mbar_init(&b_empty[s], 1);
+        }
+        for (int s = 0; s < kARing; ++s) {
+            mbar_init(&adq_full[s], 8);
+            mbar_init(&adq_empty[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, 8);
+        *abort_flag = 0u;
+        mbar_fence_init();
+        prefetch_tmap(&a.tm_w);
+        prefetch_tmap(&a.tm_y);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, kTmemCols);
+        tmem_relinquish_pair();
+    }
+    if (warp == 2) tile_prefix_build(prefix, a.counts, a.E_tot, h_pairs, kTokTile);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers are initialised before anyone arrives on them remotely
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = prefix[a.E_tot];
+
+    if (warp == 0) {
+        // ------------------------------ weight producer (my 128 rows) --------------
+        if (lane == 0) {
+            const uint16_t* scales = reinterpret_cast<const uint16_t*>(a.w2_scale);
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
+                const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
+                const int h0 = (t.wt * 2 + (int)rank) * kBlockM;
+                const int w_row = t.e * a.H + h0;
+                const int rows_here = max(0, min(kBlockM, a.H - h0));
+                const uint32_t scale_bytes = (uint32_t)rows_here * 2u;
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!mbar_wait(&w_empty[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* st = w_base + (size_t)s * kWStageBytes;
+                    mbar_expect_tx(&w_full[s], kRawBytes + scale_bytes);
+                    tma_load_2d(st, &a.tm_w, ks * (kStageK / 2), w_row, &w_full[s]);
+                    if (scale_bytes)
+                        tma_load_1d(st + kRawBytes, scales + ((size_t)t.e * a.groups + ks) * a.H + h0, scale_bytes,
+                                    &w_full[s]);
+                    if (++s == (uint32_t)kWStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 6) {
+        // ------------------------------ token producer (my 128 token rows) --------
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
+                const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
+                const int row = t.row0 + (int)rank * kTokHalf;
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!mbar_wait(&b_empty[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* b = b_base + (size_t)s * kBStageBytes;
+                    mbar_expect_tx(&b_full[s], kBStageBytes);
+                    tma_load_2d(b, &a.tm_y, ks * kStageK, row, &b_full[s]);
+                    tma_load_2d(b + kTokHalf * 128, &a.tm_y, ks * kStageK + 64, row, &b_full[s]);
+                    if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            // ------------------------------ MMA issuer (leader CTA) -----------------
+            constexpr uint32_t idesc = umma_idesc_bf16(2 * kBlockM, kTokTile);
+            constexpr int kSlab16 = (kTokHalf * 128) >> 4;
+            const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(b_base));
+            const uint32_t peer_b_empty = map_to_cta(smem_u32(&b_empty[0]), 1);
+            const uint32_t peer_adq_empty = map_to_cta(smem_u32(&adq_empty[0]), 1);
+            const uint32_t peer_acc_full = map_to_cta(smem_u32(acc_full), 1);
+            uint32_t tile_n = 0, s = 0, ph = 0, d = 0, dph = 0;
+            bool ok = true;
+            for (int item = cluster_id; item < total_tiles && ok; item += n_clusters, ++tile_n) {
+                if (!mbar_wait_cluster(acc_empty, (tile_n & 1u) ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + kAccBase;
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!mbar_wait(&b_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
+                        !mbar_wait_cluster(&b_peer[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
+                        !mbar_wait_cluster(&adq_full[d], dph, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_tmem = tmem_base + d * kACols;
+                    const uint32_t b_lo = b_lo0 + s * (uint32_t)(kBStageBytes >> 4);
+#pragma unroll
+                    for (int kk = 0; kk < kStageK / 16; ++kk)
+                        mma_bf16_ts_pair(acc, a_tmem + kk * 8, b_lo + (kk >> 2) * kSlab16 + (kk & 3) * 2, idesc,
+                                         (ks | kk) ? 1u : 0u);
+                    // release the token stage and the A buffer in both CTAs
+                    tc_commit_pair(smem_u32(&b_empty[s]));
+                    tc_commit_pair(peer_b_empty + s * 8u);
+                    tc_commit_pair(smem_u32(&adq_empty[d]));
+                    tc_commit_pair(peer_adq_empty + d * 8u);
+                    if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
+                    if (++d == (uint32_t)kARing) { d = 0; dph ^= 1u; }
+                }
+                if (ok) {
+                    tc_commit_pair(smem_u32(acc_full));
+                    tc_commit_pair(peer_acc_full);
+                }
+            }
+        } else if (lane == 0) {
+            // ------------------------------ relay (peer CTA) -------------------------
+            // tells the leader when this CTA's half of a token stage has landed
+            const uint32_t leader_b_peer = map_to_cta(smem_u32(&b_peer[0]), 0);
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!mbar_wait(&b_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_cluster(leader_b_peer + s * 8u);
+                    if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------ epilogue (my 128 features x 256 tokens) -----
+        const int q = warp & 3;
+        uint32_t tile_n = 0;
+        uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
+        uint16_t* tp = transpose + q * 1024;
+        const uint32_t leader_acc_empty = map_to_cta(smem_u32(acc_empty), 0);
+        for (int item = cluster_id; item < total_tiles; item += n_clusters, ++tile_n) {
+            const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
+            if (!mbar_wait_cluster(acc_full, tile_n & 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
+            tc_fence_after();
+            const int h_base = (t.wt * 2 + (int)rank) * kBlockM + q * 32;
+            const int n_valid = min(kTokTile, t.count - t.nt_idx * kTokTile);
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAccBase;
+            for (int c0 = 0; c0 < kTokTile; c0 += 32) {
+                if (c0 >= n_valid) break;
+                uint32_t v[32];
+                tmem_ld32(lane_addr + c0, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) tp[j * 32 + lane] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
+                __syncwarp();
+                const uint4* src = reinterpret_cast<const uint4*>(tp + lane * 32);
+                const uint4 r0 = src[0], r1 = src[1], r2 = src[2], r3 = src[3];
+                if (c0 + lane < n_valid) {
+                    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(t.row0 + c0 + lane) * a.H + h_base);
+                    if (h_base < a.H) dst[0] = r0;
+                    if (h_base + 8 < a.H) dst[1] = r1;
+                    if (h_base + 16 < a.H) dst[2] = r2;
+                    if (h_base + 24 < a.H) dst[3] = r3;
+                }
+                __syncwarp();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+        }
+    } else {
+        // ------------------------------ dequantiser (my 128 rows -> my tensor memory) --
+        const int quadrant = warp & 3;
+        const int group = (warp - kFirstDqWarp) >> 2;
+        const int row = quadrant * 32 + lane;
+        const uint32_t swz = (uint32_t)(row >> 1) & 3u;  // 64-byte TMA swizzle: 16-byte chunk ^= (row / 2) % 4
+        const __nv_bfloat162 bias = bf162_from_bits(0x43084308u);  // 136.0 twice
+        const uint32_t leader_adq_full = map_to_cta(smem_u32(&adq_full[0]), 0);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
+            for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                if ((int)(it % kDqGroups) != group) continue;
+                const int s = it % kWStages;
+                const uint32_t ph = (it / kWStages) & 1u;
+                const int d = it % kARing;
+                const uint32_t dph = (it / kARing) & 1u;
+                if (!mbar_wait(&w_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
+                    !mbar_wait_cluster(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint8_t* st = w_base + (size_t)s * kWStageBytes;
+                const uint32_t sraw = reinterpret_cast<const uint16_t*>(st + kRawBytes)[row];
+                const __nv_bfloat162 s2 = bf162_from_bits(sraw | (sraw << 16));
+                const uint32_t a_lane = tmem_base + ((uint32_t)(quadrant * 32) << 16) + d * kACols;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t o[32];
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const uint32_t chunk = (uint32_t)(half * 2 + c) ^ swz;
+                        const uint4 r4 = *reinterpret_cast<const uint4*>(st + row * 64 + chunk * 16);
+                        const uint32_t words[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+                        for (int w = 0; w < 4; ++w) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t bits = ((words[w] >> (4 * j)) & 0x000f000fu) | 0x43004300u;
+                                o[(c * 4 + w) * 4 + j] =
+                                    bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(bits), bias), s2));
+                            }
+                        }
+                    }
+                    tmem_st32(a_lane + half * 32, o);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_cluster(leader_adq_full + d * 8u);  // the leader issues the MMAs of both CTAs
+                    mbar_arrive(&w_empty[s]);
+                }
+            }
+        }
+    }
+
+    // both CTAs finish every remote access before either releases tensor memory or exits
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
+}
+
+}  // namespace
+
+int launch_ff2_pair(const Ff2Args& a, cudaStream_t stream) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(ff2_w4a16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kSmemBytes) != cudaSuccess)
+            return XMOE_ERR_CUDA;
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(a.num_sms & ~1), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, ff2_w4a16_pair_kernel, a) == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+}  // namespace xmoe

@@ -119,6 +119,7 @@ int launch_act_quant(const QuantArgs& a, cudaStream_t stream);
 int launch_ff1(const Ff1Args& a, cudaStream_t stream);
 int launch_ff1_prefill(const Ff1Args& a, cudaStream_t stream);
 int launch_ff2(const Ff2Args& a, cudaStream_t stream);
+int launch_ff2_pair(const Ff2Args& a, cudaStream_t stream);  // 256-token tiles on CTA pairs (2-SM MMA)
 int launch_combine(const CombineArgs& a, cudaStream_t stream);
 int launch_act_topk(const ActTopkArgs& a, cudaStream_t stream);
 int launch_prep_nvfp4_sf(const void* sf_in, void* sf_out, int n_mats, int rows, int kblocks16, int mb, int kb_pad,
