@@ -135,6 +135,21 @@ def test_deterministic_run_to_run():
     assert torch.equal(y1, y2)
 
 
+def test_ff1_cta_pair_variant(monkeypatch):
+    # opt-in 2-SM (cta_group::2) FF1: must give the same rows as the default kernel, bit for bit
+    shape = synth.scaled_shape(synth.SHAPES["mixtral"], hidden=512, inter=384, num_experts=4)
+    _, layer, x, logits, y, ref, view = run_case(shape, 900)
+    check_stages(shape, 900, y, ref, view)
+    yact_default = view["yact"].clone()
+    monkeypatch.setenv("XMOE_FF1_PAIR", "1")
+    y2 = layer.forward(x.cuda(), logits.cuda())
+    torch.cuda.synchronize()
+    assert layer.status(900) == 0
+    m = torch.from_numpy(Hh.valid_row_mask(ref["pack"])).cuda()
+    assert torch.equal(layer.view(900)["yact"][: len(m)][m], yact_default[: len(m)][m])
+    assert torch.equal(y, y2)
+
+
 def test_long_k_prefill_uses_wide_ff2_tile():
     # inter >= 2048 with prefill-sized experts: FF1 token-major kernel + FF2 with 256-token tiles,
     # ragged last tiles (counts not multiples of 128 or 256)

@@ -1,0 +1,285 @@
+// FF1 for prefill on CTA PAIRS: the token-major NVFP4 gate/up GEMM of ff1_nvfp4_prefill.cu
+// (same math, same epilogue, reference pointers there) issued as 2-SM MMAs
+// (tcgen05 cta_group::2, M = 256 tokens, N = 256 = 128 gate | 128 up rows, K = 64).
+//
+// Why: a single CTA stages 54 KB per 16.8 MFLOP and the kernel ran at what the L2 -> SM path
+// delivers (~9 TB/s => ~2.9 PFLOP/s). In a pair each CTA stages its own 128 token rows and only
+// HALF of the weight tile: the leader the 128 gate rows, the peer the 128 up rows. The MMA reads
+// both halves, every CTA gets gate and up columns for its own 128 tokens, and weight traffic
+// per SM halves (38 KB per 16.8 MFLOP).
+//
+// Scale factors: each CTA needs the token scales of its own rows and the weight scales of ALL 256
+// N rows in its tensor memory, so both CTAs load both (2 KB each per stage) and the leader issues
+// one cta_group::2 tcgen05.cp per tile that copies from each CTA's shared memory into that CTA's
+// tensor memory. Cross-CTA protocol as in ff2_w4a16_pair.cu: a relay thread in the peer reports
+// landed stages to the leader; the leader's commits release the stage / accumulator barriers of
+// both CTAs; both epilogues report to the leader. No multicast; every wait is bounded.
+#include "cluster.cuh"
+#include "common.cuh"
+#include "kernels.h"
+#include "tile_sched.cuh"
+
+namespace xmoe {
+
+namespace {
+
+constexpr int kTokHalf = 128;          // token rows per CTA
+constexpr int kTokTile = 256;          // token rows per pair tile
+constexpr int kWTile = 128;            // I rows per tile (per projection)
+constexpr int kStageKBytes = 128;      // 256 K elements per stage
+constexpr int kKPerStage = 256;
+constexpr int kSfBytes = 2048;
+constexpr int kABytes = kTokHalf * kStageKBytes;   // 16 KiB: my tokens
+constexpr int kBBytes = kWTile * kStageKBytes;     // 16 KiB: my half of the weight tile
+constexpr int kStageBytes = kABytes + kBBytes + 3 * kSfBytes;  // 38 KiB
+constexpr int kStages = 5;
+constexpr int kThreads = 320;          // producer, MMA / relay, 8 epilogue warps
+constexpr int kTmemCols = 512;
+constexpr int kAccCols = 256;
+constexpr int kSfSlotCols = 48;
+constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + 8192;
+
+template <int ACT>
+__global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_pair_kernel(const __grid_constant__ Ff1Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* tail = smem + (size_t)kStages * kStageBytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // [8] local: my stage landed
+    uint64_t* peer_full = full_bar + 8;                      // [8] leader: the peer's stage landed
+    uint64_t* empty_bar = peer_full + 8;                     // [8] each CTA: MMAs reading the stage retired
+    uint64_t* acc_full = empty_bar + 8;                      // [1] each CTA
+    uint64_t* acc_empty = acc_full + 1;                      // [1] leader: 16 epilogue warps drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    int* prefix = reinterpret_cast<int*>(tail + 256);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int cluster_id = blockIdx.x >> 1;
+    const int n_clusters = gridDim.x >> 1;
+    const int w_tiles = a.mb;
+    const int k_stages = (a.H + kKPerStage - 1) / kKPerStage;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&peer_full[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, 16);
+        *abort_flag = 0u;
+        mbar_fence_init();
+        prefetch_tmap(&a.tm_w);
+        prefetch_tmap(&a.tm_x);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, kTmemCols);
+        tmem_relinquish_pair();
+    }
+    if (warp == 2) tile_prefix_build(prefix, a.counts, a.E_tot, w_tiles, kTokTile);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = prefix[a.E_tot];
+
+    if (warp == 0) {
+        // ---- producer: my 128 tokens, my half of the weight tile, all scale factors ----
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
+                const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
+                const int tok_row = t.row0 + (int)rank * kTokHalf;
+                const int w_row = t.e * 2 * a.I + (int)rank * a.I + t.wt * kWTile;  // leader: gate rows, peer: up rows
+                const uint8_t* sfw_g = a.sfw + ((size_t)(t.e * 2 + 0) * a.mb + t.wt) * a.kb_pad * 512;
+                const uint8_t* sfw_u = a.sfw + ((size_t)(t.e * 2 + 1) * a.mb + t.wt) * a.kb_pad * 512;
+                const uint8_t* sfx = a.sfx + (size_t)(tok_row / kTokHalf) * a.kb_pad * 512;
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!mbar_wait_cluster(&empty_bar[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* st = smem + (size_t)s * kStageBytes;
+                    mbar_expect_tx(&full_bar[s], kStageBytes);
+                    tma_load_2d(st, &a.tm_x, ks * kStageKBytes, tok_row, &full_bar[s]);
+                    tma_load_2d(st + kABytes, &a.tm_w, ks * kStageKBytes, w_row, &full_bar[s]);
+                    uint8_t* sf = st + kABytes + kBBytes;
+                    tma_load_1d(sf, sfx + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                    tma_load_1d(sf + kSfBytes, sfw_g + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                    tma_load_1d(sf + 2 * kSfBytes, sfw_u + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                    if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            // ---- MMA issuer (leader) ----
+            constexpr uint32_t idesc = umma_idesc_nvfp4(2 * kTokHalf, 2 * kWTile);
+            constexpr uint32_t kStage16 = kStageBytes >> 4;
+            const uint32_t a_lo0 = umma_desc_lo_sw128(smem_u32(smem));
+            const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(smem + kABytes));
+            const uint32_t sf_lo0 = umma_desc_lo_sf(smem_u32(smem + kABytes + kBBytes));
+            const uint32_t peer_empty = map_to_cta(smem_u32(&empty_bar[0]), 1);
+            const uint32_t peer_acc_full = map_to_cta(smem_u32(acc_full), 1);
+            uint32_t tile_n = 0, s = 0, ph = 0, slot = 0;
+            bool ok = true;
+            for (int item = cluster_id; item < total_tiles && ok; item += n_clusters, ++tile_n) {
+                if (!mbar_wait_cluster(acc_empty, (tile_n & 1u) ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
+                tc_fence_after();
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
+                        !mbar_wait_cluster(&peer_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sf_lo = sf_lo0 + s * kStage16;
+                    const uint32_t sf_tmem = tmem_base + kAccCols + slot * kSfSlotCols;
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) {
+                        tmem_cp_sf_pair(sf_tmem + kb * 4, sf_lo + kb * 32);                                // my tokens
+                        tmem_cp_sf_pair(sf_tmem + 16 + kb * 8, sf_lo + (kSfBytes >> 4) + kb * 32);         // gate rows
+                        tmem_cp_sf_pair(sf_tmem + 16 + kb * 8 + 4, sf_lo + 2 * (kSfBytes >> 4) + kb * 32); // up rows
+                    }
+                    const uint32_t a_lo = a_lo0 + s * kStage16;
+                    const uint32_t b_lo = b_lo0 + s * kStage16;
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb)
+                        mma_nvfp4_pair(tmem_base, a_lo + kb * 2, b_lo + kb * 2, idesc, sf_tmem + kb * 4,
+                                       sf_tmem + 16 + kb * 8, (ks | kb) ? 1u : 0u);
+                    tc_commit_pair(smem_u32(&empty_bar[s]));
+                    tc_commit_pair(peer_empty + s * 8u);
+                    if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+                    slot ^= 1u;
+                }
+                if (ok) {
+                    tc_commit_pair(smem_u32(acc_full));
+                    tc_commit_pair(peer_acc_full);
+                }
+            }
+        } else if (lane == 0) {
+            // ---- relay (peer): report landed stages to the leader ----
+            const uint32_t leader_peer_full = map_to_cta(smem_u32(&peer_full[0]), 0);
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_cluster(leader_peer_full + s * 8u);
+                    if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else {
+        // ---- epilogue: my 128 tokens x (128 gate | 128 up) columns, 8 warps ----
+        const int q = warp & 3;
+        const int col_half = (warp - 2) >> 2;
+        const float xgs_inv = a.scale->xgs_inv;
+        uint16_t* yact = reinterpret_cast<uint16_t*>(a.yact);
+        const uint16_t* row_w = reinterpret_cast<const uint16_t*>(a.row_weight);
+        const uint32_t leader_acc_empty = map_to_cta(smem_u32(acc_empty), 0);
+        uint32_t tile_n = 0;
+        for (int item = cluster_id; item < total_tiles; item += n_clusters, ++tile_n) {
+            const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
+            const int n_local = (int)rank * kTokHalf + q * 32 + lane;
+            const bool row_ok = t.nt_idx * kTokTile + n_local < t.count;
+            const int r = t.row0 + n_local;
+            const float w = row_ok ? bf16_bits_to_f32(row_w[r]) : 0.f;
+            const float sg = __fmul_rn(a.w13_gs[t.e * 2 + 0], xgs_inv);
+            const float su = __fmul_rn(__fmul_rn(a.w13_gs[t.e * 2 + 1], xgs_inv), w);
+            const int i0 = t.wt * kWTile + col_half * 64;
+            if (!mbar_wait_cluster(acc_full, tile_n & 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
+            tc_fence_after();
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + col_half * 64;
+#pragma unroll 1
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+                if (i0 + c0 >= a.I) break;
+                uint32_t g[32], u[32];
+                tmem_ld32(lane_addr + c0, g);
+                tmem_ld32(lane_addr + kWTile + c0, u);
+                tmem_ld_wait();
+                if (row_ok) {
+                    uint32_t o[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float y0 = glu_apply(ACT, __uint_as_float(g[2 * j]), __uint_as_float(u[2 * j]), sg, su,
+                                                   a.alpha, a.limit, w);
+                        const float y1 = glu_apply(ACT, __uint_as_float(g[2 * j + 1]), __uint_as_float(u[2 * j + 1]), sg,
+                                                   su, a.alpha, a.limit, w);
+                        o[j] = pack_bf16x2(y0, y1);
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(yact + (size_t)r * a.I + i0 + c0);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v)
+                        if (i0 + c0 + v * 8 < a.I) dst[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+        }
+    }
+
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
+}
+
+template <int ACT>
+int launch_pair_act(const Ff1Args& a, cudaStream_t stream) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(ff1_nvfp4_pair_kernel<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kSmemBytes) != cudaSuccess)
+            return XMOE_ERR_CUDA;
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(a.num_sms & ~1), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // Persistent kernel: launch exactly as many clusters as can be resident at once. Pairs must sit
+    // inside one GPC, so this can be fewer than num_sms / 2; extra clusters would run as a second
+    // wave and double the kernel time.
+    static int resident_clusters = 0;
+    if (!resident_clusters) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, ff1_nvfp4_pair_kernel<ACT>, &cfg) != cudaSuccess || n <= 0) n = a.num_sms / 2;
+        resident_clusters = n < a.num_sms / 2 ? n : a.num_sms / 2;
+    }
+    cfg.gridDim = dim3((unsigned)(2 * resident_clusters), 1, 1);
+    return cudaLaunchKernelEx(&cfg, ff1_nvfp4_pair_kernel<ACT>, a) == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+}  // namespace
+
+int launch_ff1_pair(const Ff1Args& a, cudaStream_t stream) {
+    switch (a.activation) {
+        case 0: return launch_pair_act<0>(a, stream);
+        case 1: return launch_pair_act<1>(a, stream);
+        case 2: return launch_pair_act<2>(a, stream);
+        default: return XMOE_ERR_SHAPE;
+    }
+}
+
+}  // namespace xmoe

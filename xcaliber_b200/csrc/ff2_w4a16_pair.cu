@@ -18,6 +18,7 @@
 // Every wait is bounded; both CTAs meet at a cluster barrier before tensor memory is released.
 #include <cuda_bf16.h>
 
+#include "cluster.cuh"
 #include "common.cuh"
 #include "kernels.h"
 #include "tile_sched.cuh"
@@ -70,59 +71,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// ---- cluster helpers -------------------------------------------------------------------
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// shared::cluster address of `local_smem_addr` in CTA `rank` of this cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank) {
-    uint32_t a;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_smem_addr), "r"(rank));
-    return a;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Bounded wait with cluster-scope acquire: for barriers that receive arrivals from the peer CTA.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                                  uint32_t* status, uint32_t code) {
-    for (uint32_t spin = 0; spin < XMOE_SPIN_LIMIT; ++spin) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(smem_u32(bar)), "r"(parity), "r"(XMOE_WAIT_HINT_NS)
-            : "memory");
-        if (ok) return true;
-        if (*abort_flag) return false;
-    }
-    *abort_flag = 1u;
-    if (status) atomicCAS(status, XMOE_DEV_OK, code | (blockIdx.x & 0xffu));
-    return false;
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
-                 "r"(ncols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-// Arrive on the barrier at `cluster_addr` (any CTA of the pair) once all MMAs issued so far retire.
-__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
-                 : "memory");
-}
 // 2-SM MMA: D (256 x N, 128 rows in each CTA's tensor memory) (+)= A (each CTA's tensor memory)
 // * B (N/2 rows in each CTA's shared memory at the same offset).
 __device__ __forceinline__ void mma_bf16_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
@@ -433,6 +381,16 @@ int launch_ff2_pair(const Ff2Args& a, cudaStream_t stream) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    // Persistent kernel: launch exactly as many clusters as can be resident at once. Pairs must sit
+    // inside one GPC, so this can be fewer than num_sms / 2; extra clusters would run as a second
+    // wave and double the kernel time.
+    static int resident_clusters = 0;
+    if (!resident_clusters) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, ff2_w4a16_pair_kernel, &cfg) != cudaSuccess || n <= 0) n = a.num_sms / 2;
+        resident_clusters = n < a.num_sms / 2 ? n : a.num_sms / 2;
+    }
+    cfg.gridDim = dim3((unsigned)(2 * resident_clusters), 1, 1);
     return cudaLaunchKernelEx(&cfg, ff2_w4a16_pair_kernel, a) == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 

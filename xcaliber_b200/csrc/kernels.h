@@ -118,6 +118,7 @@ int launch_act_scale_from_amax(const float* amax, float* scale, cudaStream_t str
 int launch_act_quant(const QuantArgs& a, cudaStream_t stream);
 int launch_ff1(const Ff1Args& a, cudaStream_t stream);
 int launch_ff1_prefill(const Ff1Args& a, cudaStream_t stream);
+int launch_ff1_pair(const Ff1Args& a, cudaStream_t stream);  // 256-token tiles on CTA pairs (2-SM MMA)
 int launch_ff2(const Ff2Args& a, cudaStream_t stream);
 int launch_ff2_pair(const Ff2Args& a, cudaStream_t stream);  // 256-token tiles on CTA pairs (2-SM MMA)
 int launch_combine(const CombineArgs& a, cudaStream_t stream);
