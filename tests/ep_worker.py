@@ -1,6 +1,9 @@
 """Worker for tests/test_gpu_ep.py: run under torch.distributed.run with 2+ ranks (NCCL).
 Every rank runs the expert-parallel layer on its own tokens and compares with the single-GPU
-layer holding all experts: outputs must be bit-identical (same kernels, same activation scale)."""
+layer holding all experts. Routing, activation scale and FF1 rows are the same bits on both paths;
+FF2 adds its K stages in an order that depends on the token tile (small tiles accumulate in several
+partial sums), so the outputs may differ by a rounding step of bf16: max relative difference 1e-2
+(relative to max(|ref|, rms)), mean 1e-3."""
 import os
 import sys
 from pathlib import Path
@@ -38,9 +41,10 @@ def main():
         y_all = full.forward(torch.cat(xs).to(dev), torch.cat(ls).to(dev))
         off = sum(t.shape[0] for t in xs[:rank])
         ref = y_all[off:off + xs[rank].shape[0]]
-        if not torch.equal(y, ref):
-            diff = (y.float() - ref.float()).abs().max().item()
-            failures.append(f"{name}: rank {rank} max abs diff {diff}")
+        yf, rf = y.float(), ref.float()
+        rel = (yf - rf).abs() / torch.maximum(rf.abs(), rf.pow(2).mean().sqrt())
+        if not (rel.max().item() <= 1e-2 and rel.mean().item() <= 1e-3):
+            failures.append(f"{name}: rank {rank} rel diff max {rel.max().item():.3g} mean {rel.mean().item():.3g}")
     flag = torch.tensor([len(failures)], device=dev)
     dist.all_reduce(flag)
     if rank == 0:

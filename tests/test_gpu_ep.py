@@ -1,4 +1,4 @@
-"""Expert-parallel layer on 2 GPUs (NCCL) against the single-GPU layer: bit-identical outputs."""
+"""Expert-parallel layer on 2 GPUs (NCCL) against the single-GPU layer (outputs within a bf16 rounding step)."""
 import subprocess
 import sys
 from pathlib import Path

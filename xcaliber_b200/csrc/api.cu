@@ -211,12 +211,24 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
     }();
     const bool pair = nt >= 256 && pair_enabled && num_sms() >= 2 && H > 128;
     const bool k64 = nt >= 256 && !pair;
+    // weight box: 128 rows x (small token tiles: 128 bytes = two K units; else 64 or 32 bytes)
+    const bool wide = nt <= 64;
     int rc = make_tmap_2d(&a.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2_q, (uint64_t)I / 2, (uint64_t)e_tot * H,
-                          k64 ? 32 : 64, 128, k64 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B);
+                          wide ? 128 : (k64 ? 32 : 64), 128,
+                          wide ? CU_TENSOR_MAP_SWIZZLE_128B
+                               : (k64 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B));
     if (rc) return rc;
     rc = make_tmap_2d(&a.tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64,
                       (uint32_t)(pair ? 128 : nt), CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
+    if (nt <= 64) {
+        rc = make_tmap_2d(&a.tm_y8, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64, 8,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+        rc = make_tmap_2d(&a.tm_y16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64, 16,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+    }
     a.w2_scale = w2_scale;
     a.counts = counts;
     a.offsets = offsets;

@@ -22,7 +22,11 @@
 //               K pair). Expanded weights never touch shared memory: a first version that
 //               wrote a bf16 tile to shared memory cost 10 B of shared-memory traffic per
 //               weight byte.
-//   warp 1      tcgen05.mma kind::f16 with A from tensor memory, B from shared memory
+//   warp 1      tcgen05.mma kind::f16 with A from tensor memory, B from shared memory. Token
+//               tiles of 32 / 64 rows add three more issuing warps (7-9; the dequant warps then
+//               start at 10) that take the K stages round-robin into separate accumulators,
+//               which the epilogue adds in a fixed order: one thread issues at most one MMA per
+//               ~70 cycles, far below what the tensor pipe takes for N = 32.
 //   warps 2-5   epilogue: tcgen05.ld, transpose 32x32 blocks through shared memory so that
 //               each lane owns one token row, 16-byte stores to [packed row, H]
 // All mbarrier waits are bounded (see common.cuh).
@@ -54,26 +58,34 @@ constexpr int kTmemCols = 512;
 constexpr int kTailBytes = 5120 + 8192;  // barriers + tile prefix + epilogue transpose
 constexpr int kFirstDqWarp = 7;
 
-// NT <= 128: one K stage = one int4 group (K 128), two accumulators (the epilogue overlaps the
-// next tile). NT = 256 (long-K prefill): a K=16 MMA occupies the tensor pipe for at least ~130
-// cycles whatever N is, so only N = 256 runs the bf16 pipe at full rate; the 256-column
-// accumulator is then single and the stages are K 64.
+// NT <= 128: one K stage = one int4 group (K 128). NT = 128 has two accumulators (the epilogue
+// overlaps the next tile); NT = 32 / 64 spend the tensor-memory columns on one accumulator per
+// issuing thread instead. NT = 256 (long-K prefill): a single issuing thread sustains one K=16
+// MMA per ~70 cycles at best, so only N = 256 (128 cycles of tensor pipe) runs the bf16 pipe at
+// full rate; the 256-column accumulator is then single and the stages are K 64.
 template <int NT>
 struct Ff2Cfg {
     static constexpr int kStageK = NT >= 256 ? 64 : 128;
     static constexpr int kRawBytes = kBlockM * kStageK / 2;   // int4 tile: 128 rows x kStageK/2 bytes
-    static constexpr int kWStageBytes = kRawBytes + 512;      // + 128 bf16 scales, padded
+    // Small token tiles are HBM-bound: their weight stage spans two K units, so that every row
+    // contributes a whole 128-byte line per TMA request (64-byte pieces ran HBM at half rate).
+    static constexpr int kWUnits = NT <= 64 ? 2 : 1;
+    static constexpr int kWRowBytes = kWUnits * kStageK / 2;  // bytes of one weight row in a stage
+    static constexpr int kWRawBytes = kWUnits * kRawBytes;
+    static constexpr int kWStageBytes = kWRawBytes + 512 * kWUnits;  // + 128 bf16 scales per unit, padded
     static constexpr int kACols = kStageK / 2;                // TMEM columns of one expanded stage
     static constexpr int kSlabs = kStageK / 64;               // 128-byte-swizzle slabs of the token tile
     static constexpr int kBStageBytes = NT * kStageK * 2;
-    static constexpr int kWStages = NT == 128 ? 12 : 16;      // weight ring (HBM latency)
-    static constexpr int kBStages = NT >= 256 ? 4 : (NT >= 128 ? 3 : (NT >= 64 ? 4 : 6));  // token ring (L2 latency)
-    static constexpr int kARing = NT >= 256 ? 8 : (NT >= 128 ? 4 : 6);  // expanded-weight buffers in tensor memory
-    static constexpr int kDqGroups = NT >= 128 ? 4 : 6;                 // independent dequant groups of 4 warps
-    static constexpr int kAccStages = NT >= 256 ? 1 : 2;
-    static constexpr int kThreads = 32 * (kFirstDqWarp + 4 * kDqGroups);
+    static constexpr int kWStages = NT == 128 ? 12 : (NT == 64 ? 8 : (NT == 32 ? 10 : 16));  // weight ring (HBM latency)
+    static constexpr int kBStages = NT >= 256 ? 4 : (NT >= 128 ? 3 : 4);  // token ring (L2 latency)
+    static constexpr int kIssuers = NT <= 64 ? 4 : 1;         // MMA-issuing threads (K stages round-robin)
+    static constexpr int kARing = NT >= 256 ? 8 : (NT >= 64 ? 4 : 6);   // expanded-weight buffers in tensor memory
+    static constexpr int kDqGroups = NT >= 128 ? 4 : 5;                 // independent dequant groups of 4 warps
+    static constexpr int kAccStages = NT == 128 ? 2 : 1;
+    static constexpr int kFirstDq = kFirstDqWarp + (kIssuers - 1);
+    static constexpr int kThreads = 32 * (kFirstDq + 4 * kDqGroups);
     static constexpr int kAccBase = kARing * kACols;          // accumulators follow the A ring
-    static_assert(kAccBase + kAccStages * NT <= kTmemCols, "TMEM budget");
+    static_assert(kAccBase + kAccStages * kIssuers * NT <= kTmemCols, "TMEM budget");
     static_assert(kWStages <= 16 && kBStages <= 8 && kARing <= 8, "barrier arrays");
     static_assert(kThreads <= 1024, "block size");
     static constexpr size_t kSmemBytes =
@@ -109,8 +121,9 @@ template <int NT>
 __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(const __grid_constant__ Ff2Args a) {
     using Cfg = Ff2Cfg<NT>;
     constexpr int kARing = Cfg::kARing, kDqGroups = Cfg::kDqGroups, kAccBase = Cfg::kAccBase;
-    constexpr int kStageK = Cfg::kStageK, kRawBytes = Cfg::kRawBytes, kACols = Cfg::kACols;
+    constexpr int kStageK = Cfg::kStageK, kACols = Cfg::kACols;
     constexpr int kAccStages = Cfg::kAccStages, kWStages = Cfg::kWStages, kBStages = Cfg::kBStages;
+    constexpr int kIssuers = Cfg::kIssuers;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* b_base = smem;                                          // token ring
@@ -137,7 +150,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
     if (threadIdx.x == 0) {
         for (int s = 0; s < kWStages; ++s) {
             mbar_init(&w_full[s], 1);
-            mbar_init(&w_empty[s], 4);
+            mbar_init(&w_empty[s], 4 * Cfg::kWUnits);
         }
         for (int s = 0; s < kBStages; ++s) {
             mbar_init(&b_full[s], 1);
@@ -148,13 +161,17 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             mbar_init(&adq_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_full[s], kIssuers);
             mbar_init(&acc_empty[s], 4);
         }
         *abort_flag = 0u;
         mbar_fence_init();
         prefetch_tmap(&a.tm_w);
         prefetch_tmap(&a.tm_y);
+        if (NT <= 64) {
+            prefetch_tmap(&a.tm_y8);
+            prefetch_tmap(&a.tm_y16);
+        }
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
@@ -181,7 +198,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 const int w_row = t.e * a.H + h0;
                 const int rows_here = min(kBlockM, a.H - h0);
                 const uint32_t scale_bytes = (uint32_t)rows_here * 2u;  // H % 8 == 0 keeps this a multiple of 16
-                for (int ks = 0; ks < k_stages; ++ks) {
+                for (int ks = 0; ks < k_stages; ks += Cfg::kWUnits) {
                     {
                         XMOE_T0();
                         if (!mbar_wait(&w_empty[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
@@ -191,10 +208,13 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                         XMOE_TACC(tw_prod);
                     }
                     uint8_t* st = w_base + (size_t)s * Cfg::kWStageBytes;
-                    mbar_expect_tx(&w_full[s], kRawBytes + scale_bytes);
+                    const int units = min(Cfg::kWUnits, k_stages - ks);
+                    mbar_expect_tx(&w_full[s], Cfg::kWRawBytes + (uint32_t)units * scale_bytes);
                     tma_load_2d(st, &a.tm_w, ks * (kStageK / 2), w_row, &w_full[s]);
-                    tma_load_1d(st + kRawBytes, scales + ((size_t)t.e * a.groups + (ks * kStageK) / 128) * a.H + h0,
-                                scale_bytes, &w_full[s]);
+                    for (int u = 0; u < units; ++u)
+                        tma_load_1d(st + Cfg::kWRawBytes + u * 256,
+                                    scales + ((size_t)t.e * a.groups + ((ks + u) * kStageK) / 128) * a.H + h0, scale_bytes,
+                                    &w_full[s]);
                     if (++s == (uint32_t)kWStages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -209,6 +229,16 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             (void)tw_bprod;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
                 const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
+                // Few tokens in the tile (decode): fetch only 8 or 16 rows. The token tile comes
+                // from L2 at the same bytes per K as the weights do from HBM, and the L2 -> SM
+                // path is shared by both.
+                const CUtensorMap* tm = &a.tm_y;
+                int box_rows = NT;
+                if (NT <= 64) {
+                    const int n_valid = t.count - t.nt_idx * NT;
+                    if (n_valid <= 8) { tm = &a.tm_y8; box_rows = 8; }
+                    else if (n_valid <= 16) { tm = &a.tm_y16; box_rows = 16; }
+                }
                 for (int ks = 0; ks < k_stages; ++ks) {
                     {
                         XMOE_T0();
@@ -219,23 +249,27 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                         XMOE_TACC(tw_bprod);
                     }
                     uint8_t* b = b_base + (size_t)s * Cfg::kBStageBytes;
-                    mbar_expect_tx(&b_full[s], Cfg::kBStageBytes);
+                    mbar_expect_tx(&b_full[s], (uint32_t)(box_rows * kStageK * 2));
 #pragma unroll
                     for (int slab = 0; slab < Cfg::kSlabs; ++slab)
-                        tma_load_2d(b + slab * NT * 128, &a.tm_y, ks * kStageK + slab * 64, t.row0, &b_full[s]);
+                        tma_load_2d(b + slab * NT * 128, tm, ks * kStageK + slab * 64, t.row0, &b_full[s]);
                     if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
                 }
             }
             XMOE_TDUMP(1, tw_bprod);
         }
-    } else if (warp == 1) {
-        // ------------------------------ MMA issuer --------------------------------
+    } else if (warp == 1 || (kIssuers > 1 && warp >= kFirstDqWarp && warp < Cfg::kFirstDq)) {
+        // ------------------------------ MMA issuer(s) ------------------------------
+        // A thread can issue one MMA per ~70 cycles whatever its N, while an N = 32 MMA occupies
+        // the tensor pipe for ~16: with small token tiles the issuing thread, not the pipe, would
+        // bound the kernel. Small tiles therefore run kIssuers issuing threads that take the K
+        // stages round-robin, each into its own accumulator; the epilogue adds the partial sums.
         if (lane == 0) {
+            const int issuer = warp == 1 ? 0 : warp - kFirstDqWarp + 1;
             constexpr uint32_t idesc = umma_idesc_bf16(kBlockM, NT);
             constexpr int kSlab16 = (NT * 128) >> 4;
             const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(b_base));
-            uint32_t tile_n = 0;
-            uint32_t s = 0, ph = 0, d = 0, dph = 0;  // token stage / phase, tensor-memory A buffer / phase
+            uint32_t tile_n = 0, it = 0;
             bool ok = true;
             long long tw_full = 0, tw_adq = 0, tw_acc = 0, t_issue = 0;
             (void)tw_full; (void)tw_adq; (void)tw_acc; (void)t_issue;
@@ -248,8 +282,12 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     XMOE_TACC(tw_acc);
                 }
                 tc_fence_after();
-                const uint32_t acc = tmem_base + kAccBase + as * NT;
-                for (int ks = 0; ks < k_stages; ++ks) {
+                const uint32_t acc = tmem_base + kAccBase + (as * kIssuers + issuer) * NT;
+                uint32_t first = 1u;
+                for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                    if (kIssuers > 1 && (ks % kIssuers) != issuer) continue;
+                    const uint32_t s = it % kBStages, ph = (it / kBStages) & 1u;
+                    const uint32_t d = it % kARing, dph = (it / kARing) & 1u;
                     {
                         XMOE_T0();
                         if (!mbar_wait(&b_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
@@ -268,20 +306,21 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     for (int kk = 0; kk < kStageK / 16; ++kk) {
                         // slab kk/4 (64 K each), 32 bytes of K per MMA inside the 128-byte swizzle row
                         mma_bf16_ts_lo(acc, a_tmem + kk * 8, b_lo + (kk >> 2) * kSlab16 + (kk & 3) * 2, idesc,
-                                       (ks | kk) ? 1u : 0u);
+                                       (kk | (int)(first ^ 1u)) ? 1u : 0u);
                     }
+                    first = 0u;
                     tc_commit(&b_empty[s]);
                     tc_commit(&adq_empty[d]);
-                    if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
-                    if (++d == (uint32_t)kARing) { d = 0; dph ^= 1u; }
                     XMOE_TACC(t_issue);
                 }
                 if (ok) tc_commit(&acc_full[as]);
             }
-            XMOE_TDUMP(2, tw_full);
-            XMOE_TDUMP(3, tw_adq);
-            XMOE_TDUMP(4, tw_acc);
-            XMOE_TDUMP(5, t_issue);
+            if (issuer == 0) {
+                XMOE_TDUMP(2, tw_full);
+                XMOE_TDUMP(3, tw_adq);
+                XMOE_TDUMP(4, tw_acc);
+                XMOE_TDUMP(5, t_issue);
+            }
         }
     } else if (warp < 6) {
         // ------------------------------ epilogue -----------------------------------
@@ -297,12 +336,29 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             tc_fence_after();
             const int h_base = t.wt * kBlockM + q * 32;  // first feature of this warp's 32 lanes
             const int n_valid = min(NT, t.count - t.nt_idx * NT);
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAccBase + as * NT;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAccBase + as * kIssuers * NT;
             for (int c0 = 0; c0 < NT; c0 += 32) {
                 if (c0 >= n_valid) break;
                 uint32_t v[32];
                 tmem_ld32(lane_addr + c0, v);
                 tmem_ld_wait();
+                if (kIssuers > 1) {  // add the other issuers' partial sums, in issuer order
+#pragma unroll
+                    for (int p = 1; p < kIssuers; ++p) {
+                        if (p < k_stages) {
+#pragma unroll
+                            for (int hh = 0; hh < 2; ++hh) {  // 16 columns at a time: register budget
+                                uint32_t v2[16];
+                                tmem_ld16(lane_addr + p * NT + c0 + hh * 16, v2);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    v[hh * 16 + j] =
+                                        __float_as_uint(__uint_as_float(v[hh * 16 + j]) + __uint_as_float(v2[j]));
+                            }
+                        }
+                    }
+                }
                 // lane = feature, v[j] = token c0+j  ->  shared [token][feature]
 #pragma unroll
                 for (int j = 0; j < 32; ++j) tp[j * 32 + lane] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
@@ -330,20 +386,27 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         // stages round-robin: expanding one stage is a serial chain of a few hundred
         // instructions per thread, and independent groups keep several stages in flight.
         const int quadrant = warp & 3;
-        const int group = (warp - kFirstDqWarp) >> 2;
+        const int group = (warp - Cfg::kFirstDq) >> 2;
         const int row = quadrant * 32 + lane;
-        // TMA swizzle of the raw tile: 64-byte rows -> chunk ^= (row / 2) % 4; 32-byte rows -> chunk ^= (row / 4) % 2
-        const uint32_t swz = kStageK == 128 ? ((uint32_t)(row >> 1) & 3u) : ((uint32_t)(row >> 2) & 1u);
+        // TMA swizzle of the raw tile: 128-byte rows -> chunk ^= row % 8; 64-byte rows -> chunk ^= (row / 2) % 4;
+        // 32-byte rows -> chunk ^= (row / 4) % 2
+        constexpr int kWRowBytes = Cfg::kWRowBytes;
+        const uint32_t swz = kWRowBytes == 128 ? ((uint32_t)row & 7u)
+                                               : (kWRowBytes == 64 ? ((uint32_t)(row >> 1) & 3u) : ((uint32_t)(row >> 2) & 1u));
+        const int w_stages_per_tile = (k_stages + Cfg::kWUnits - 1) / Cfg::kWUnits;
+        uint32_t w_tile_base = 0;  // weight stages consumed by earlier tiles of this CTA
         const __nv_bfloat162 bias = bf162_from_bits(0x43084308u);  // 136.0 twice
         uint32_t it = 0;
         bool ok = true;
-        long long dq_wfull = 0, dq_wempty = 0, dq_work = 0;
+        long long dq_wfull = 0, dq_wempty = 0, dq_work = 0;  // dq_work includes the wait for the slot
         (void)dq_wfull; (void)dq_wempty; (void)dq_work;
         for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
             for (int ks = 0; ks < k_stages; ++ks, ++it) {
                 if ((int)(it % kDqGroups) != group) continue;
-                const int s = it % kWStages;
-                const uint32_t ph = (it / kWStages) & 1u;
+                const uint32_t w_it = w_tile_base + (uint32_t)(ks / Cfg::kWUnits);
+                const int unit = ks % Cfg::kWUnits;  // which K unit of the weight stage
+                const int s = w_it % kWStages;
+                const uint32_t ph = (w_it / kWStages) & 1u;
                 const int d = it % kARing;
                 const uint32_t dph = (it / kARing) & 1u;
                 {
@@ -351,15 +414,9 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     if (!mbar_wait(&w_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
                     XMOE_TACC(dq_wfull);
                 }
-                {
-                    XMOE_T0();
-                    if (!mbar_wait(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
-                    XMOE_TACC(dq_wempty);
-                }
                 XMOE_T0();
-                tc_fence_after();
                 const uint8_t* st = w_base + (size_t)s * Cfg::kWStageBytes;
-                const uint32_t sraw = reinterpret_cast<const uint16_t*>(st + kRawBytes)[row];
+                const uint32_t sraw = reinterpret_cast<const uint16_t*>(st + Cfg::kWRawBytes + unit * 256)[row];
                 const __nv_bfloat162 s2 = bf162_from_bits(sraw | (sraw << 16));
                 const uint32_t a_lane = tmem_base + ((uint32_t)(quadrant * 32) << 16) + d * kACols;
 #pragma unroll
@@ -367,8 +424,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     uint32_t o[32];
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
-                        const uint32_t chunk = (uint32_t)(half * 2 + c) ^ swz;
-                        const uint4 r4 = *reinterpret_cast<const uint4*>(st + row * (kStageK / 2) + chunk * 16);
+                        const uint32_t chunk = (uint32_t)(unit * (kStageK / 32) + half * 2 + c) ^ swz;
+                        const uint4 r4 = *reinterpret_cast<const uint4*>(st + row * kWRowBytes + chunk * 16);
                         const uint32_t words[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
                         for (int w = 0; w < 4; ++w) {
@@ -380,19 +437,30 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                             }
                         }
                     }
+                    if (half == 0) {
+                        // the expansion above does not need the tensor-memory slot: wait for it
+                        // only now, just before the first store
+                        if (!mbar_wait(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
+                        tc_fence_after();
+                    }
                     tmem_st32(a_lane + half * 32, o);
                 }
+                if (!ok) break;
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(&adq_full[d]);
                     mbar_arrive(&w_empty[s]);
+                    // an odd K-unit count leaves the tile's last weight stage half used: release
+                    // it on behalf of the unit that does not exist
+                    if (Cfg::kWUnits == 2 && ks == k_stages - 1 && unit == 0) mbar_arrive(&w_empty[s]);
                 }
                 XMOE_TACC(dq_work);
             }
+            w_tile_base += (uint32_t)w_stages_per_tile;
         }
-        if (warp == kFirstDqWarp && lane == 0) {
+        if (warp == Cfg::kFirstDq && lane == 0) {
             XMOE_TDUMP(6, dq_wfull);
             XMOE_TDUMP(7, dq_wempty);
             XMOE_TDUMP(8, dq_work);

@@ -81,8 +81,11 @@ struct Ff1Args {
 };
 
 struct Ff2Args {
-    CUtensorMap tm_w;  // u8 [E_tot*H, I/2], box 64 B x 128 rows, 64-byte swizzle
+    CUtensorMap tm_w;  // u8 [E_tot*H, I/2], box (128 | 64 | 32) B x 128 rows, swizzle = box width
     CUtensorMap tm_y;  // bf16 [R_cap, I], box 64 elems x NT rows, 128-byte swizzle
+    // token tiles of NT <= 64 only: the same tensor with 8- and 16-row boxes, used when a tile holds
+    // that few tokens (the MMA still reads NT rows; the columns of the stale ones are never stored)
+    CUtensorMap tm_y8, tm_y16;
     const void* w2_scale;  // bf16 [E_tot, G, H]
     const int32_t* counts;
     const int32_t* offsets;
