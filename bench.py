@@ -188,9 +188,11 @@ def main() -> int:
     if world > 1:
         from xcaliber_b200.ep import ExpertParallelMoE
 
-        layer = ExpertParallelMoE(shape, ckpt, device=dev)
+        layer = ExpertParallelMoE(shape, ckpt, device=dev, max_tokens=n)
         fwd = lambda: layer.forward(x, logits)  # noqa: E731
-        launches_per_step = layer.local.kernel_launches_per_forward + 4
+        # home side: router, amax, route pack (2), post counts, dispatch, scale, wait data, return, wait
+        # returns, combine; owner side: route pack (2), quantise, FF1, FF2 (+ activation top-k)
+        launches_per_step = 11 + layer.local.kernel_launches_per_forward - 3
     else:
         pw = ops.PreparedWeights.from_checkpoint(shape, ckpt.w13_packed, ckpt.w13_scale, ckpt.w13_gs,
                                                  ckpt.w2_qweight, ckpt.w2_scales, router_bias=ckpt.router_bias,
@@ -346,7 +348,9 @@ def main() -> int:
                                   f"dequantise-then-bf16-matmul oracle, 1 run, {med:.1f} s"}
 
     if world > 1:
-        statuses = [layer.local.status(m) for (m, _h) in list(layer.local._ws)[:1]]
+        statuses = [loc.status(m) for loc in layer._local_by_tile.values() for (m, _h) in list(loc._ws)[:1]]
+        if layer.peer is not None:
+            statuses.append(layer.peer.status())
     else:
         statuses = [layer.status(n)]
     if rank == 0:

@@ -226,6 +226,48 @@ int xmoe_repack_gptq(const void* qweight, void* out, int32_t num_mats, int32_t k
 /* Same target layout from K-major bytes [.., K/2] with low nibble = lower K. */
 int xmoe_repack_int4_kmajor(const void* w_in, void* out, size_t n_words, xmoe_stream_t stream);
 
+/* ---- expert parallelism over peer memory (one process per GPU, one node) ---------------- */
+/* No counterpart in the reference: its plugin refuses EP != 1 (vllm/xcaliber_int4_vllm/method.py:130-138).
+ * Rank g owns routed experts [g * experts_per_rank, (g + 1) * experts_per_rank). Every rank holds the
+ * four buffers below, the other ranks map them (CUDA IPC / symmetric memory; the library takes plain
+ * device pointers and never opens a handle itself), and the same call sequence runs on every rank's
+ * stream with no host synchronisation:
+ *   xmoe_ep_post_counts -> xmoe_ep_dispatch -> xmoe_ep_wait_data -> xmoe_forward_routed (y = NULL, n =
+ *   cap_rows, top_k = 1, on recv_x[rank]) -> xmoe_ep_return -> xmoe_ep_wait_ret -> xmoe_combine on
+ *   ret_rows[rank]. All device-side waits are bounded; xmoe_ep_status reports what went wrong. */
+#define XMOE_EP_MAX_WORLD 8
+#define XMOE_EP_CTL_BYTES 512
+#define XMOE_EP_TIMEOUT 1u   /* a peer's flag did not arrive within the spin limit */
+#define XMOE_EP_CAPACITY 2u  /* a row position or home slot fell outside the buffers */
+#define XMOE_EP_EXPERT 4u    /* an expert id outside [0, world * experts_per_rank) */
+typedef struct xmoe_ep_buffers {
+    int32_t world, rank, hidden, experts_per_rank;
+    int32_t cap_rows; /* rows of recv_x / recv_meta: worst case world * max_tokens * top_k */
+    int32_t ret_cap;  /* rows of ret_rows: >= max_tokens * top_k (+ room the caller uses for shared experts) */
+    void* ctl[XMOE_EP_MAX_WORLD];       /* XMOE_EP_CTL_BYTES each, zeroed once before the first call */
+    void* recv_x[XMOE_EP_MAX_WORLD];    /* bf16 [cap_rows, hidden] */
+    void* recv_meta[XMOE_EP_MAX_WORLD]; /* 16 bytes per row */
+    void* ret_rows[XMOE_EP_MAX_WORLD];  /* bf16 [ret_cap, hidden] */
+} xmoe_ep_buffers;
+/* counts_global: int32 [world * experts_per_rank] rows per expert among this rank's tokens (xmoe_route_pack's
+ * counts, run over ALL experts); amax_local: this rank's activation amax (fp32, device) or NULL. */
+int xmoe_ep_post_counts(const xmoe_ep_buffers* b, const int32_t* counts_global, const float* amax_local,
+                        xmoe_stream_t stream);
+/* topk_off = xmoe_route_pack's order inside the expert. amax_global (device fp32, may be NULL) receives the
+ * maximum over all ranks' amax_local: feed it to xmoe_act_scale_from_amax. */
+int xmoe_ep_dispatch(const xmoe_ep_buffers* b, const void* x, const int32_t* topk_idx, const void* topk_w,
+                     const int32_t* topk_off, const int32_t* counts_global, int32_t n_tokens, int32_t top_k,
+                     int32_t idx_stride, float* amax_global, xmoe_stream_t stream);
+/* e_recv int32 [cap_rows] (local expert id, -1 beyond the received rows), w_recv bf16 [cap_rows], n_recv int32 [1]. */
+int xmoe_ep_wait_data(const xmoe_ep_buffers* b, int32_t* e_recv, void* w_recv, int32_t* n_recv,
+                      xmoe_stream_t stream);
+/* out_rows / topk_row: the local pipeline's FF2 rows and packed-row index per received row (workspace view). */
+int xmoe_ep_return(const xmoe_ep_buffers* b, const void* out_rows, const int32_t* topk_row, int32_t expected_rows,
+                   xmoe_stream_t stream);
+int xmoe_ep_wait_ret(const xmoe_ep_buffers* b, xmoe_stream_t stream);
+/* Synchronises the stream and returns the sticky XMOE_EP_* bits of this rank's control block (0 = fine). */
+int xmoe_ep_status(const xmoe_ep_buffers* b, xmoe_stream_t stream, uint32_t* bits_out);
+
 /* Host helper: the 65536-entry sigmoid table indexed by bf16 bit pattern. */
 void xmoe_fill_sigmoid_lut(float* host_out);
 

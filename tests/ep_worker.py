@@ -1,6 +1,6 @@
 """Worker for tests/test_gpu_ep.py: run under torch.distributed.run with 2+ ranks (NCCL).
-Every rank runs the expert-parallel layer on its own tokens and compares with the single-GPU
-layer holding all experts. Routing, activation scale and FF1 rows are the same bits on both paths;
+Every rank runs the expert-parallel layer on its own tokens, once per transport (peer memory and
+NCCL; they must agree bit for bit), and compares with the single-GPU layer holding all experts. Routing, activation scale and FF1 rows are the same bits on both paths;
 FF2 adds its K stages in an order that depends on the token tile (small tiles accumulate in several
 partial sums), so the outputs may differ by a rounding step of bf16: max relative difference 1e-2
 (relative to max(|ref|, rms)), mean 1e-3."""
@@ -31,9 +31,17 @@ def main():
             x, lg = synth.make_inputs(shape, ck, n + 8 * r, seed=r)
             xs.append(x)
             ls.append(lg)
-        ep = ExpertParallelMoE(shape, ck, device=dev)
-        y = ep.forward(xs[rank].to(dev), ls[rank].to(dev))
-        torch.cuda.synchronize()
+        ys = {}
+        for transport in ("peer", "nccl"):
+            ep = ExpertParallelMoE(shape, ck, device=dev, transport=transport, max_tokens=128)
+            for _ in range(3):  # repeated calls reuse the exchange buffers and their flags
+                ys[transport] = ep.forward(xs[rank].to(dev), ls[rank].to(dev))
+            torch.cuda.synchronize()
+            if ep.peer is not None and ep.peer.status():
+                failures.append(f"{name}: rank {rank} peer exchange status {ep.peer.status():#x}")
+        if not torch.equal(ys["peer"], ys["nccl"]):
+            failures.append(f"{name}: rank {rank} peer and nccl transports differ")
+        y = ys["peer"]
         # single-GPU reference on the concatenation of all ranks' tokens (same global amax)
         pw = ops.PreparedWeights.from_checkpoint(shape, ck.w13_packed, ck.w13_scale, ck.w13_gs, ck.w2_qweight,
                                                  ck.w2_scales, router_bias=ck.router_bias, device=dev)

@@ -45,6 +45,19 @@ class XMoEWorkspaceView(C.Structure):
     ]
 
 
+EP_MAX_WORLD = 8
+EP_CTL_BYTES = 512
+
+
+class XMoEEpBuffers(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32), ("hidden", C.c_int32), ("experts_per_rank", C.c_int32),
+        ("cap_rows", C.c_int32), ("ret_cap", C.c_int32),
+        ("ctl", C.c_void_p * EP_MAX_WORLD), ("recv_x", C.c_void_p * EP_MAX_WORLD),
+        ("recv_meta", C.c_void_p * EP_MAX_WORLD), ("ret_rows", C.c_void_p * EP_MAX_WORLD),
+    ]
+
+
 # name -> (restype, argtypes); every symbol of include/xmoe_b200.h
 _P, _I, _F, _SZ = C.c_void_p, C.c_int32, C.c_float, C.c_size_t
 SIGNATURES = {
@@ -73,6 +86,12 @@ SIGNATURES = {
     "xmoe_act_topk": (C.c_int, [_P, _P, _P, _I, _I, _I, _I, _P]),
     "xmoe_ff2": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "xmoe_combine": (C.c_int, [_P, _P, _I, _I, _I, _I, _P, _P]),
+    "xmoe_ep_post_counts": (C.c_int, [C.POINTER(XMoEEpBuffers), _P, _P, _P]),
+    "xmoe_ep_dispatch": (C.c_int, [C.POINTER(XMoEEpBuffers), _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
+    "xmoe_ep_wait_data": (C.c_int, [C.POINTER(XMoEEpBuffers), _P, _P, _P, _P]),
+    "xmoe_ep_return": (C.c_int, [C.POINTER(XMoEEpBuffers), _P, _P, _I, _P]),
+    "xmoe_ep_wait_ret": (C.c_int, [C.POINTER(XMoEEpBuffers), _P]),
+    "xmoe_ep_status": (C.c_int, [C.POINTER(XMoEEpBuffers), _P, C.POINTER(C.c_uint32)]),
     "xmoe_nvfp4_sf_bytes": (_SZ, [_I, _I, _I]),
     "xmoe_prep_nvfp4_sf": (C.c_int, [_P, _P, _I, _I, _I, _P]),
     "xmoe_repack_gptq": (C.c_int, [_P, _P, _I, _I, _I, _P]),

@@ -129,6 +129,10 @@ __global__ __launch_bounds__(256) void act_quant_pack_kernel(
          unit += (size_t)gridDim.x * 8) {
         const int t = (int)(unit / units_per_token);
         const int h0 = (int)(unit % units_per_token) * 512 + (int)lane * 16;
+        // a token none of whose slots got a row (expert id -1 in caller-supplied routing): nothing to store
+        bool any_row = false;
+        for (int k = 0; k < k_eff; ++k) any_row |= topk_row[(size_t)t * idx_stride + k] >= 0;
+        if (!any_row) continue;
         uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         if (h0 < H) {  // H is a multiple of 16
             const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * H + h0);

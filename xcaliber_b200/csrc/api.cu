@@ -251,7 +251,8 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     if (n < 0) return XMOE_ERR_ARG;
     if (n == 0) return XMOE_OK;
     if (n > (1 << 22)) return XMOE_ERR_LIMIT;
-    if (!w || !x || !y || !ws || (!logits && !ext_idx)) return XMOE_ERR_ARG;
+    if (!w || !x || !ws || (!logits && !ext_idx)) return XMOE_ERR_ARG;
+    if (!y && !ext_idx) return XMOE_ERR_ARG;  // y may be null only with caller-supplied routing (rows stay in the workspace)
     if (!w->w13_packed || !w->w13_sf || !w->w13_gs || !w->w2_q || !w->w2_scale) return XMOE_ERR_ARG;
     if (reinterpret_cast<uintptr_t>(ws) & 1023u) return XMOE_ERR_WORKSPACE;
     const Layout L = make_layout(cfg, n);
@@ -378,7 +379,7 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     c.H = H;
     c.k_eff = L.k_eff;
     c.idx_stride = L.k_eff;
-    rc = launch_combine(c, stream);
+    rc = y ? launch_combine(c, stream) : XMOE_OK;
     prof_mark(8, stream);
     if (g_prof.ev && g_prof.step < g_prof.max_steps) ++g_prof.step;
     return rc;
@@ -681,6 +682,36 @@ int xmoe_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int
         return XMOE_ERR_SHAPE;
     return run_ff2(w2_q, w2_scale, yact, counts, offsets, out_rows, status, e_tot, H, I, (size_t)packed_rows_,
                    token_tile, (cudaStream_t)stream);
+}
+
+int xmoe_ep_post_counts(const xmoe_ep_buffers* b, const int32_t* counts_global, const float* amax_local,
+                        xmoe_stream_t stream) {
+    return launch_ep_post_counts(b, counts_global, amax_local, (cudaStream_t)stream);
+}
+int xmoe_ep_dispatch(const xmoe_ep_buffers* b, const void* x, const int32_t* topk_idx, const void* topk_w,
+                     const int32_t* topk_off, const int32_t* counts_global, int32_t n_tokens, int32_t top_k,
+                     int32_t idx_stride, float* amax_global, xmoe_stream_t stream) {
+    return launch_ep_dispatch(b, x, topk_idx, topk_w, topk_off, counts_global, n_tokens, top_k, idx_stride, amax_global,
+                              (cudaStream_t)stream);
+}
+int xmoe_ep_wait_data(const xmoe_ep_buffers* b, int32_t* e_recv, void* w_recv, int32_t* n_recv, xmoe_stream_t stream) {
+    return launch_ep_wait_data(b, e_recv, w_recv, n_recv, (cudaStream_t)stream);
+}
+int xmoe_ep_return(const xmoe_ep_buffers* b, const void* out_rows, const int32_t* topk_row, int32_t expected_rows,
+                   xmoe_stream_t stream) {
+    return launch_ep_return(b, out_rows, topk_row, expected_rows, (cudaStream_t)stream);
+}
+int xmoe_ep_wait_ret(const xmoe_ep_buffers* b, xmoe_stream_t stream) {
+    return launch_ep_wait_ret(b, (cudaStream_t)stream);
+}
+int xmoe_ep_status(const xmoe_ep_buffers* b, xmoe_stream_t stream, uint32_t* bits_out) {
+    if (!b || !bits_out || b->rank < 0 || b->rank >= XMOE_EP_MAX_WORLD || !b->ctl[b->rank]) return XMOE_ERR_ARG;
+    if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return XMOE_ERR_CUDA;
+    // the sticky error word sits after the count table, the amax slots, three flag arrays and three counters
+    const size_t off = (64 + 8 + 24 + 3) * 4;
+    if (cudaMemcpy(bits_out, (const uint8_t*)b->ctl[b->rank] + off, 4, cudaMemcpyDeviceToHost) != cudaSuccess)
+        return XMOE_ERR_CUDA;
+    return XMOE_OK;
 }
 
 int xmoe_combine(const void* out_rows, const int32_t* topk_row, int32_t n, int32_t H, int32_t k_eff, int32_t idx_stride,

@@ -1,0 +1,337 @@
+// Expert-parallel token exchange over peer memory (NVLink / NVSwitch), device side.
+//
+// Not in the reference (its plugin refuses EP != 1, vllm/xcaliber_int4_vllm/method.py:130-138).
+// One process per GPU; every rank maps every other rank's exchange buffers (plain peer
+// pointers, no multicast). A layer call is a fixed sequence of kernels on each rank's stream,
+// with no host synchronisation and no host-known row counts:
+//
+//   post_counts   per-destination row counts + local activation amax -> every rank's table
+//   dispatch      wait for all tables; copy each (token, slot) row and its (local expert, gate
+//                 weight, home slot) record straight into the owner rank's receive buffer, at a
+//                 position fixed by (source rank, expert, order inside the expert)
+//   wait_data     wait until every rank's rows have landed; expand the records into the
+//                 routing arrays of the local pipeline (expert id -1 = unused row)
+//   (local route pack -> NVFP4 quantise -> FF1 -> FF2 on the received rows)
+//   return        copy each FF2 output row back to its home rank, slot (token * k + slot)
+//   wait_ret      wait until every rank has returned its rows; the home rank then sums them
+//
+// Synchronisation is by epoch-valued flags in each rank's control block: a writer stores data,
+// fences at system scope and then releases the flag in the READER's memory; a reader spins on
+// its own memory. Every spin is bounded: when it gives up it records XMOE_EP_TIMEOUT in the
+// control block and the kernel carries on (on incomplete data) so that the stream drains.
+// The flags of one call also fence buffer reuse: nobody starts call t+1 before it has seen
+// every rank's return flag of call t, and a rank raises that flag only after its last read of
+// its receive buffer and count table.
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace xmoe {
+
+namespace {
+
+constexpr int kMaxWorld = 8;
+constexpr int kMaxEpExperts = 1024;
+constexpr uint32_t kSpinLimit = 1u << 24;  // x ~200 ns: a few seconds
+
+struct EpCtl {  // 512 bytes, zero-initialised by the host before the first call
+    int32_t counts[kMaxWorld][kMaxWorld];  // [source rank][destination rank] rows
+    uint32_t amax[kMaxWorld];              // fp32 bits (non-negative: ordered as integers)
+    uint32_t flag_counts[kMaxWorld];
+    uint32_t flag_data[kMaxWorld];
+    uint32_t flag_ret[kMaxWorld];
+    uint32_t epoch;            // local: number of calls started
+    uint32_t ticket_dispatch;  // local: CTAs of the dispatch kernel that finished storing
+    uint32_t ticket_return;
+    uint32_t error;            // local: sticky XMOE_EP_* bits
+    uint32_t pad[28];
+};
+static_assert(sizeof(EpCtl) == XMOE_EP_CTL_BYTES, "control block layout");
+static_assert(offsetof(EpCtl, error) == (64 + 8 + 24 + 3) * 4, "xmoe_ep_status reads the error word at this offset");
+static_assert(kMaxWorld == XMOE_EP_MAX_WORLD, "public limit");
+
+constexpr uint32_t kErrTimeout = XMOE_EP_TIMEOUT, kErrCapacity = XMOE_EP_CAPACITY, kErrExpert = XMOE_EP_EXPERT;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Bounded wait until *flag has reached `epoch` (wrap-safe).
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* error) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
+        __nanosleep(200);
+    }
+    atomicOr(error, kErrTimeout);
+    return false;
+}
+
+struct EpCtx {
+    EpCtl* ctl[kMaxWorld];
+    uint4* recv_x[kMaxWorld];     // bf16 [cap_rows, H]
+    int4* recv_meta[kMaxWorld];   // [cap_rows]: local expert, gate weight bits, home slot, 0
+    uint4* ret_rows[kMaxWorld];   // bf16 [ret_cap, H]
+    int world, rank, H, experts_per_rank, cap_rows, ret_cap;
+};
+
+__global__ __launch_bounds__(256) void ep_post_counts_kernel(EpCtx c, const int32_t* __restrict__ counts_global,
+                                                            const float* __restrict__ amax_local) {
+    __shared__ int dest_sum[kMaxWorld];
+    __shared__ uint32_t epoch;
+    EpCtl* me = c.ctl[c.rank];
+    if (threadIdx.x == 0) {
+        epoch = me->epoch + 1u;
+        me->epoch = epoch;
+    }
+    if (threadIdx.x < c.world) {
+        int s = 0;
+        for (int e = 0; e < c.experts_per_rank; ++e) s += counts_global[threadIdx.x * c.experts_per_rank + e];
+        dest_sum[threadIdx.x] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x < c.world) {
+        EpCtl* peer = c.ctl[threadIdx.x];
+        for (int d = 0; d < c.world; ++d) peer->counts[c.rank][d] = dest_sum[d];
+        peer->amax[c.rank] = __float_as_uint(amax_local ? fabsf(amax_local[0]) : 0.f);
+        __threadfence_system();
+        st_release_sys(&peer->flag_counts[c.rank], epoch);
+    }
+}
+
+// Warp copy of one bf16 row (H % 8 == 0), 16 bytes per lane and step.
+__device__ __forceinline__ void copy_row(uint4* dst, const uint4* src, int hv, int lane) {
+    for (int i = lane; i < hv; i += 32) dst[i] = src[i];
+}
+
+__global__ __launch_bounds__(256) void ep_dispatch_kernel(EpCtx c, const uint4* __restrict__ x,
+                                                         const int32_t* __restrict__ topk_idx,
+                                                         const uint16_t* __restrict__ topk_w,
+                                                         const int32_t* __restrict__ topk_off,
+                                                         const int32_t* __restrict__ counts_global, int n, int top_k,
+                                                         int idx_stride, float* __restrict__ amax_global) {
+    __shared__ int base[kMaxWorld];         // rows of lower ranks ahead of mine at each destination
+    __shared__ int pre[kMaxEpExperts];      // rows of earlier experts of the same owner rank (mine only)
+    EpCtl* me = c.ctl[c.rank];
+    const uint32_t epoch = me->epoch;
+    if (threadIdx.x < c.world) wait_flag(&me->flag_counts[threadIdx.x], epoch, &me->error);
+    __syncthreads();
+    const int E = c.world * c.experts_per_rank;
+    if (threadIdx.x < c.world) {
+        int s = 0;
+        for (int r = 0; r < c.rank; ++r) s += me->counts[r][threadIdx.x];
+        base[threadIdx.x] = s;
+    }
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int first = (e / c.experts_per_rank) * c.experts_per_rank;
+        int s = 0;
+        for (int q = first; q < e; ++q) s += counts_global[q];
+        pre[e] = s;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0 && amax_global) {
+        uint32_t m = 0;
+        for (int r = 0; r < c.world; ++r) m = max(m, me->amax[r]);
+        amax_global[0] = __uint_as_float(m);
+    }
+    __syncthreads();
+    const int hv = c.H / 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total = n * top_k;
+    for (int a = blockIdx.x * 8 + warp; a < total; a += gridDim.x * 8) {
+        const int t = a / top_k, k = a - t * top_k;
+        const int e = topk_idx[(size_t)t * idx_stride + k];
+        if (e < 0 || e >= E) {
+            if (lane == 0) atomicOr(&me->error, kErrExpert);
+            continue;
+        }
+        const int d = e / c.experts_per_rank;
+        const int row = base[d] + pre[e] + topk_off[(size_t)t * idx_stride + k];
+        if (row < 0 || row >= c.cap_rows) {
+            if (lane == 0) atomicOr(&me->error, kErrCapacity);
+            continue;
+        }
+        copy_row(c.recv_x[d] + (size_t)row * hv, x + (size_t)t * hv, hv, lane);
+        if (lane == 0)
+            c.recv_meta[d][row] = make_int4(e - d * c.experts_per_rank, (int)topk_w[(size_t)t * idx_stride + k], a, 0);
+    }
+    // every store of this CTA is ordered before its ticket; the last CTA raises the flags
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t ticket = atomicAdd(&me->ticket_dispatch, 1u);
+        if (ticket == gridDim.x - 1) {
+            me->ticket_dispatch = 0u;
+            __threadfence_system();
+            for (int p = 0; p < c.world; ++p) st_release_sys(&c.ctl[p]->flag_data[c.rank], epoch);
+        }
+    }
+}
+
+__global__ __launch_bounds__(256) void ep_wait_data_kernel(EpCtx c, int32_t* __restrict__ e_recv,
+                                                          uint16_t* __restrict__ w_recv, int32_t* __restrict__ n_recv) {
+    __shared__ int total;
+    EpCtl* me = c.ctl[c.rank];
+    const uint32_t epoch = me->epoch;
+    if (threadIdx.x < c.world) wait_flag(&me->flag_data[threadIdx.x], epoch, &me->error);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int s = 0;
+        for (int r = 0; r < c.world; ++r) s += me->counts[r][c.rank];
+        total = min(s, c.cap_rows);
+        if (blockIdx.x == 0 && n_recv) n_recv[0] = total;
+    }
+    __syncthreads();
+    const int4* meta = c.recv_meta[c.rank];
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < c.cap_rows; j += gridDim.x * blockDim.x) {
+        if (j < total) {
+            const int4 m = meta[j];
+            e_recv[j] = m.x;
+            w_recv[j] = (uint16_t)m.y;
+        } else {
+            e_recv[j] = -1;
+            w_recv[j] = 0;
+        }
+    }
+}
+
+__global__ __launch_bounds__(256) void ep_return_kernel(EpCtx c, const uint4* __restrict__ out_rows,
+                                                       const int32_t* __restrict__ topk_row) {
+    __shared__ int bound[kMaxWorld + 1];  // receive-buffer regions by source rank
+    EpCtl* me = c.ctl[c.rank];
+    const uint32_t epoch = me->epoch;
+    if (threadIdx.x == 0) {
+        int s = 0;
+        for (int r = 0; r < c.world; ++r) {
+            bound[r] = s;
+            s += me->counts[r][c.rank];
+        }
+        bound[c.world] = min(s, c.cap_rows);
+    }
+    __syncthreads();
+    const int hv = c.H / 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total = bound[c.world];
+    const int4* meta = c.recv_meta[c.rank];
+    for (int j = blockIdx.x * 8 + warp; j < total; j += gridDim.x * 8) {
+        int r = 0;
+        while (r + 1 < c.world && j >= bound[r + 1]) ++r;
+        const int slot = meta[j].z;
+        const int prow = topk_row[j];
+        if (slot < 0 || slot >= c.ret_cap || prow < 0) {
+            if (lane == 0) atomicOr(&me->error, kErrCapacity);
+            continue;
+        }
+        copy_row(c.ret_rows[r] + (size_t)slot * hv, out_rows + (size_t)prow * hv, hv, lane);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t ticket = atomicAdd(&me->ticket_return, 1u);
+        if (ticket == gridDim.x - 1) {
+            me->ticket_return = 0u;
+            __threadfence_system();
+            for (int p = 0; p < c.world; ++p) st_release_sys(&c.ctl[p]->flag_ret[c.rank], epoch);
+        }
+    }
+}
+
+__global__ void ep_wait_ret_kernel(EpCtx c) {
+    EpCtl* me = c.ctl[c.rank];
+    if (threadIdx.x < c.world) wait_flag(&me->flag_ret[threadIdx.x], me->epoch, &me->error);
+}
+
+int make_ctx(const xmoe_ep_buffers* b, EpCtx* c) {
+    if (!b || b->world < 1 || b->world > kMaxWorld || b->rank < 0 || b->rank >= b->world) return XMOE_ERR_ARG;
+    if (b->hidden <= 0 || b->hidden % 8 || b->experts_per_rank <= 0) return XMOE_ERR_SHAPE;
+    if (b->world * b->experts_per_rank > kMaxEpExperts) return XMOE_ERR_LIMIT;
+    if (b->cap_rows <= 0 || b->ret_cap <= 0) return XMOE_ERR_ARG;
+    for (int r = 0; r < b->world; ++r) {
+        if (!b->ctl[r] || !b->recv_x[r] || !b->recv_meta[r] || !b->ret_rows[r]) return XMOE_ERR_ARG;
+        c->ctl[r] = (EpCtl*)b->ctl[r];
+        c->recv_x[r] = (uint4*)b->recv_x[r];
+        c->recv_meta[r] = (int4*)b->recv_meta[r];
+        c->ret_rows[r] = (uint4*)b->ret_rows[r];
+    }
+    c->world = b->world;
+    c->rank = b->rank;
+    c->H = b->hidden;
+    c->experts_per_rank = b->experts_per_rank;
+    c->cap_rows = b->cap_rows;
+    c->ret_cap = b->ret_cap;
+    return XMOE_OK;
+}
+
+int grid_for(int warps_of_work) {
+    int blocks = (warps_of_work + 7) / 8;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    return blocks;
+}
+
+}  // namespace
+
+int launch_ep_post_counts(const xmoe_ep_buffers* b, const int32_t* counts_global, const float* amax_local,
+                          cudaStream_t stream) {
+    EpCtx c;
+    int rc = make_ctx(b, &c);
+    if (rc) return rc;
+    if (!counts_global) return XMOE_ERR_ARG;
+    ep_post_counts_kernel<<<1, 256, 0, stream>>>(c, counts_global, amax_local);
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+int launch_ep_dispatch(const xmoe_ep_buffers* b, const void* x, const int32_t* topk_idx, const void* topk_w,
+                       const int32_t* topk_off, const int32_t* counts_global, int n, int top_k, int idx_stride,
+                       float* amax_global, cudaStream_t stream) {
+    EpCtx c;
+    int rc = make_ctx(b, &c);
+    if (rc) return rc;
+    if (n < 0 || top_k < 1 || idx_stride < top_k) return XMOE_ERR_ARG;
+    if (n > 0 && (!x || !topk_idx || !topk_w || !topk_off)) return XMOE_ERR_ARG;
+    if (!counts_global) return XMOE_ERR_ARG;
+    if ((long long)n * top_k > b->ret_cap) return XMOE_ERR_LIMIT;
+    ep_dispatch_kernel<<<grid_for(n * top_k), 256, 0, stream>>>(c, (const uint4*)x, topk_idx, (const uint16_t*)topk_w,
+                                                               topk_off, counts_global, n, top_k, idx_stride,
+                                                               amax_global);
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+int launch_ep_wait_data(const xmoe_ep_buffers* b, int32_t* e_recv, void* w_recv, int32_t* n_recv,
+                        cudaStream_t stream) {
+    EpCtx c;
+    int rc = make_ctx(b, &c);
+    if (rc) return rc;
+    if (!e_recv || !w_recv) return XMOE_ERR_ARG;
+    int blocks = (c.cap_rows + 255) / 256;
+    blocks = blocks > 148 ? 148 : blocks;
+    ep_wait_data_kernel<<<blocks, 256, 0, stream>>>(c, e_recv, (uint16_t*)w_recv, n_recv);
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+int launch_ep_return(const xmoe_ep_buffers* b, const void* out_rows, const int32_t* topk_row, int expected_rows,
+                     cudaStream_t stream) {
+    EpCtx c;
+    int rc = make_ctx(b, &c);
+    if (rc) return rc;
+    if (!out_rows || !topk_row) return XMOE_ERR_ARG;
+    ep_return_kernel<<<grid_for(expected_rows > 0 ? expected_rows : 1), 256, 0, stream>>>(c, (const uint4*)out_rows,
+                                                                                          topk_row);
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+int launch_ep_wait_ret(const xmoe_ep_buffers* b, cudaStream_t stream) {
+    EpCtx c;
+    int rc = make_ctx(b, &c);
+    if (rc) return rc;
+    ep_wait_ret_kernel<<<1, 32, 0, stream>>>(c);
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+}  // namespace xmoe

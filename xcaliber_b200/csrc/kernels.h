@@ -8,6 +8,8 @@
 #include <cstddef>
 #include <cstdint>
 
+#include "../../include/xmoe_b200.h"
+
 namespace xmoe {
 
 struct RouterArgs {
@@ -129,6 +131,15 @@ int launch_act_topk(const ActTopkArgs& a, cudaStream_t stream);
 int launch_prep_nvfp4_sf(const void* sf_in, void* sf_out, int n_mats, int rows, int kblocks16, int mb, int kb_pad,
                          cudaStream_t stream);
 int launch_repack_gptq(const void* qweight, void* out, int E, int K, int O, cudaStream_t stream);
+int launch_ep_post_counts(const xmoe_ep_buffers* b, const int32_t* counts_global, const float* amax_local,
+                          cudaStream_t stream);
+int launch_ep_dispatch(const xmoe_ep_buffers* b, const void* x, const int32_t* topk_idx, const void* topk_w,
+                       const int32_t* topk_off, const int32_t* counts_global, int n, int top_k, int idx_stride,
+                       float* amax_global, cudaStream_t stream);
+int launch_ep_wait_data(const xmoe_ep_buffers* b, int32_t* e_recv, void* w_recv, int32_t* n_recv, cudaStream_t stream);
+int launch_ep_return(const xmoe_ep_buffers* b, const void* out_rows, const int32_t* topk_row, int expected_rows,
+                     cudaStream_t stream);
+int launch_ep_wait_ret(const xmoe_ep_buffers* b, cudaStream_t stream);
 int launch_repack_kmajor_int4(const void* w_in, void* out, size_t n_words, cudaStream_t stream);
 
 }  // namespace xmoe

@@ -328,7 +328,7 @@ __global__ __launch_bounds__(256) void route_scatter_kernel(
         for (int k = 0; k < topk; ++k) {
             const int e = topk_idx[(size_t)t_mine * idx_stride + k];
             if (e >= 0 && e < E) atomicAdd(&warp_base[warp][e], 1);
-            else atomicExch(status, 0x600u);  // expert id outside [0, E)
+            else if (e != -1) atomicExch(status, 0x600u);  // expert id outside [0, E); -1 = slot not in use
         }
         for (int s = 0; s < n_shared; ++s) atomicAdd(&warp_base[warp][E + s], 1);
     }

@@ -7,8 +7,11 @@ replica of the shared experts; tokens are data-parallel. Per layer call:
   1. route the local tokens over all E experts (router kernel);
   2. agree on the activation scale: local amax -> max all-reduce (4 bytes) -> XGS/XGSINV, so
      every rank quantises with the scale one GPU would have used on the whole batch;
-  3. dispatch: one NCCL all-to-all of (bf16 row, local expert id, gate weight) per assignment,
-     grouped by destination rank (counts exchanged first);
+  3. dispatch: each (token, slot) row travels to the owner rank with (local expert id, gate weight):
+     by default as kernels that store straight into the owner's receive buffer over NVLink peer
+     memory, positions agreed through a device-side count table (no host synchronisation,
+     csrc/ep_p2p.cu); with transport="nccl" as one NCCL all-to-all grouped by destination rank
+     (counts exchanged first, one host read);
   4. run the local pipeline (route pack -> NVFP4 quantise -> FF1 -> FF2) on the received rows;
   5. combine: the reverse all-to-all returns one bf16 row per assignment; the home rank sums
      its k rows (+ shared-expert rows) in slot order with the combine kernel.
@@ -105,10 +108,117 @@ def ep_forward(x, topk_idx, topk_w, experts_per_rank, local_experts_fn, combine_
     return combine_fn(rows, topk_row.contiguous())
 
 
-class ExpertParallelMoE:
-    """The CUDA instantiation: NCCL all-to-all + the library's kernels for every compute step."""
+def _round_up(v: int, m: int) -> int:
+    return (v + m - 1) // m * m
 
-    def __init__(self, shape, checkpoint, group=None, device="cuda"):
+
+class PeerExchange:
+    """Exchange buffers of the peer-memory transport: one symmetric allocation per rank, mapped by
+    every rank of the group (torch symmetric memory does the handle exchange; the library only sees
+    plain device pointers), plus the per-call scratch, all sized once for `max_tokens`."""
+
+    def __init__(self, shape, e_local: int, max_tokens: int, device, group=None):
+        import ctypes as C
+
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _lib
+
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > _lib.EP_MAX_WORLD:
+            raise RuntimeError(f"peer-memory exchange supports at most {_lib.EP_MAX_WORLD} ranks")
+        k, h = shape.top_k, shape.hidden
+        self.max_tokens = max_tokens
+        self.cap_rows = _round_up(self.world * max_tokens * k, 128)
+        self.ret_cap = max_tokens * (k + shape.num_shared_experts)
+        sizes = dict(ctl=_lib.EP_CTL_BYTES, recv_x=self.cap_rows * h * 2, recv_meta=self.cap_rows * 16,
+                     ret_rows=self.ret_cap * h * 2)
+        offs, total = {}, 0
+        for name, nbytes in sizes.items():
+            offs[name] = total
+            total += _round_up(nbytes, 1024)
+        pg = group if group is not None else dist.group.WORLD
+        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+        self.handle = symm.rendezvous(self.buf, pg.group_name)
+        self.buf.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every rank's control block is zero before anyone posts to it
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        b = _lib.XMoEEpBuffers()
+        b.world, b.rank, b.hidden, b.experts_per_rank = self.world, self.rank, h, e_local
+        b.cap_rows, b.ret_cap = self.cap_rows, self.ret_cap
+        for r in range(self.world):
+            b.ctl[r] = ptrs[r] + offs["ctl"]
+            b.recv_x[r] = ptrs[r] + offs["recv_x"]
+            b.recv_meta[r] = ptrs[r] + offs["recv_meta"]
+            b.ret_rows[r] = ptrs[r] + offs["ret_rows"]
+        self.c_buffers = b
+        self.ref = C.byref(b)
+
+        def local(name, dtype, *dims):
+            return self.buf[offs[name]: offs[name] + sizes[name]].view(dtype).reshape(*dims)
+
+        self.recv_x = local("recv_x", torch.bfloat16, self.cap_rows, h)
+        self.ret_rows = local("ret_rows", torch.bfloat16, self.ret_cap, h)
+        e = self.world * e_local
+        i32 = dict(dtype=torch.int32, device=device)
+        r_cap = max_tokens * k + 128 * e
+        self.counts = torch.zeros(e, **i32)
+        self.offsets = torch.zeros(e + 1, **i32)
+        self.topk_off = torch.zeros(max_tokens, k, **i32)
+        self.topk_row = torch.zeros(max_tokens, k, **i32)
+        self.row_token = torch.zeros(r_cap, **i32)
+        self.row_weight = torch.zeros(r_cap, dtype=torch.bfloat16, device=device)
+        self.pack_scratch = torch.zeros(max(1, _lib.lib().xmoe_route_pack_scratch_bytes(max_tokens, e, 0)),
+                                        dtype=torch.uint8, device=device)
+        self.pack_status = torch.zeros(1, **i32)
+        self.amax_global = torch.zeros(1, dtype=torch.float32, device=device)
+        self.e_recv = torch.zeros(self.cap_rows, 1, **i32)
+        self.w_recv = torch.zeros(self.cap_rows, 1, dtype=torch.bfloat16, device=device)
+        self.n_recv = torch.zeros(1, **i32)
+        self.home_slots = {}
+
+    def slots(self, n: int, k_eff: int, device) -> torch.Tensor:
+        """topk_row of the home-side combine: row (token * k + slot), shared-expert rows after n * k."""
+        key = (n, k_eff)
+        t = self.home_slots.get(key)
+        if t is None:
+            k = self.topk_off.shape[1]
+            routed = torch.arange(n * k, dtype=torch.int32, device=device).reshape(n, k)
+            if k_eff > k:
+                ns = k_eff - k
+                sh = (n * k + torch.arange(n * ns, dtype=torch.int32, device=device)).reshape(n, ns)
+                routed = torch.cat([routed, sh], dim=1)
+            t = self.home_slots[key] = routed.contiguous()
+        return t
+
+    def status(self) -> int:
+        import ctypes as C
+
+        from . import _lib
+        from .ops import _stream
+
+        bits = C.c_uint32(0)
+        _lib.check(_lib.lib().xmoe_ep_status(self.ref, _stream(), C.byref(bits)), "xmoe_ep_status")
+        return bits.value
+
+
+def local_token_tile(rows: int, e_local: int) -> int:
+    """Token tile of the local pipeline from the rows a rank expects under balanced routing (the
+    library's own choice would see the receive buffer's capacity, world times larger)."""
+    avg = rows / max(e_local, 1)
+    if avg > 48.0:
+        return 128 if rows > 64 else 64
+    return 64 if avg > 20.0 else 32
+
+
+class ExpertParallelMoE:
+    """The CUDA instantiation. transport="peer" (default): the exchange runs as kernels over peer
+    memory with no host synchronisation; transport="nccl": NCCL all-to-all with host-side counts."""
+
+    def __init__(self, shape, checkpoint, group=None, device="cuda", transport: str = "peer",
+                 max_tokens: int = 4096):
         from . import ops
         from .synth import scaled_shape
 
@@ -128,6 +238,13 @@ class ExpertParallelMoE:
                                                  checkpoint.w13_gs[sl], checkpoint.w2_qweight[sl],
                                                  checkpoint.w2_scales[sl], device=device)
         self.local = ops.FusedMoE(local_shape, pw)
+        self._local_shape, self._local_pw, self._local_by_tile, self._local_ptrs = local_shape, pw, {}, {}
+        if transport not in ("peer", "nccl"):
+            raise ValueError("transport must be 'peer' or 'nccl'")
+        self.transport = transport
+        self.max_tokens = max_tokens
+        self.peer = PeerExchange(shape, self.e_local, max_tokens, torch.device(device), group) \
+            if transport == "peer" else None
         # router state lives with the full expert count
         self.router_weights = ops.PreparedWeights(
             pw.w13_packed, pw.w13_sf, pw.w13_gs, pw.w2_q, pw.w2_scale,
@@ -145,8 +262,17 @@ class ExpertParallelMoE:
             self.shared = ops.FusedMoE(sh_shape, spw)
         self._scale = None
 
+    def _local_layer(self, home_tokens: int):
+        """The local pipeline with the token tile fixed from this rank's own batch (both transports
+        use the same rule, so they run the same kernels)."""
+        tile = local_token_tile(home_tokens * self.shape.top_k, self.e_local)
+        local = self._local_by_tile.get(tile)
+        if local is None:
+            local = self._local_by_tile[tile] = self.ops.FusedMoE(self._local_shape, self._local_pw, token_tile=tile)
+        return tile, local
+
     def _local_experts(self, x_rows, e_local, w):
-        return self.local.forward_routed(x_rows, e_local, w, act_scale=self._scale)
+        return self._local_layer(self._home_tokens)[1].forward_routed(x_rows, e_local, w, act_scale=self._scale)
 
     def _shared(self, x):
         ns = self.shape.num_shared_experts
@@ -158,8 +284,52 @@ class ExpertParallelMoE:
         v = self.shared.view(n)
         return v["out_rows"].index_select(0, v["topk_row"].reshape(-1).to(torch.int64))
 
+    def _forward_peer(self, x: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+        """Steps 1-5 with the exchange as kernels over peer memory: nothing here waits on the host."""
+        from . import _lib
+        from .ops import _stream
+
+        ops, px, lib = self.ops, self.peer, _lib.lib()
+        n, k = x.shape[0], self.shape.top_k
+        if n > px.max_tokens:
+            raise RuntimeError(f"{n} tokens exceed the exchange buffers (max_tokens={px.max_tokens})")
+        x = x.contiguous()
+        idx, w = ops.router_topk(router_logits, self.shape, self.router_weights)
+        scale_local = ops.act_amax(x)
+        st = _stream()
+        e = self.shape.num_experts
+        _lib.check(lib.xmoe_route_pack(idx.data_ptr(), w.data_ptr(), n, e, k, k, 0, px.pack_scratch.data_ptr(),
+                                       px.counts.data_ptr(), px.offsets.data_ptr(), px.topk_off.data_ptr(),
+                                       px.topk_row.data_ptr(), px.row_token.data_ptr(), px.row_weight.data_ptr(),
+                                       px.pack_status.data_ptr(), st), "xmoe_route_pack")
+        _lib.check(lib.xmoe_ep_post_counts(px.ref, px.counts.data_ptr(), scale_local[2:3].data_ptr(), st),
+                   "xmoe_ep_post_counts")
+        _lib.check(lib.xmoe_ep_dispatch(px.ref, x.data_ptr(), idx.data_ptr(), w.data_ptr(), px.topk_off.data_ptr(),
+                                        px.counts.data_ptr(), n, k, k, px.amax_global.data_ptr(), st),
+                   "xmoe_ep_dispatch")
+        self._scale = ops.act_scale_from_amax(px.amax_global)
+        _lib.check(lib.xmoe_ep_wait_data(px.ref, px.e_recv.data_ptr(), px.w_recv.data_ptr(), px.n_recv.data_ptr(), st),
+                   "xmoe_ep_wait_data")
+        tile, local = self._local_layer(n)
+        local.forward_routed_rows(px.recv_x, px.e_recv, px.w_recv, act_scale=self._scale)
+        ptrs = self._local_ptrs.get(tile)
+        if ptrs is None:
+            v = local.view(px.cap_rows)
+            ptrs = self._local_ptrs[tile] = (v["out_rows"].data_ptr(), v["topk_row"].data_ptr())
+        _lib.check(lib.xmoe_ep_return(px.ref, ptrs[0], ptrs[1], n * k, st), "xmoe_ep_return")
+        k_eff = k
+        if self.shared is not None:
+            y_sh = self._shared(x)
+            px.ret_rows[n * k: n * k + y_sh.shape[0]].copy_(y_sh)
+            k_eff = k + self.shape.num_shared_experts
+        _lib.check(lib.xmoe_ep_wait_ret(px.ref, st), "xmoe_ep_wait_ret")
+        return ops.combine(px.ret_rows, px.slots(n, k_eff, x.device))
+
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+        if self.peer is not None:
+            return self._forward_peer(x, router_logits)
         ops = self.ops
+        self._home_tokens = x.shape[0]
         idx, w = ops.router_topk(router_logits, self.shape, self.router_weights)
         scale = ops.act_amax(x)
         amax = scale[2:3].clone()
