@@ -21,8 +21,8 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
+import threading
 import time
 from pathlib import Path
 
@@ -36,10 +36,6 @@ from xcaliber_b200 import synth  # noqa: E402
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 NVFP4_NOMINAL_TFLOPS = 9000.0  # dense NVFP4 spec figure; there is no measured FP4 peak on this pool
-SMI_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
 
 def measured_peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
@@ -51,49 +47,83 @@ def measured_peaks() -> dict:
 
 
 class ClockSampler:
-    """nvidia-smi polled every 100 ms while the timed region runs (read-only query)."""
+    """SM clock and clock-event reasons of one GPU, read through NVML every 10 ms by a thread while
+    the timed region runs (read-only queries; nothing is set). The samples are also written to
+    gpurun_out/clocks_rank<i>.csv."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
-        self.proc = None
         self.path = ROOT / "gpurun_out" / f"clocks_rank{gpu_index}.csv"
+        self.samples, self.thread, self.handle, self.nv = [], None, None, None
+        self.stop_flag = threading.Event()
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(gpu_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            try:
+                self.handle = nv.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.handle = nv.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.nv = nv
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self.handle, nv.NVML_CLOCK_SM)
+        except Exception as exc:  # NVML missing: report that instead of guessing
+            self.error = f"NVML unavailable: {exc}"
+
+    def _sample(self):
+        nv = self.nv
+        sm = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+        try:
+            reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+        except Exception:
+            reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+        try:
+            power = nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+        except Exception:
+            power = float("nan")
+        self.samples.append((time.perf_counter(), sm, int(reasons), power))
+
+    def _run(self):
+        while not self.stop_flag.is_set():
+            try:
+                self._sample()
+            except Exception:
+                break
+            self.stop_flag.wait(0.01)
 
     def start(self):
-        try:
-            self.path.parent.mkdir(exist_ok=True)
-            self.fh = open(self.path, "w")
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={SMI_QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.fh,
-                                         stderr=subprocess.DEVNULL)
-        except OSError:
-            self.proc = None
+        if self.nv is None:
+            return
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
+        if self.nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.error], "samples": 0}
         try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        self.fh.close()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.path.read_text().splitlines():
-            f = [c.strip() for c in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+            self._sample()  # at least one sample taken while the last kernels are still in flight
+        except Exception:
+            pass
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
+        sm = [s[1] for s in self.samples]
+        bits = 0
+        for s in self.samples:
+            bits |= s[2]
+        try:
+            self.path.parent.mkdir(exist_ok=True)
+            with open(self.path, "w") as fh:
+                fh.write("t_s,sm_mhz,reason_bits,power_w\n")
+                for t, mhz, r, pw in self.samples:
+                    fh.write(f"{t:.4f},{mhz},{r:#x},{pw:.1f}\n")
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(name for bit, name in self.REASONS.items() if bits & bit), "samples": len(sm)}
 
 
 def cpu_oracle_tokens_per_s(shape, weights_cpu, sample_tokens: int, steps: int, warmup: int):
