@@ -37,10 +37,12 @@ constexpr int kABytes = kTokTile * kStageKBytes;      // 16 KiB activations
 constexpr int kBBytes = 2 * kWTile * kStageKBytes;    // 32 KiB gate|up weights
 constexpr int kStageBytes = kABytes + kBBytes + 3 * kSfBytes;   // 54 KiB
 constexpr int kStages = 4;
-constexpr int kThreads = 320;        // producer warp, MMA warp, 8 epilogue warps
+constexpr int kThreads = 416;        // producer warp, MMA warp, 8 epilogue warps, 3 scale-factor copy warps
+constexpr int kFirstSfWarp = 10;
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = 256;
-constexpr int kSfSlotCols = 48;        // per slot: 4 K-blocks x (tokens 4 + gate 4 + up 4)
+constexpr int kSfSlotCols = 48;        // per stage: 4 K-blocks x (tokens 4 + gate 4 + up 4)
+static_assert(kAccCols + kStages * kSfSlotCols <= kTmemCols, "TMEM budget");
 constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + 8192;
 
 template <int ACT>
@@ -52,7 +54,8 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
     uint64_t* empty_bar = full_bar + 8;
     uint64_t* acc_full = empty_bar + 8;
     uint64_t* acc_empty = acc_full + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    uint64_t* sf_ready = acc_empty + 1;  // [kStages] the three scale-factor copies of the stage are in tensor memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_ready + 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     int* prefix = reinterpret_cast<int*>(tail + 256);
 
@@ -65,6 +68,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
+            mbar_init(&sf_ready[s], 3);
         }
         mbar_init(acc_full, 1);
         mbar_init(acc_empty, 8);
@@ -120,27 +124,21 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
             constexpr uint32_t kStage16 = kStageBytes >> 4;
             const uint32_t a_lo0 = umma_desc_lo_sw128(smem_u32(smem));
             const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(smem + kABytes));
-            const uint32_t sf_lo0 = umma_desc_lo_sf(smem_u32(smem + kABytes + kBBytes));
-            uint32_t tile_n = 0, s = 0, ph = 0, slot = 0;
+            uint32_t tile_n = 0, s = 0, ph = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tile_n) {
                 if (!mbar_wait(acc_empty, (tile_n & 1u) ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
                 tc_fence_after();
                 XMOE_TRACE_STAMP(tile_n, 0);
                 for (int ks = 0; ks < k_stages; ++ks) {
-                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
+                    // operands landed (full_bar) and their scale factors are in tensor memory (sf_ready)
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
+                        !mbar_wait(&sf_ready[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t sf_lo = sf_lo0 + s * kStage16;
-                    const uint32_t sf_tmem = tmem_base + kAccCols + slot * kSfSlotCols;
-#pragma unroll
-                    for (int kb = 0; kb < 4; ++kb) {
-                        tmem_cp_sf_lo(sf_tmem + kb * 4, sf_lo + kb * 32);                                // tokens
-                        tmem_cp_sf_lo(sf_tmem + 16 + kb * 8, sf_lo + (kSfBytes >> 4) + kb * 32);         // gate
-                        tmem_cp_sf_lo(sf_tmem + 16 + kb * 8 + 4, sf_lo + 2 * (kSfBytes >> 4) + kb * 32); // up
-                    }
+                    const uint32_t sf_tmem = tmem_base + kAccCols + s * kSfSlotCols;
                     const uint32_t a_lo = a_lo0 + s * kStage16;
                     const uint32_t b_lo = b_lo0 + s * kStage16;
 #pragma unroll
@@ -150,10 +148,40 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
                     }
                     tc_commit(&empty_bar[s]);
                     if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
-                    slot ^= 1u;
                 }
                 if (ok) tc_commit(acc_full);
                 XMOE_TRACE_STAMP(tile_n, 1);
+            }
+        }
+    } else if (warp >= kFirstSfWarp) {
+        // Scale-factor copies, shared memory -> tensor memory, one thread per operand (tokens, gate
+        // rows, up rows). A thread issues at most one tcgen05 instruction per ~65 cycles; with the
+        // 12 copies of a stage on the MMA thread, issuing (not the tensor pipe, not L2) bounded the
+        // kernel at ~1240 cycles per stage. The copies of stage s may start as soon as its bytes have
+        // landed: full_bar[s] completing also means the MMAs that read the previous contents of this
+        // stage's tensor-memory columns have retired (the producer waited for them).
+        if (lane == 0) {
+            const int which = warp - kFirstSfWarp;  // 0 tokens, 1 gate, 2 up
+            constexpr uint32_t kStage16 = kStageBytes >> 4;
+            const uint32_t sf_lo0 = umma_desc_lo_sf(smem_u32(smem + kABytes + kBBytes)) + which * (kSfBytes >> 4);
+            const uint32_t col0 = which == 0 ? 0u : (which == 1 ? 16u : 20u);
+            const uint32_t col_step = which == 0 ? 4u : 8u;
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sf_lo = sf_lo0 + s * kStage16;
+                    const uint32_t sf_tmem = tmem_base + kAccCols + s * kSfSlotCols + col0;
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) tmem_cp_sf_lo(sf_tmem + kb * col_step, sf_lo + kb * 32);
+                    tc_commit(&sf_ready[s]);
+                    if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+                }
             }
         }
     } else {
