@@ -1,7 +1,7 @@
 // Helpers for kernels that run as clusters of two CTAs and issue 2-SM MMAs (tcgen05
 // cta_group::2): peer addressing, remote mbarrier arrives, cluster-scope bounded waits, paired
-// tensor-memory allocation and commits that target either CTA's barrier. No multicast is used:
-// every TMA load is a plain local load; commits name one barrier (one CTA) each.
+// tensor-memory allocation and commits that target either CTA's barrier (or, with an arrival
+// mask, the same barrier in both). No data is ever multicast: every TMA load is a plain local load.
 #pragma once
 
 #include "common.cuh"
@@ -49,6 +49,15 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols
 __device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
                  : "memory");
+}
+// Same, arriving on the barrier at the same shared-memory offset in every CTA of `cta_mask`
+// (bit i = CTA rank i of the cluster): one instruction instead of one commit per CTA. This is a
+// multicast of the ARRIVAL only; no data is multicast.
+__device__ __forceinline__ void tc_commit_pair_mask(uint32_t local_addr, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(local_addr), "h"(cta_mask)
+        : "memory");
 }
 // 2-SM block-scaled NVFP4 MMA: D (256 x N; 128 rows in each CTA's tensor memory) (+)= A (128 rows
 // from each CTA's shared memory) * B (N/2 rows from each CTA's shared memory, same offsets);

@@ -25,6 +25,16 @@
 
 namespace xmoe {
 
+#ifdef XMOE_TRACE
+// Debug build only: per-cluster cycle totals of where the leader's MMA thread waits.
+__device__ long long g_ff2p_trace[148 * 8];
+#define XMOE_T0() const long long t0__ = clock64()
+#define XMOE_TACC(var) var += clock64() - t0__
+#else
+#define XMOE_T0() do {} while (0)
+#define XMOE_TACC(var) do {} while (0)
+#endif
+
 namespace {
 
 constexpr int kBlockM = 128;             // weight rows per CTA
@@ -34,8 +44,8 @@ constexpr int kStageK = 128;             // one int4 group
 constexpr int kRawBytes = kBlockM * kStageK / 2;
 constexpr int kWStageBytes = kRawBytes + 512;
 constexpr int kBStageBytes = kTokHalf * kStageK * 2;   // 32 KiB: two 128-byte-swizzle slabs
-constexpr int kWStages = 12;
-constexpr int kBStages = 3;
+constexpr int kWStages = 5;
+constexpr int kBStages = 5;
 constexpr int kACols = kStageK / 2;      // 64
 constexpr int kARing = 4;
 constexpr int kDqGroups = 4;
@@ -120,8 +130,9 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
             mbar_init(&w_empty[s], 4);
         }
         for (int s = 0; s < kBStages; ++s) {
-            mbar_init(&b_full[s], 1);
-            mbar_init(&b_peer[s], 1);
+            // leader: its own TMA bytes + the peer's report that its half has landed
+            mbar_init(&b_full[s], leader ? 2 : 1);
+            mbar_init(&b_peer[s], 1);  // unused
             mbar_init(&b_empty[s], 1);
         }
         for (int s = 0; s < kARing; ++s) {
@@ -201,22 +212,32 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
             constexpr uint32_t idesc = umma_idesc_bf16(2 * kBlockM, kTokTile);
             constexpr int kSlab16 = (kTokHalf * 128) >> 4;
             const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(b_base));
-            const uint32_t peer_b_empty = map_to_cta(smem_u32(&b_empty[0]), 1);
-            const uint32_t peer_adq_empty = map_to_cta(smem_u32(&adq_empty[0]), 1);
-            const uint32_t peer_acc_full = map_to_cta(smem_u32(acc_full), 1);
             uint32_t tile_n = 0, s = 0, ph = 0, d = 0, dph = 0;
             bool ok = true;
+            long long tw_b = 0, tw_bp = 0, tw_adq = 0, tw_acc = 0, t_issue = 0;
+            (void)tw_b; (void)tw_bp; (void)tw_adq; (void)tw_acc; (void)t_issue;
+            const long long t_start = clock64();
+            (void)t_start;
             for (int item = cluster_id; item < total_tiles && ok; item += n_clusters, ++tile_n) {
-                if (!mbar_wait_cluster(acc_empty, (tile_n & 1u) ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
+                {
+                    XMOE_T0();
+                    if (!mbar_wait_cluster(acc_empty, (tile_n & 1u) ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
+                    XMOE_TACC(tw_acc);
+                }
                 tc_fence_after();
                 const uint32_t acc = tmem_base + kAccBase;
                 for (int ks = 0; ks < k_stages; ++ks) {
-                    if (!mbar_wait(&b_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
-                        !mbar_wait_cluster(&b_peer[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
-                        !mbar_wait_cluster(&adq_full[d], dph, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) {
-                        ok = false;
-                        break;
+                    {
+                        XMOE_T0();
+                        if (!mbar_wait(&b_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
+                        XMOE_TACC(tw_b);
                     }
+                    {
+                        XMOE_T0();
+                        if (!mbar_wait_cluster(&adq_full[d], dph, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
+                        XMOE_TACC(tw_adq);
+                    }
+                    XMOE_T0();
                     tc_fence_after();
                     const uint32_t a_tmem = tmem_base + d * kACols;
                     const uint32_t b_lo = b_lo0 + s * (uint32_t)(kBStageBytes >> 4);
@@ -225,22 +246,25 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
                         mma_bf16_ts_pair(acc, a_tmem + kk * 8, b_lo + (kk >> 2) * kSlab16 + (kk & 3) * 2, idesc,
                                          (ks | kk) ? 1u : 0u);
                     // release the token stage and the A buffer in both CTAs
-                    tc_commit_pair(smem_u32(&b_empty[s]));
-                    tc_commit_pair(peer_b_empty + s * 8u);
-                    tc_commit_pair(smem_u32(&adq_empty[d]));
-                    tc_commit_pair(peer_adq_empty + d * 8u);
+                    tc_commit_pair_mask(smem_u32(&b_empty[s]), 3);
+                    tc_commit_pair_mask(smem_u32(&adq_empty[d]), 3);
                     if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
                     if (++d == (uint32_t)kARing) { d = 0; dph ^= 1u; }
+                    XMOE_TACC(t_issue);
                 }
-                if (ok) {
-                    tc_commit_pair(smem_u32(acc_full));
-                    tc_commit_pair(peer_acc_full);
-                }
+                if (ok) tc_commit_pair_mask(smem_u32(acc_full), 3);
             }
+#ifdef XMOE_TRACE
+            if (cluster_id < 148) {
+                long long* o = g_ff2p_trace + cluster_id * 8;
+                o[0] = tw_b; o[1] = tw_bp; o[2] = tw_adq; o[3] = tw_acc; o[4] = t_issue; o[5] = clock64() - t_start;
+                o[6] = tile_n;
+            }
+#endif
         } else if (lane == 0) {
             // ------------------------------ relay (peer CTA) -------------------------
             // tells the leader when this CTA's half of a token stage has landed
-            const uint32_t leader_b_peer = map_to_cta(smem_u32(&b_peer[0]), 0);
+            const uint32_t leader_b_full = map_to_cta(smem_u32(&b_full[0]), 0);
             uint32_t s = 0, ph = 0;
             bool ok = true;
             for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
@@ -249,7 +273,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
                         ok = false;
                         break;
                     }
-                    mbar_arrive_cluster(leader_b_peer + s * 8u);
+                    mbar_arrive_cluster(leader_b_full + s * 8u);
                     if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -360,6 +384,12 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
 }
 
 }  // namespace
+
+#ifdef XMOE_TRACE
+extern "C" int xmoe_ff2_pair_trace_dump(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_ff2p_trace, sizeof(g_ff2p_trace));
+}
+#endif
 
 int launch_ff2_pair(const Ff2Args& a, cudaStream_t stream) {
     static bool attr_set = false;
