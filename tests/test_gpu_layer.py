@@ -136,12 +136,13 @@ def test_deterministic_run_to_run():
 
 
 def test_ff1_cta_pair_variant(monkeypatch):
-    # opt-in 2-SM (cta_group::2) FF1: must give the same rows as the default kernel, bit for bit
+    # 2-SM (cta_group::2) FF1, the default for prefill-sized experts, and the single-CTA kernel
+    # (XMOE_FF1_PAIR=0) must give the same rows, bit for bit
     shape = synth.scaled_shape(synth.SHAPES["mixtral"], hidden=512, inter=384, num_experts=4)
     _, layer, x, logits, y, ref, view = run_case(shape, 900)
     check_stages(shape, 900, y, ref, view)
     yact_default = view["yact"].clone()
-    monkeypatch.setenv("XMOE_FF1_PAIR", "1")
+    monkeypatch.setenv("XMOE_FF1_PAIR", "0")
     y2 = layer.forward(x.cuda(), logits.cuda())
     torch.cuda.synchronize()
     assert layer.status(900) == 0

@@ -191,10 +191,9 @@ int run_ff1(const void* w13_packed, const void* w13_sf, const float* w13_gs, con
     a.alpha = alpha;
     a.limit = limit;
     a.num_sms = num_sms();
-    // The CTA-pair variant (2-SM MMA, 256-token tiles) is correct but, as measured, slower than the
-    // single-CTA kernel (0.81 vs 0.66 ms on the Mixtral shape): it is opt-in with XMOE_FF1_PAIR=1.
+    // prefill-sized experts run 256-token tiles on CTA pairs unless XMOE_FF1_PAIR=0
     const char* pair_env = getenv("XMOE_FF1_PAIR");
-    const bool pair_enabled = pair_env && pair_env[0] == '1';
+    const bool pair_enabled = !(pair_env && pair_env[0] == '0');
     if (nt == 128 && pair_enabled && a.num_sms >= 2 && rows / (size_t)e_tot >= 320) return launch_ff1_pair(a, stream);
     return launch_ff1(a, stream);
 }

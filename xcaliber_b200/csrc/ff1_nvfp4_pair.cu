@@ -9,11 +9,17 @@
 // per SM halves (38 KB per 16.8 MFLOP).
 //
 // Scale factors: each CTA needs the token scales of its own rows and the weight scales of ALL 256
-// N rows in its tensor memory, so both CTAs load both (2 KB each per stage) and the leader issues
-// one cta_group::2 tcgen05.cp per tile that copies from each CTA's shared memory into that CTA's
-// tensor memory. Cross-CTA protocol as in ff2_w4a16_pair.cu: a relay thread in the peer reports
-// landed stages to the leader; the leader's commits release the stage / accumulator barriers of
-// both CTAs; both epilogues report to the leader. No multicast; every wait is bounded.
+// N rows in its tensor memory, so both CTAs load both (2 KB each per stage). Three threads of the
+// leader (tokens / gate / up) issue the cta_group::2 tcgen05.cp that copy from each CTA's shared
+// memory into that CTA's tensor memory; the MMA thread only waits, issues four MMAs and two commits
+// per stage (a thread issues one tcgen05 instruction per ~65 cycles: with the copies on the MMA
+// thread the kernel was issue-bound). Cross-CTA protocol: the peer's relay thread reports a landed
+// stage with a remote arrive on the leader's full barrier (count 2: own bytes + the report); the
+// leader's commits carry an arrival mask and release the stage / accumulator barriers of both
+// CTAs; both epilogues report to the leader. No data multicast; every wait is bounded.
+#include <cstdio>
+#include <cstdlib>
+
 #include "cluster.cuh"
 #include "common.cuh"
 #include "kernels.h"
@@ -33,10 +39,12 @@ constexpr int kABytes = kTokHalf * kStageKBytes;   // 16 KiB: my tokens
 constexpr int kBBytes = kWTile * kStageKBytes;     // 16 KiB: my half of the weight tile
 constexpr int kStageBytes = kABytes + kBBytes + 3 * kSfBytes;  // 38 KiB
 constexpr int kStages = 5;
-constexpr int kThreads = 320;          // producer, MMA / relay, 8 epilogue warps
+constexpr int kThreads = 416;          // producer, MMA / relay, 8 epilogue warps, 3 scale-factor copy warps
+constexpr int kFirstSfWarp = 10;
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = 256;
 constexpr int kSfSlotCols = 48;
+static_assert(kAccCols + kStages * kSfSlotCols <= kTmemCols, "TMEM budget");
 constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + 8192;
 
 template <int ACT>
@@ -45,8 +53,8 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_pair_kernel(const __gri
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* tail = smem + (size_t)kStages * kStageBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // [8] local: my stage landed
-    uint64_t* peer_full = full_bar + 8;                      // [8] leader: the peer's stage landed
-    uint64_t* empty_bar = peer_full + 8;                     // [8] each CTA: MMAs reading the stage retired
+    uint64_t* sf_ready = full_bar + 8;                       // [8] leader: the stage's scale factors are in both CTAs' tensor memory
+    uint64_t* empty_bar = sf_ready + 8;                      // [8] each CTA: MMAs reading the stage retired
     uint64_t* acc_full = empty_bar + 8;                      // [1] each CTA
     uint64_t* acc_empty = acc_full + 1;                      // [1] leader: 16 epilogue warps drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
@@ -64,8 +72,8 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_pair_kernel(const __gri
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&peer_full[s], 1);
+            mbar_init(&full_bar[s], leader ? 2 : 1);  // leader: own bytes + the peer's report that its stage landed
+            mbar_init(&sf_ready[s], 3);
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(acc_full, 1);
@@ -123,48 +131,33 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_pair_kernel(const __gri
             constexpr uint32_t kStage16 = kStageBytes >> 4;
             const uint32_t a_lo0 = umma_desc_lo_sw128(smem_u32(smem));
             const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(smem + kABytes));
-            const uint32_t sf_lo0 = umma_desc_lo_sf(smem_u32(smem + kABytes + kBBytes));
-            const uint32_t peer_empty = map_to_cta(smem_u32(&empty_bar[0]), 1);
-            const uint32_t peer_acc_full = map_to_cta(smem_u32(acc_full), 1);
-            uint32_t tile_n = 0, s = 0, ph = 0, slot = 0;
+            uint32_t tile_n = 0, s = 0, ph = 0;
             bool ok = true;
             for (int item = cluster_id; item < total_tiles && ok; item += n_clusters, ++tile_n) {
                 if (!mbar_wait_cluster(acc_empty, (tile_n & 1u) ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
                 tc_fence_after();
                 for (int ks = 0; ks < k_stages; ++ks) {
-                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
-                        !mbar_wait_cluster(&peer_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
+                    if (!mbar_wait_cluster(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
+                        !mbar_wait(&sf_ready[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t sf_lo = sf_lo0 + s * kStage16;
-                    const uint32_t sf_tmem = tmem_base + kAccCols + slot * kSfSlotCols;
-#pragma unroll
-                    for (int kb = 0; kb < 4; ++kb) {
-                        tmem_cp_sf_pair(sf_tmem + kb * 4, sf_lo + kb * 32);                                // my tokens
-                        tmem_cp_sf_pair(sf_tmem + 16 + kb * 8, sf_lo + (kSfBytes >> 4) + kb * 32);         // gate rows
-                        tmem_cp_sf_pair(sf_tmem + 16 + kb * 8 + 4, sf_lo + 2 * (kSfBytes >> 4) + kb * 32); // up rows
-                    }
+                    const uint32_t sf_tmem = tmem_base + kAccCols + s * kSfSlotCols;
                     const uint32_t a_lo = a_lo0 + s * kStage16;
                     const uint32_t b_lo = b_lo0 + s * kStage16;
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb)
                         mma_nvfp4_pair(tmem_base, a_lo + kb * 2, b_lo + kb * 2, idesc, sf_tmem + kb * 4,
                                        sf_tmem + 16 + kb * 8, (ks | kb) ? 1u : 0u);
-                    tc_commit_pair(smem_u32(&empty_bar[s]));
-                    tc_commit_pair(peer_empty + s * 8u);
+                    tc_commit_pair_mask(smem_u32(&empty_bar[s]), 3);
                     if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
-                    slot ^= 1u;
                 }
-                if (ok) {
-                    tc_commit_pair(smem_u32(acc_full));
-                    tc_commit_pair(peer_acc_full);
-                }
+                if (ok) tc_commit_pair_mask(smem_u32(acc_full), 3);
             }
         } else if (lane == 0) {
             // ---- relay (peer): report landed stages to the leader ----
-            const uint32_t leader_peer_full = map_to_cta(smem_u32(&peer_full[0]), 0);
+            const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[0]), 0);
             uint32_t s = 0, ph = 0;
             bool ok = true;
             for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
@@ -173,7 +166,35 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_pair_kernel(const __gri
                         ok = false;
                         break;
                     }
-                    mbar_arrive_cluster(leader_peer_full + s * 8u);
+                    mbar_arrive_cluster(leader_full + s * 8u);
+                    if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp >= kFirstSfWarp) {
+        // ---- scale-factor copies (leader): one thread per operand; a cta_group::2 copy moves each
+        // CTA's shared-memory tile into that CTA's tensor memory. A stage's copies may start once
+        // BOTH CTAs' bytes have landed (the leader's full barrier counts the peer's report).
+        if (lane == 0 && leader) {
+            const int which = warp - kFirstSfWarp;  // 0 my tokens, 1 gate rows, 2 up rows
+            constexpr uint32_t kStage16 = kStageBytes >> 4;
+            const uint32_t sf_lo0 = umma_desc_lo_sf(smem_u32(smem + kABytes + kBBytes)) + which * (kSfBytes >> 4);
+            const uint32_t col0 = which == 0 ? 0u : (which == 1 ? 16u : 20u);
+            const uint32_t col_step = which == 0 ? 4u : 8u;
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!mbar_wait_cluster(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sf_lo = sf_lo0 + s * kStage16;
+                    const uint32_t sf_tmem = tmem_base + kAccCols + s * kSfSlotCols + col0;
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) tmem_cp_sf_pair(sf_tmem + kb * col_step, sf_lo + kb * 32);
+                    tc_commit_pair(smem_u32(&sf_ready[s]));
                     if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -266,6 +287,9 @@ int launch_pair_act(const Ff1Args& a, cudaStream_t stream) {
         int n = 0;
         if (cudaOccupancyMaxActiveClusters(&n, ff1_nvfp4_pair_kernel<ACT>, &cfg) != cudaSuccess || n <= 0) n = a.num_sms / 2;
         resident_clusters = n < a.num_sms / 2 ? n : a.num_sms / 2;
+        if (getenv("XMOE_DEBUG"))
+            fprintf(stderr, "xmoe: ff1 pair kernel: %d resident clusters of 2 CTAs (occupancy query %d, %d SMs)\n",
+                    resident_clusters, n, a.num_sms);
     }
     cfg.gridDim = dim3((unsigned)(2 * resident_clusters), 1, 1);
     return cudaLaunchKernelEx(&cfg, ff1_nvfp4_pair_kernel<ACT>, a) == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;

@@ -18,6 +18,9 @@
 // Every wait is bounded; both CTAs meet at a cluster barrier before tensor memory is released.
 #include <cuda_bf16.h>
 
+#include <cstdio>
+#include <cstdlib>
+
 #include "cluster.cuh"
 #include "common.cuh"
 #include "kernels.h"
@@ -419,6 +422,7 @@ int launch_ff2_pair(const Ff2Args& a, cudaStream_t stream) {
         int n = 0;
         if (cudaOccupancyMaxActiveClusters(&n, ff2_w4a16_pair_kernel, &cfg) != cudaSuccess || n <= 0) n = a.num_sms / 2;
         resident_clusters = n < a.num_sms / 2 ? n : a.num_sms / 2;
+        if (getenv("XMOE_DEBUG")) fprintf(stderr, "xmoe: ff2 pair kernel: %d resident clusters of 2 CTAs (occupancy query %d, %d SMs)\n", resident_clusters, n, a.num_sms);
     }
     cfg.gridDim = dim3((unsigned)(2 * resident_clusters), 1, 1);
     return cudaLaunchKernelEx(&cfg, ff2_w4a16_pair_kernel, a) == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
