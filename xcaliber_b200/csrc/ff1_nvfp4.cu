@@ -33,7 +33,8 @@ constexpr int kBlockM = 128;          // weight rows per tile (per projection)
 constexpr int kStageKBytes = 128;     // packed bytes along K per stage = 256 K elements
 constexpr int kKPerStage = 256;
 constexpr int kSfStageBytes = 2048;   // 4 K-blocks of 64 x 512-byte scale tiles
-constexpr int kThreads = 192;         // producer warp, MMA warp, 4 epilogue warps
+constexpr int kThreads = 288;         // producer warp, MMA warp, 4 epilogue warps, 3 scale-factor copy warps
+constexpr int kFirstSfWarp = 6;
 constexpr int kMaxExperts = 1024 + 8;
 constexpr int kTmemCols = 512;
 
@@ -47,7 +48,7 @@ struct Ff1Cfg {
     static constexpr int kAccCols = 2 * NT;                 // gate + up
     static constexpr int kSfColsBase = kAccStages * kAccCols;
     static constexpr int kSfColsPerSlot = 48;               // 4 K-blocks x (gate 4 + up 4 + tokens 4)
-    static_assert(kSfColsBase + 2 * kSfColsPerSlot <= kTmemCols, "TMEM budget");
+    static_assert(kSfColsBase + kStages * kSfColsPerSlot <= kTmemCols, "TMEM budget");  // one slot per stage
     static constexpr int kTxBytes = kStageBytes;
     static constexpr size_t kSmemBytes = 1024 /*align slack*/ + (size_t)kStages * kStageBytes + 8192;
 };
@@ -106,7 +107,8 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
     uint64_t* empty_bar = full_bar + 8;                                 // [kStages]
     uint64_t* acc_full = empty_bar + 8;                                 // [2]
     uint64_t* acc_empty = acc_full + 2;                                 // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* sf_ready = acc_empty + 2;                                 // [kStages] scale factors of the stage are in tensor memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_ready + 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     int* prefix = reinterpret_cast<int*>(tail + 256);                   // [e_tot + 1]
 
@@ -119,6 +121,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
         for (int s = 0; s < Cfg::kStages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
+            mbar_init(&sf_ready[s], 3);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&acc_full[s], 1);
@@ -179,8 +182,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
             const uint32_t ag_lo0 = umma_desc_lo_sw128(smem_u32(stage_base));
             const uint32_t au_lo0 = umma_desc_lo_sw128(smem_u32(stage_base + Cfg::kABytes));
             const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(stage_base + 2 * Cfg::kABytes));
-            const uint32_t sf_lo0 = umma_desc_lo_sf(smem_u32(stage_base + 2 * Cfg::kABytes + Cfg::kBBytes));
-            uint32_t tile_n = 0, s = 0, ph = 0, slot = 0;
+            uint32_t tile_n = 0, s = 0, ph = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tile_n) {
                 const uint32_t as = tile_n % Cfg::kAccStages;
@@ -190,19 +192,13 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
                 const uint32_t acc_gate = tmem_base + as * Cfg::kAccCols;
                 const uint32_t acc_up = acc_gate + NT;
                 for (int ks = 0; ks < k_stages; ++ks) {
-                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
+                        !mbar_wait(&sf_ready[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t sf_lo = sf_lo0 + s * kStage16;
-                    const uint32_t sf_tmem = tmem_base + Cfg::kSfColsBase + slot * Cfg::kSfColsPerSlot;
-#pragma unroll
-                    for (int kb = 0; kb < 4; ++kb) {
-                        tmem_cp_sf_lo(sf_tmem + kb * 4, sf_lo + kb * 32);
-                        tmem_cp_sf_lo(sf_tmem + 16 + kb * 4, sf_lo + (kSfStageBytes >> 4) + kb * 32);
-                        tmem_cp_sf_lo(sf_tmem + 32 + kb * 4, sf_lo + 2 * (kSfStageBytes >> 4) + kb * 32);
-                    }
+                    const uint32_t sf_tmem = tmem_base + Cfg::kSfColsBase + s * Cfg::kSfColsPerSlot;
                     const uint32_t ag_lo = ag_lo0 + s * kStage16, au_lo = au_lo0 + s * kStage16;
                     const uint32_t b_lo = b_lo0 + s * kStage16;
 #pragma unroll
@@ -215,9 +211,38 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
                     }
                     tc_commit(&empty_bar[s]);
                     if (++s == (uint32_t)Cfg::kStages) { s = 0; ph ^= 1u; }
-                    slot ^= 1u;
                 }
                 if (ok) tc_commit(&acc_full[as]);
+            }
+        }
+    } else if (warp >= kFirstSfWarp) {
+        // ------------------------------ scale-factor copies ------------------------
+        // One thread per operand (gate rows, up rows, tokens) moves the stage's scale factors from
+        // shared to tensor memory. A thread issues one tcgen05 instruction per ~65 cycles: with these
+        // 12 copies on the MMA thread (21 instructions per 40 KB stage) issuing capped the kernel
+        // near 8 TB/s. full_bar[s] completing also means the MMAs that read the previous contents of
+        // this stage's tensor-memory columns have retired (the producer waited for them).
+        if (lane == 0) {
+            const int which = warp - kFirstSfWarp;  // 0 gate, 1 up, 2 tokens
+            constexpr uint32_t kStage16 = Cfg::kStageBytes >> 4;
+            const uint32_t sf_lo0 = umma_desc_lo_sf(smem_u32(stage_base + 2 * Cfg::kABytes + Cfg::kBBytes)) +
+                                    which * (kSfStageBytes >> 4);
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sf_lo = sf_lo0 + s * kStage16;
+                    const uint32_t sf_tmem = tmem_base + Cfg::kSfColsBase + s * Cfg::kSfColsPerSlot + which * 16;
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) tmem_cp_sf_lo(sf_tmem + kb * 4, sf_lo + kb * 32);
+                    tc_commit(&sf_ready[s]);
+                    if (++s == (uint32_t)Cfg::kStages) { s = 0; ph ^= 1u; }
+                }
             }
         }
     } else {
