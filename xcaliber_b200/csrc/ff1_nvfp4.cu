@@ -142,13 +142,15 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = prefix[a.E_tot];
+    const int tile_stride = balanced_stride(total_tiles, (int)gridDim.x);
+    const int first_tile = (int)blockIdx.x < tile_stride ? (int)blockIdx.x : total_tiles;  // CTAs beyond the stride idle
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+            for (int item = first_tile; item < total_tiles && ok; item += tile_stride) {
                 const TileInfo t = decode_tile(item, prefix, a.counts, a.offsets, a.E_tot, mt_tiles, NT);
                 const int gate_row = t.e * 2 * a.I + t.mt * kBlockM;
                 const int up_row = gate_row + a.I;
@@ -184,7 +186,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
             const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(stage_base + 2 * Cfg::kABytes));
             uint32_t tile_n = 0, s = 0, ph = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tile_n) {
+            for (int item = first_tile; item < total_tiles && ok; item += tile_stride, ++tile_n) {
                 const uint32_t as = tile_n % Cfg::kAccStages;
                 const uint32_t aph = (tile_n / Cfg::kAccStages) & 1u;
                 if (!mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
@@ -229,7 +231,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
                                     which * (kSfStageBytes >> 4);
             uint32_t s = 0, ph = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+            for (int item = first_tile; item < total_tiles && ok; item += tile_stride) {
                 for (int ks = 0; ks < k_stages; ++ks) {
                     if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
                         ok = false;
@@ -252,7 +254,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
         uint32_t tile_n = 0;
         uint16_t* yact = reinterpret_cast<uint16_t*>(a.yact);
         const uint16_t* row_w = reinterpret_cast<const uint16_t*>(a.row_weight);
-        for (int item = blockIdx.x; item < total_tiles; item += gridDim.x, ++tile_n) {
+        for (int item = first_tile; item < total_tiles; item += tile_stride, ++tile_n) {
             const TileInfo t = decode_tile(item, prefix, a.counts, a.offsets, a.E_tot, mt_tiles, NT);
             const uint32_t as = tile_n % Cfg::kAccStages;
             const uint32_t aph = (tile_n / Cfg::kAccStages) & 1u;

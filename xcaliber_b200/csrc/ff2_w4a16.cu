@@ -183,6 +183,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = prefix[a.E_tot];
+    const int tile_stride = balanced_stride(total_tiles, (int)gridDim.x);
+    const int first_tile = (int)blockIdx.x < tile_stride ? (int)blockIdx.x : total_tiles;  // CTAs beyond the stride idle
 
     if (warp == 0) {
         // ------------------------------ weight producer ---------------------------
@@ -192,7 +194,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             bool ok = true;
             long long tw_prod = 0;
             (void)tw_prod;
-            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+            for (int item = first_tile; item < total_tiles && ok; item += tile_stride) {
                 const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
                 const int h0 = t.wt * kBlockM;
                 const int w_row = t.e * a.H + h0;
@@ -227,7 +229,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             bool ok = true;
             long long tw_bprod = 0;
             (void)tw_bprod;
-            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+            for (int item = first_tile; item < total_tiles && ok; item += tile_stride) {
                 const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
                 // Few tokens in the tile (decode): fetch only 8 or 16 rows. The token tile comes
                 // from L2 at the same bytes per K as the weights do from HBM, and the L2 -> SM
@@ -273,7 +275,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             bool ok = true;
             long long tw_full = 0, tw_adq = 0, tw_acc = 0, t_issue = 0;
             (void)tw_full; (void)tw_adq; (void)tw_acc; (void)t_issue;
-            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tile_n) {
+            for (int item = first_tile; item < total_tiles && ok; item += tile_stride, ++tile_n) {
                 const uint32_t as = tile_n % kAccStages;
                 const uint32_t aph = (tile_n / kAccStages) & 1u;
                 {
@@ -328,7 +330,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         uint32_t tile_n = 0;
         uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
         uint16_t* tp = transpose + q * 1024;  // this warp's 32 tokens x 32 features
-        for (int item = blockIdx.x; item < total_tiles; item += gridDim.x, ++tile_n) {
+        for (int item = first_tile; item < total_tiles; item += tile_stride, ++tile_n) {
             const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
             const uint32_t as = tile_n % kAccStages;
             const uint32_t aph = (tile_n / kAccStages) & 1u;
@@ -400,7 +402,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         bool ok = true;
         long long dq_wfull = 0, dq_wempty = 0, dq_work = 0;  // dq_work includes the wait for the slot
         (void)dq_wfull; (void)dq_wempty; (void)dq_work;
-        for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+        for (int item = first_tile; item < total_tiles && ok; item += tile_stride) {
             for (int ks = 0; ks < k_stages; ++ks, ++it) {
                 if ((int)(it % kDqGroups) != group) continue;
                 const uint32_t w_it = w_tile_base + (uint32_t)(ks / Cfg::kWUnits);

@@ -99,6 +99,17 @@ __device__ __forceinline__ float glu_apply(int act, float g_acc, float u_acc, fl
     return __fmul_rn(__fmul_rn(g, u_w), rcp_approx(__fadd_rn(1.0f, e)));
 }
 
+// Persistent kernels walk the tile list with a stride. Striding by the grid size leaves the
+// last round mostly idle when the tile count is a little above a multiple of it (896 tiles on 148
+// CTAs: six full rounds and one of 8 tiles). With the same number of rounds, the smallest stride
+// that covers the list spreads the tiles evenly (896 -> 7 rounds of 128): in a bandwidth-bound
+// kernel every round then moves data at full rate. CTAs beyond the stride have no tiles.
+__device__ __forceinline__ int balanced_stride(int total_tiles, int grid) {
+    if (total_tiles <= 0) return grid;
+    const int rounds = (total_tiles + grid - 1) / grid;
+    return (total_tiles + rounds - 1) / rounds;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
