@@ -107,6 +107,14 @@ int xmoe_read_status(const void* workspace, uint32_t* host_out, xmoe_stream_t st
 int xmoe_forward_routed(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const int32_t* topk_idx,
                         const void* topk_w, const float* act_scale, int32_t n_tokens, void* y, void* workspace,
                         size_t workspace_bytes, xmoe_stream_t stream);
+/* Same for a buffer of n_tokens rows of which only the first *n_valid_dev (device int32, may be
+ * NULL) are in use: the others must carry expert id -1 and are not scanned by the quantiser.
+ * y may be NULL here and above: the combine is skipped and the FF2 rows stay in the workspace.
+ * No reference counterpart (used by the expert-parallel receive path). */
+int xmoe_forward_routed_bounded(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const int32_t* topk_idx,
+                                const void* topk_w, const float* act_scale, int32_t n_tokens,
+                                const int32_t* n_valid_dev, void* y, void* workspace, size_t workspace_bytes,
+                                xmoe_stream_t stream);
 
 /* Per-stage device timing of xmoe_forward* calls, the counterpart of the reference harness's
  * per-kernel timing (sm120a/benchmarks/benchmark.cu:381-399). begin(max_steps > 0) makes every

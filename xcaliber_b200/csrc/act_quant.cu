@@ -120,9 +120,10 @@ __device__ __forceinline__ uint32_t e2m1x2(uint32_t x2, uint32_t scale2) {
 __global__ __launch_bounds__(256) void act_quant_pack_kernel(
     const uint16_t* __restrict__ x, const ActScale* __restrict__ scale, const int32_t* __restrict__ topk_row,
     int N, int H, int k_eff, int idx_stride, uint8_t* __restrict__ xq, uint8_t* __restrict__ sfx, int kb_pad,
-    int units_per_token, int nt) {
+    int units_per_token, int nt, const int32_t* __restrict__ n_valid) {
     const float xgs = scale->xgs;
     const uint32_t lane = lane_id();
+    if (n_valid) N = min(N, max(*n_valid, 0));
     const size_t total_units = (size_t)N * units_per_token;
     const int h_pad = kb_pad * 64;
     for (size_t unit = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5); unit < total_units;
@@ -189,7 +190,7 @@ int launch_act_quant(const QuantArgs& a, cudaStream_t stream) {
     if (blocks > 148 * 16) blocks = 148 * 16;
     act_quant_pack_kernel<<<(int)blocks, 256, 0, stream>>>((const uint16_t*)a.x, a.scale, a.topk_row, a.N, a.H,
                                                            a.k_eff, a.idx_stride, (uint8_t*)a.xq, (uint8_t*)a.sfx,
-                                                           a.kb_pad, units_per_token, a.nt);
+                                                           a.kb_pad, units_per_token, a.nt, a.n_valid);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 

@@ -244,7 +244,7 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
 
 int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* logits,
                  const int32_t* ext_idx, const void* ext_w, const float* ext_scale, int n, void* y, void* ws,
-                 size_t ws_bytes, cudaStream_t stream) {
+                 size_t ws_bytes, cudaStream_t stream, const int32_t* n_valid_dev = nullptr) {
     int rc = check_cfg(cfg);
     if (rc) return rc;
     if (n < 0) return XMOE_ERR_ARG;
@@ -273,7 +273,12 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
 
     if (ext_idx) {
         // caller-supplied routing: widen [N, top_k] to the [N, k_eff] workspace arrays
-        if (cudaMemcpy2DAsync(topk_idx, (size_t)L.k_eff * 4, ext_idx, (size_t)cfg->top_k * 4, (size_t)cfg->top_k * 4, n,
+        if (L.k_eff == cfg->top_k) {  // same row pitch: one flat copy each (a pitched copy of 4-byte rows is slow)
+            if (cudaMemcpyAsync(topk_idx, ext_idx, (size_t)n * L.k_eff * 4, cudaMemcpyDeviceToDevice, stream) !=
+                    cudaSuccess ||
+                cudaMemcpyAsync(topk_w, ext_w, (size_t)n * L.k_eff * 2, cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+                return XMOE_ERR_CUDA;
+        } else if (cudaMemcpy2DAsync(topk_idx, (size_t)L.k_eff * 4, ext_idx, (size_t)cfg->top_k * 4, (size_t)cfg->top_k * 4, n,
                               cudaMemcpyDeviceToDevice, stream) != cudaSuccess ||
             cudaMemcpy2DAsync(topk_w, (size_t)L.k_eff * 2, ext_w, (size_t)cfg->top_k * 2, (size_t)cfg->top_k * 2, n,
                               cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
@@ -343,6 +348,7 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     q.sfx = b + L.off_sfx;
     q.kb_pad = L.kb_pad;
     q.nt = L.nt;
+    q.n_valid = n_valid_dev;
     if ((rc = launch_act_quant(q, stream))) return rc;
     prof_mark(4, stream);
 
@@ -430,6 +436,14 @@ int xmoe_forward_routed(const xmoe_config* cfg, const xmoe_weights* w, const voi
     if (!topk_idx || !topk_w) return XMOE_ERR_ARG;
     return forward_impl(cfg, w, x, nullptr, topk_idx, topk_w, act_scale, n, y, workspace, workspace_bytes,
                         (cudaStream_t)stream);
+}
+
+int xmoe_forward_routed_bounded(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const int32_t* topk_idx,
+                                const void* topk_w, const float* act_scale, int32_t n, const int32_t* n_valid_dev, void* y,
+                                void* workspace, size_t workspace_bytes, xmoe_stream_t stream) {
+    if (!topk_idx || !topk_w) return XMOE_ERR_ARG;
+    return forward_impl(cfg, w, x, nullptr, topk_idx, topk_w, act_scale, n, y, workspace, workspace_bytes,
+                        (cudaStream_t)stream, n_valid_dev);
 }
 
 int xmoe_profile_begin(int32_t max_steps) {
@@ -643,6 +657,7 @@ int xmoe_act_quant_pack(const void* x, const float* act_scale, const int32_t* to
     q.sfx = sfx;
     q.kb_pad = (int)align_up((size_t)H / 64, 4);
     q.nt = token_tile;
+    q.n_valid = nullptr;
     return launch_act_quant(q, (cudaStream_t)stream);
 }
 

@@ -61,6 +61,7 @@ struct QuantArgs {
     void* sfx;  // u8 [R_cap/nt, KB, 512]
     int kb_pad; // K blocks of 64 per row, rounded up to a multiple of 4
     int nt;     // token tile the scale-factor tiles are laid out for: 32, 64 or 128
+    const int32_t* n_valid;  // optional, device: tokens at and beyond *n_valid have no rows and are not scanned
 };
 
 struct Ff1Args {

@@ -311,7 +311,7 @@ class ExpertParallelMoE:
         _lib.check(lib.xmoe_ep_wait_data(px.ref, px.e_recv.data_ptr(), px.w_recv.data_ptr(), px.n_recv.data_ptr(), st),
                    "xmoe_ep_wait_data")
         tile, local = self._local_layer(n)
-        local.forward_routed_rows(px.recv_x, px.e_recv, px.w_recv, act_scale=self._scale)
+        local.forward_routed_rows(px.recv_x, px.e_recv, px.w_recv, act_scale=self._scale, n_valid=px.n_recv)
         ptrs = self._local_ptrs.get(tile)
         if ptrs is None:
             v = local.view(px.cap_rows)

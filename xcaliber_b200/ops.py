@@ -196,20 +196,21 @@ class FusedMoE:
         return y
 
     def forward_routed_rows(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
-                            act_scale: torch.Tensor | None = None) -> None:
+                            act_scale: torch.Tensor | None = None, n_valid: torch.Tensor | None = None) -> None:
         """forward_routed without the final combine: the FF2 rows stay in the workspace
         (view(n)["out_rows"], indexed by view(n)["topk_row"]). topk_idx / topk_w must already be
-        int32 / bf16 and contiguous; an expert id of -1 marks a slot that is not in use."""
+        int32 / bf16 and contiguous; an expert id of -1 marks a slot that is not in use. n_valid
+        (device int32 [1], optional): only the first n_valid rows are in use."""
         n = x.shape[0]
         if n == 0:
             return
         if topk_idx.dtype != torch.int32 or topk_w.dtype != torch.bfloat16:
             raise TypeError("topk_idx must be int32 and topk_w bf16")
         ws = self.workspace(n)
-        check(_lib.lib().xmoe_forward_routed(C.byref(self.cfg), C.byref(self._wstruct), x.data_ptr(),
-                                             topk_idx.data_ptr(), topk_w.data_ptr(), _ptr(act_scale), n, None,
-                                             ws.data_ptr(), ws.numel(), _stream()),
-              "xmoe_forward_routed")
+        check(_lib.lib().xmoe_forward_routed_bounded(C.byref(self.cfg), C.byref(self._wstruct), x.data_ptr(),
+                                                     topk_idx.data_ptr(), topk_w.data_ptr(), _ptr(act_scale), n,
+                                                     _ptr(n_valid), None, ws.data_ptr(), ws.numel(), _stream()),
+              "xmoe_forward_routed_bounded")
 
     def forward_host(self, x_host: torch.Tensor, logits_host: torch.Tensor, y_host: torch.Tensor) -> torch.Tensor:
         """Host (pinned) buffers in and out; copies and the stream sync happen inside the C call."""
