@@ -20,13 +20,31 @@ __global__ __launch_bounds__(256) void act_amax_kernel(const uint4* __restrict__
                                                        const uint16_t* __restrict__ tail, int n_tail,
                                                        uint32_t* __restrict__ scratch, ActScale* __restrict__ scale) {
     __shared__ uint32_t warp_max[8];
-    uint32_t mx = 0u;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
-        const uint4 v = x[i];
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    // magnitudes of two bf16 at a time (packed unsigned 16-bit max); four independent 16-byte loads
+    // in flight per thread
+    uint32_t mx2 = 0u;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < n_vec; i += 4 * stride) {
+        uint4 v[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) mx = max(mx, max(w[j] & 0x7fffu, (w[j] >> 16) & 0x7fffu));
+        for (int u = 0; u < 4; ++u) v[u] = x[i + u * stride];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            mx2 = __vmaxu2(mx2, v[u].x & 0x7fff7fffu);
+            mx2 = __vmaxu2(mx2, v[u].y & 0x7fff7fffu);
+            mx2 = __vmaxu2(mx2, v[u].z & 0x7fff7fffu);
+            mx2 = __vmaxu2(mx2, v[u].w & 0x7fff7fffu);
+        }
     }
+    for (; i < n_vec; i += stride) {
+        const uint4 v = x[i];
+        mx2 = __vmaxu2(mx2, v.x & 0x7fff7fffu);
+        mx2 = __vmaxu2(mx2, v.y & 0x7fff7fffu);
+        mx2 = __vmaxu2(mx2, v.z & 0x7fff7fffu);
+        mx2 = __vmaxu2(mx2, v.w & 0x7fff7fffu);
+    }
+    uint32_t mx = max(mx2 & 0xffffu, mx2 >> 16);
     if (blockIdx.x == 0 && (int)threadIdx.x < n_tail) mx = max(mx, (uint32_t)tail[threadIdx.x] & 0x7fffu);
     mx = __reduce_max_sync(0xffffffffu, mx);
     if (lane_id() == 0) warp_max[threadIdx.x >> 5] = mx;
