@@ -328,6 +328,15 @@ def main() -> int:
         if tr is not None:
             roofline["traffic"] = tr
     ff1_ms, ff2_ms = per_stage.get("ff1", 0.0), per_stage.get("ff2", 0.0)
+    # the tensor-pipe ceiling for NVFP4 as this GPU delivers it (resident operands, no data movement):
+    # there is no library GEMM to take an NVFP4 peak from
+    mma_probe = {}
+    if world == 1 and rank == 0:
+        try:
+            mma_probe = {"nvfp4_mma_tflops_measured": ops.probe_mma_rate("nvfp4", 262144),
+                         "bf16_mma_tflops_measured": ops.probe_mma_rate("bf16", 262144)}
+        except Exception as exc:  # the probe is an aid; the bench line stands without it
+            mma_probe = {"mma_probe_error": str(exc)}
     extra = {
         "stage_ms": {k: round(v, 5) for k, v in per_stage.items()},
         "ff1_tflops": flops_ff1 / (ff1_ms * 1e-3) / 1e12 if ff1_ms else None,
@@ -335,7 +344,10 @@ def main() -> int:
         "ff2_tflops": flops_ff2 / (ff2_ms * 1e-3) / 1e12 if ff2_ms else None,
         "ff2_frac_of_bf16_sustained": flops_ff2 / (ff2_ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"] if ff2_ms else None,
         "layer_useful_tflops": synth.algorithmic_flops(shape, n) / (ms_step * 1e-3) / 1e12,
+        **mma_probe,
     }
+    if ff1_ms and mma_probe.get("nvfp4_mma_tflops_measured"):
+        extra["ff1_frac_of_measured_nvfp4_mma_rate"] = extra["ff1_tflops"] / mma_probe["nvfp4_mma_tflops_measured"]
 
     # ---- decode point of the same layer (N = 16 per GPU), CUDA-graph replay, HBM roofline
     decode = None

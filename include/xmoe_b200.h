@@ -276,6 +276,13 @@ int xmoe_ep_wait_ret(const xmoe_ep_buffers* b, xmoe_stream_t stream);
 /* Synchronises the stream and returns the sticky XMOE_EP_* bits of this rank's control block (0 = fine). */
 int xmoe_ep_status(const xmoe_ep_buffers* b, xmoe_stream_t stream, uint32_t* bits_out);
 
+/* Measurement aid, no reference counterpart: the rate at which this GPU retires tcgen05.mma
+ * instructions of the largest shape (M 128, N 256) with operands resident on chip, one issuing
+ * thread per SM, n_mma instructions each (rounded down to a multiple of 64; ~100000 runs for a
+ * few milliseconds). kind 0 = NVFP4 block-scaled (K 64), 1 = bf16 (K 16). Writes dense TFLOP/s
+ * of the whole GPU to *tflops_out; synchronises the stream; allocates 4 bytes for the call. */
+int xmoe_probe_mma_rate(int32_t kind, int32_t n_mma, double* tflops_out, xmoe_stream_t stream);
+
 /* Host helper: the 65536-entry sigmoid table indexed by bf16 bit pattern. */
 void xmoe_fill_sigmoid_lut(float* host_out);
 

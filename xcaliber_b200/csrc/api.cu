@@ -446,6 +446,10 @@ int xmoe_forward_routed_bounded(const xmoe_config* cfg, const xmoe_weights* w, c
                         (cudaStream_t)stream, n_valid_dev);
 }
 
+int xmoe_probe_mma_rate(int32_t kind, int32_t n_mma, double* tflops_out, xmoe_stream_t stream) {
+    return probe_mma_rate(kind, n_mma, tflops_out, (cudaStream_t)stream);
+}
+
 int xmoe_profile_begin(int32_t max_steps) {
     if (g_prof.ev) {
         for (size_t i = 0; i < (size_t)g_prof.max_steps * (kProfStages + 1); ++i) cudaEventDestroy(g_prof.ev[i]);

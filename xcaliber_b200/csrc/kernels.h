@@ -141,6 +141,7 @@ int launch_ep_wait_data(const xmoe_ep_buffers* b, int32_t* e_recv, void* w_recv,
 int launch_ep_return(const xmoe_ep_buffers* b, const void* out_rows, const int32_t* topk_row, int expected_rows,
                      cudaStream_t stream);
 int launch_ep_wait_ret(const xmoe_ep_buffers* b, cudaStream_t stream);
+int probe_mma_rate(int kind, int n_mma, double* tflops_out, cudaStream_t stream);
 int launch_repack_kmajor_int4(const void* w_in, void* out, size_t n_words, cudaStream_t stream);
 
 }  // namespace xmoe

@@ -277,6 +277,15 @@ def combine(rows: torch.Tensor, topk_row: torch.Tensor, out: torch.Tensor | None
 STAGE_NAMES = ("router", "route_pack", "act_amax", "act_quant", "ff1", "act_topk", "ff2", "combine")
 
 
+def probe_mma_rate(kind: str = "nvfp4", n_mma: int = 65536) -> float:
+    """Dense TFLOP/s at which the GPU retires resident-operand tcgen05.mma instructions (M 128, N 256):
+    the tensor-pipe ceiling used as a roofline denominator where no library GEMM exists (NVFP4)."""
+    out = C.c_double(0.0)
+    check(_lib.lib().xmoe_probe_mma_rate({"nvfp4": 0, "bf16": 1}[kind], n_mma, C.byref(out), _stream()),
+          "xmoe_probe_mma_rate")
+    return out.value
+
+
 def profile_begin(max_steps: int) -> None:
     check(_lib.lib().xmoe_profile_begin(max_steps), "xmoe_profile_begin")
 
