@@ -240,7 +240,7 @@ int xmoe_repack_int4_kmajor(const void* w_in, void* out, size_t n_words, xmoe_st
  * four buffers below, the other ranks map them (CUDA IPC / symmetric memory; the library takes plain
  * device pointers and never opens a handle itself), and the same call sequence runs on every rank's
  * stream with no host synchronisation:
- *   xmoe_ep_post_counts -> xmoe_ep_dispatch -> xmoe_ep_wait_data -> xmoe_forward_routed (y = NULL, n =
+ *   xmoe_ep_post_counts -> xmoe_ep_dispatch -> xmoe_ep_wait_data -> xmoe_forward_routed_bounded (y = NULL, n =
  *   cap_rows, top_k = 1, on recv_x[rank]) -> xmoe_ep_return -> xmoe_ep_wait_ret -> xmoe_combine on
  *   ret_rows[rank]. All device-side waits are bounded; xmoe_ep_status reports what went wrong. */
 #define XMOE_EP_MAX_WORLD 8

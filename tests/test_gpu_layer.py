@@ -158,3 +158,35 @@ def test_long_k_prefill_uses_wide_ff2_tile():
     _, _, _, _, y, ref, view = run_case(shape, 700)
     assert view["token_tile"] == 128
     check_stages(shape, 700, y, ref, view)
+
+
+def test_routed_rows_with_unused_slots_and_row_bound():
+    # the expert-parallel receive path: a buffer of cap rows, the first m in use, expert id -1 beyond;
+    # rows-only output must equal the routed forward on the m rows alone
+    shape = synth.scaled_shape(synth.SHAPES["toy"], top_k=1, num_shared_experts=0)
+    w, layer = Hh.build_layer(shape, token_tile=32)  # same tile for both calls: same summation order
+    m, cap = 70, 256
+    x, _ = synth.make_inputs(shape, w, cap)
+    g = torch.Generator().manual_seed(3)
+    idx = torch.randint(0, shape.num_experts, (cap, 1), generator=g, dtype=torch.int32)
+    idx[m:] = -1
+    gate = torch.rand(cap, 1, generator=g).to(torch.bfloat16)
+    xd, idxd, gd = x.cuda(), idx.cuda(), gate.cuda()
+    y_ref = layer.forward_routed(xd[:m], idxd[:m], gd[:m])
+    scale = layer.view(m)["act_scale"].clone()
+    n_valid = torch.tensor([m], dtype=torch.int32, device="cuda")
+    layer.forward_routed_rows(xd, idxd, gd, act_scale=scale, n_valid=n_valid)
+    torch.cuda.synchronize()
+    assert layer.status(cap) == 0
+    v = layer.view(cap)
+    rows = v["topk_row"][:m, 0].long()
+    assert (v["topk_row"][m:, 0] == -1).all()
+    assert torch.equal(v["out_rows"][rows], y_ref)
+
+
+def test_tensor_pipe_probe_reports_plausible_rates():
+    from xcaliber_b200 import ops
+    nv = ops.probe_mma_rate("nvfp4", 65536)
+    bf = ops.probe_mma_rate("bf16", 65536)
+    # B200 nominal dense rates are 9000 / 2250 TFLOP/s; the probe must land in that neighbourhood
+    assert 4000 < nv < 10000 and 1000 < bf < 2600 and 3.0 < nv / bf < 5.0, (nv, bf)

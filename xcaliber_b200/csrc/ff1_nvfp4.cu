@@ -53,49 +53,6 @@ struct Ff1Cfg {
     static constexpr size_t kSmemBytes = 1024 /*align slack*/ + (size_t)kStages * kStageBytes + 8192;
 };
 
-struct TileInfo {
-    int e, mt, nt_idx, count, row0;
-};
-
-// prefix[e] = number of tiles of experts < e; built once per CTA in shared memory.
-__device__ __forceinline__ void build_tile_prefix(int* prefix, const int32_t* counts, int e_tot, int mt_tiles, int NT) {
-    // one warp, 32 experts per step with a running carry
-    const int lane = threadIdx.x & 31;
-    int carry = 0;
-    for (int base = 0; base < e_tot; base += 32) {
-        const int e = base + lane;
-        const int v = e < e_tot ? ((counts[e] + NT - 1) / NT) * mt_tiles : 0;
-        int incl = v;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const int o = __shfl_up_sync(0xffffffffu, incl, d);
-            if (lane >= d) incl += o;
-        }
-        if (e < e_tot) prefix[e] = carry + incl - v;
-        carry += __shfl_sync(0xffffffffu, incl, 31);
-    }
-    if (lane == 0) prefix[e_tot] = carry;
-}
-
-__device__ __forceinline__ TileInfo decode_tile(int item, const int* prefix, const int32_t* counts,
-                                                const int32_t* offsets, int e_tot, int mt_tiles, int NT) {
-    int lo = 0, hi = e_tot;  // largest e with prefix[e] <= item
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (prefix[mid] <= item) lo = mid; else hi = mid;
-    }
-    TileInfo t;
-    t.e = lo;
-    const int local = item - prefix[lo];
-    t.count = counts[lo];
-    const int n_tiles = (t.count + NT - 1) / NT;
-    // token tiles innermost: CTAs of one wave share the weight tile through L2
-    t.mt = local / n_tiles;
-    t.nt_idx = local % n_tiles;
-    t.row0 = offsets[lo] + t.nt_idx * NT;
-    return t;
-}
-
 template <int NT>
 __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_constant__ Ff1Args a) {
     using Cfg = Ff1Cfg<NT>;
@@ -136,7 +93,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
-    if (warp == 2) build_tile_prefix(prefix, a.counts, a.E_tot, mt_tiles, NT);
+    if (warp == 2) tile_prefix_build(prefix, a.counts, a.E_tot, mt_tiles, NT);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -151,11 +108,11 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
             uint32_t it = 0;
             bool ok = true;
             for (int item = first_tile; item < total_tiles && ok; item += tile_stride) {
-                const TileInfo t = decode_tile(item, prefix, a.counts, a.offsets, a.E_tot, mt_tiles, NT);
-                const int gate_row = t.e * 2 * a.I + t.mt * kBlockM;
+                const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
+                const int gate_row = t.e * 2 * a.I + t.wt * kBlockM;
                 const int up_row = gate_row + a.I;
-                const uint8_t* sfw_g = a.sfw + ((size_t)(t.e * 2 + 0) * a.mb + t.mt) * a.kb_pad * 512;
-                const uint8_t* sfw_u = a.sfw + ((size_t)(t.e * 2 + 1) * a.mb + t.mt) * a.kb_pad * 512;
+                const uint8_t* sfw_g = a.sfw + ((size_t)(t.e * 2 + 0) * a.mb + t.wt) * a.kb_pad * 512;
+                const uint8_t* sfw_u = a.sfw + ((size_t)(t.e * 2 + 1) * a.mb + t.wt) * a.kb_pad * 512;
                 const uint8_t* sfx = a.sfx + (size_t)(t.row0 / NT) * a.kb_pad * 512;
                 for (int ks = 0; ks < k_stages; ++ks, ++it) {
                     const int s = it % Cfg::kStages;
@@ -255,14 +212,14 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
         uint16_t* yact = reinterpret_cast<uint16_t*>(a.yact);
         const uint16_t* row_w = reinterpret_cast<const uint16_t*>(a.row_weight);
         for (int item = first_tile; item < total_tiles; item += tile_stride, ++tile_n) {
-            const TileInfo t = decode_tile(item, prefix, a.counts, a.offsets, a.E_tot, mt_tiles, NT);
+            const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
             const uint32_t as = tile_n % Cfg::kAccStages;
             const uint32_t aph = (tile_n / Cfg::kAccStages) & 1u;
             if (!mbar_wait(&acc_full[as], aph, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
             tc_fence_after();
             const float sg = __fmul_rn(a.w13_gs[t.e * 2 + 0], xgs_inv);
             const float su = __fmul_rn(a.w13_gs[t.e * 2 + 1], xgs_inv);
-            const int i_idx = t.mt * kBlockM + q * 32 + lane;
+            const int i_idx = t.wt * kBlockM + q * 32 + lane;
             const bool i_ok = i_idx < a.I;
             const int n_valid = min(NT, t.count - t.nt_idx * NT);
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + as * Cfg::kAccCols;

@@ -52,25 +52,9 @@ __device__ __forceinline__ TileInfo tile_decode(int item, const int* prefix, con
     return t;
 }
 
-// activation 0: silu(g)*u; 1: clamped SwiGLU (min(g,limit) * sigmoid(alpha*g)) * (clamp(u)+1);
-// 2: tanh-GELU(g)*u. fp32 with the approximate ex2 / rcp units, like the reference epilogue
-// (xR64FF1.cu:356-386).
-__device__ __forceinline__ float glu_act(float g, float u, int activation, float alpha, float limit) {
-    if (activation == 1) {
-        g = fminf(g, limit);
-        u = fminf(fmaxf(u, -limit), limit);
-        const float s = rcp_approx(1.0f + ex2_approx(-alpha * g * 1.4426950408889634f));
-        return g * s * (u + 1.0f);
-    }
-    if (activation == 2) {
-        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
-        const float t = 1.0f - 2.0f * rcp_approx(1.0f + ex2_approx(2.0f * inner * 1.4426950408889634f));
-        return 0.5f * g * (1.0f + t) * u;
-    }
-    return g * u * rcp_approx(1.0f + ex2_approx(-g * 1.4426950408889634f));
-}
-
-// The one GLU epilogue both FF1 kernels use. g_acc / u_acc are the raw fp32 accumulators, sg the
+// The one GLU epilogue all FF1 kernels use (activation 0: silu(g)*u; 1: clamped SwiGLU
+// (min(g,limit) * sigmoid(alpha*g)) * (clamp(u)+1); 2: tanh-GELU(g)*u; fp32 with the approximate ex2 /
+// rcp units, like the reference epilogue, xR64FF1.cu:356-386). g_acc / u_acc are the raw fp32 accumulators, sg the
 // gate scale (weight_global_scale * XGSINV), su_w the up scale times the routing weight, w the
 // routing weight (needed on its own only where the activation adds a constant to u). Every
 // operation is an explicit round-to-nearest intrinsic so that the compiler cannot contract or
