@@ -61,6 +61,12 @@ constexpr size_t kSmemBytes = 1024 + (size_t)kBStages * kBStageBytes + (size_t)k
 static_assert(kSmemBytes <= 232448, "shared memory");
 static_assert(kAccBase + kTokTile <= kTmemCols, "TMEM budget");
 
+// MMA N of a token tile: its valid rows rounded up to 32, at most 256 (both CTAs derive it from the tile).
+__device__ __forceinline__ int tile_n_eff(const TileInfo& t) {
+    const int n_valid = t.count - t.nt_idx * kTokTile;
+    return n_valid >= kTokTile ? kTokTile : ((n_valid + 31) & ~31);
+}
+
 __device__ __forceinline__ __nv_bfloat162 bf162_from_bits(uint32_t bits) {
     __nv_bfloat162 v;
     memcpy(&v, &bits, 4);
@@ -195,7 +201,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
             bool ok = true;
             for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
                 const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
-                const int row = t.row0 + (int)rank * kTokHalf;
+                const int row = t.row0 + (int)rank * (tile_n_eff(t) >> 1);
                 for (int ks = 0; ks < k_stages; ++ks) {
                     if (!mbar_wait(&b_empty[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
                         ok = false;
@@ -212,7 +218,6 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
     } else if (warp == 1) {
         if (lane == 0 && leader) {
             // ------------------------------ MMA issuer (leader CTA) -----------------
-            constexpr uint32_t idesc = umma_idesc_bf16(2 * kBlockM, kTokTile);
             constexpr int kSlab16 = (kTokHalf * 128) >> 4;
             const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(b_base));
             uint32_t tile_n = 0, s = 0, ph = 0, d = 0, dph = 0;
@@ -229,6 +234,10 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
                 }
                 tc_fence_after();
                 const uint32_t acc = tmem_base + kAccBase;
+                // the ragged last token tile of an expert runs with a narrower N (cost ~ N, floor at the
+                // issue rate): each CTA then stages N/2 of its rows instead of 128
+                const uint32_t idesc =
+                    umma_idesc_bf16(2 * kBlockM, (uint32_t)tile_n_eff(tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile)));
                 for (int ks = 0; ks < k_stages; ++ks) {
                     {
                         XMOE_T0();
