@@ -272,6 +272,14 @@ int xmoe_ep_wait_data(const xmoe_ep_buffers* b, int32_t* e_recv, void* w_recv, i
 /* out_rows / topk_row: the local pipeline's FF2 rows and packed-row index per received row (workspace view). */
 int xmoe_ep_return(const xmoe_ep_buffers* b, const void* out_rows, const int32_t* topk_row, int32_t expected_rows,
                    xmoe_stream_t stream);
+/* The owner-side pipeline with the return transfer fused into FF2: route pack -> quantise -> FF1 -> FF2
+ * on recv_x[rank] (cfg: the rank's experts, top_k = 1, no shared experts), where the FF2 epilogue stores
+ * every output row straight into its home rank's ret_rows slot and a last tiny kernel raises the return
+ * flags. Replaces xmoe_forward_routed_bounded + xmoe_ep_return. row_dst_scratch: 8 bytes per packed row
+ * (xmoe_packed_rows(cfg, cap_rows)). */
+int xmoe_ep_forward_local(const xmoe_ep_buffers* b, const xmoe_config* cfg, const xmoe_weights* w,
+                          const int32_t* e_recv, const void* w_recv, const float* act_scale, const int32_t* n_recv_dev,
+                          void* row_dst_scratch, void* workspace, size_t workspace_bytes, xmoe_stream_t stream);
 int xmoe_ep_wait_ret(const xmoe_ep_buffers* b, xmoe_stream_t stream);
 /* Synchronises the stream and returns the sticky XMOE_EP_* bits of this rank's control block (0 = fine). */
 int xmoe_ep_status(const xmoe_ep_buffers* b, xmoe_stream_t stream, uint32_t* bits_out);

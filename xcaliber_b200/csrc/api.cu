@@ -199,9 +199,11 @@ int run_ff1(const void* w13_packed, const void* w13_sf, const float* w13_gs, con
 }
 
 int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int32_t* counts, const int32_t* offsets,
-            void* out_rows, uint32_t* status, int e_tot, int H, int I, size_t rows, int nt, cudaStream_t stream) {
+            void* out_rows, uint32_t* status, int e_tot, int H, int I, size_t rows, int nt, cudaStream_t stream,
+            const unsigned long long* row_dst = nullptr) {
     Ff2Args a;
     memset(&a, 0, sizeof(a));
+    a.row_dst = row_dst;
     // 256-token tiles run on CTA pairs (2-SM MMA) unless XMOE_FF2_PAIR=0: each CTA stages 128 token
     // rows and K 128 (64-byte weight rows). The single-CTA 256 variant uses K 64 (32-byte rows).
     static const bool pair_enabled = [] {
@@ -244,8 +246,10 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
 
 int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* logits,
                  const int32_t* ext_idx, const void* ext_w, const float* ext_scale, int n, void* y, void* ws,
-                 size_t ws_bytes, cudaStream_t stream, const int32_t* n_valid_dev = nullptr) {
+                 size_t ws_bytes, cudaStream_t stream, const int32_t* n_valid_dev = nullptr,
+                 const xmoe_ep_buffers* ep_ret = nullptr, unsigned long long* row_dst = nullptr) {
     int rc = check_cfg(cfg);
+    if (ep_ret && (!row_dst || !ext_idx || cfg->top_k + cfg->num_shared_experts != 1)) return XMOE_ERR_ARG;
     if (rc) return rc;
     if (n < 0) return XMOE_ERR_ARG;
     if (n == 0) return XMOE_OK;
@@ -321,6 +325,10 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     p.status = status;
     prof_mark(1, stream);
     if ((rc = launch_route_pack(p, stream))) return rc;
+    if (ep_ret) {  // expert-parallel receive side: FF2 will store every row at its home rank
+        if (cudaMemsetAsync(row_dst, 0, L.rows * 8, stream) != cudaSuccess) return XMOE_ERR_CUDA;
+        if ((rc = launch_ep_row_dst(ep_ret, topk_row, row_dst, stream))) return rc;
+    }
     prof_mark(2, stream);
 
     AmaxArgs am;
@@ -372,8 +380,9 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     prof_mark(6, stream);
 
     if ((rc = run_ff2(w->w2_q, w->w2_scale, b + L.off_yact, counts, offsets, b + L.off_out, status, L.e_tot, H, I,
-                      L.rows, ff2_token_tile(cfg, L.nt), stream)))
+                      L.rows, ff2_token_tile(cfg, L.nt), stream, ep_ret ? row_dst : nullptr)))
         return rc;
+    if (ep_ret && (rc = launch_ep_signal_ret(ep_ret, stream))) return rc;
     prof_mark(7, stream);
 
     CombineArgs c;
@@ -718,6 +727,14 @@ int xmoe_ep_wait_data(const xmoe_ep_buffers* b, int32_t* e_recv, void* w_recv, i
 int xmoe_ep_return(const xmoe_ep_buffers* b, const void* out_rows, const int32_t* topk_row, int32_t expected_rows,
                    xmoe_stream_t stream) {
     return launch_ep_return(b, out_rows, topk_row, expected_rows, (cudaStream_t)stream);
+}
+int xmoe_ep_forward_local(const xmoe_ep_buffers* b, const xmoe_config* cfg, const xmoe_weights* w,
+                          const int32_t* e_recv, const void* w_recv, const float* act_scale, const int32_t* n_recv_dev,
+                          void* row_dst_scratch, void* workspace, size_t workspace_bytes, xmoe_stream_t stream) {
+    if (!b || !e_recv || !w_recv || !row_dst_scratch || b->rank < 0 || b->rank >= XMOE_EP_MAX_WORLD) return XMOE_ERR_ARG;
+    if (!cfg || cfg->hidden != b->hidden || cfg->num_experts != b->experts_per_rank) return XMOE_ERR_SHAPE;
+    return forward_impl(cfg, w, b->recv_x[b->rank], nullptr, e_recv, w_recv, act_scale, b->cap_rows, nullptr, workspace,
+                        workspace_bytes, (cudaStream_t)stream, n_recv_dev, b, (unsigned long long*)row_dst_scratch);
 }
 int xmoe_ep_wait_ret(const xmoe_ep_buffers* b, xmoe_stream_t stream) {
     return launch_ep_wait_ret(b, (cudaStream_t)stream);

@@ -242,6 +242,46 @@ __global__ __launch_bounds__(256) void ep_return_kernel(EpCtx c, const uint4* __
     }
 }
 
+// Destination of every packed row of the local pipeline: the slot of its home rank's return buffer.
+// With this table the FF2 epilogue stores its rows straight into peer memory (no separate return copy).
+__global__ __launch_bounds__(256) void ep_row_dst_kernel(EpCtx c, const int32_t* __restrict__ topk_row,
+                                                        unsigned long long* __restrict__ row_dst) {
+    __shared__ int bound[kMaxWorld + 1];
+    EpCtl* me = c.ctl[c.rank];
+    if (threadIdx.x == 0) {
+        int s = 0;
+        for (int r = 0; r < c.world; ++r) {
+            bound[r] = s;
+            s += me->counts[r][c.rank];
+        }
+        bound[c.world] = min(s, c.cap_rows);
+    }
+    __syncthreads();
+    const int total = bound[c.world];
+    const int4* meta = c.recv_meta[c.rank];
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < total; j += gridDim.x * blockDim.x) {
+        int r = 0;
+        while (r + 1 < c.world && j >= bound[r + 1]) ++r;
+        const int slot = meta[j].z;
+        const int prow = topk_row[j];
+        if (slot < 0 || slot >= c.ret_cap || prow < 0) {
+            atomicOr(&me->error, kErrCapacity);
+            continue;
+        }
+        row_dst[prow] = (unsigned long long)(uintptr_t)c.ret_rows[r] + (unsigned long long)slot * c.H * 2ull;
+    }
+}
+
+// Raised after the kernel whose stores were the return transfer: stream order puts those stores
+// before this kernel, the system fence and the releases publish them to the peers.
+__global__ void ep_signal_ret_kernel(EpCtx c) {
+    EpCtl* me = c.ctl[c.rank];
+    if (threadIdx.x < c.world) {
+        __threadfence_system();
+        st_release_sys(&c.ctl[threadIdx.x]->flag_ret[c.rank], me->epoch);
+    }
+}
+
 __global__ void ep_wait_ret_kernel(EpCtx c) {
     EpCtl* me = c.ctl[c.rank];
     if (threadIdx.x < c.world) wait_flag(&me->flag_ret[threadIdx.x], me->epoch, &me->error);
@@ -323,6 +363,26 @@ int launch_ep_return(const xmoe_ep_buffers* b, const void* out_rows, const int32
     if (!out_rows || !topk_row) return XMOE_ERR_ARG;
     ep_return_kernel<<<grid_for(expected_rows > 0 ? expected_rows : 1), 256, 0, stream>>>(c, (const uint4*)out_rows,
                                                                                           topk_row);
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+int launch_ep_row_dst(const xmoe_ep_buffers* b, const int32_t* topk_row, unsigned long long* row_dst,
+                      cudaStream_t stream) {
+    EpCtx c;
+    int rc = make_ctx(b, &c);
+    if (rc) return rc;
+    if (!topk_row || !row_dst) return XMOE_ERR_ARG;
+    int blocks = (c.cap_rows + 255) / 256;
+    blocks = blocks > 148 ? 148 : blocks;
+    ep_row_dst_kernel<<<blocks, 256, 0, stream>>>(c, topk_row, row_dst);
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
+int launch_ep_signal_ret(const xmoe_ep_buffers* b, cudaStream_t stream) {
+    EpCtx c;
+    int rc = make_ctx(b, &c);
+    if (rc) return rc;
+    ep_signal_ret_kernel<<<1, 32, 0, stream>>>(c);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 

@@ -369,11 +369,16 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 const uint4* src = reinterpret_cast<const uint4*>(tp + lane * 32);
                 const uint4 r0 = src[0], r1 = src[1], r2 = src[2], r3 = src[3];
                 if (c0 + lane < n_valid) {
-                    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(t.row0 + c0 + lane) * a.H + h_base);
-                    if (h_base < a.H) dst[0] = r0;
-                    if (h_base + 8 < a.H) dst[1] = r1;
-                    if (h_base + 16 < a.H) dst[2] = r2;
-                    if (h_base + 24 < a.H) dst[3] = r3;
+                    const int prow = t.row0 + c0 + lane;
+                    // the row's home: this GPU's row buffer, or (expert parallel) a peer's return buffer
+                    uint16_t* row_ptr = a.row_dst ? reinterpret_cast<uint16_t*>(a.row_dst[prow]) : out + (size_t)prow * a.H;
+                    if (row_ptr) {
+                        uint4* dst = reinterpret_cast<uint4*>(row_ptr + h_base);
+                        if (h_base < a.H) dst[0] = r0;
+                        if (h_base + 8 < a.H) dst[1] = r1;
+                        if (h_base + 16 < a.H) dst[2] = r2;
+                        if (h_base + 24 < a.H) dst[3] = r3;
+                    }
                 }
                 __syncwarp();
             }

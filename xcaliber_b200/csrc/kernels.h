@@ -93,6 +93,10 @@ struct Ff2Args {
     const int32_t* counts;
     const int32_t* offsets;
     void* out;  // bf16 [R_cap, H]
+    // optional [R_cap]: where each packed row's output goes instead of `out` (byte address of the row
+    // start, 0 = nowhere). Expert-parallel ranks point it at the home ranks' return buffers, so that
+    // the epilogue's stores are the return transfer.
+    const unsigned long long* row_dst;
     uint32_t* status;
     int E_tot, H, I, groups;  // groups = ceil(I / 128)
     int nt;
@@ -141,6 +145,8 @@ int launch_ep_wait_data(const xmoe_ep_buffers* b, int32_t* e_recv, void* w_recv,
 int launch_ep_return(const xmoe_ep_buffers* b, const void* out_rows, const int32_t* topk_row, int expected_rows,
                      cudaStream_t stream);
 int launch_ep_wait_ret(const xmoe_ep_buffers* b, cudaStream_t stream);
+int launch_ep_row_dst(const xmoe_ep_buffers* b, const int32_t* topk_row, unsigned long long* row_dst, cudaStream_t stream);
+int launch_ep_signal_ret(const xmoe_ep_buffers* b, cudaStream_t stream);
 int probe_mma_rate(int kind, int n_mma, double* tflops_out, cudaStream_t stream);
 int launch_repack_kmajor_int4(const void* w_in, void* out, size_t n_words, cudaStream_t stream);
 

@@ -13,8 +13,9 @@ replica of the shared experts; tokens are data-parallel. Per layer call:
      csrc/ep_p2p.cu); with transport="nccl" as one NCCL all-to-all grouped by destination rank
      (counts exchanged first, one host read);
   4. run the local pipeline (route pack -> NVFP4 quantise -> FF1 -> FF2) on the received rows;
-  5. combine: the reverse all-to-all returns one bf16 row per assignment; the home rank sums
-     its k rows (+ shared-expert rows) in slot order with the combine kernel.
+  5. combine: one bf16 row per assignment returns to its home rank (peer transport: the FF2 epilogue
+     stores it straight into the home rank's buffer; NCCL transport: the reverse all-to-all); the home
+     rank sums its k rows (+ shared-expert rows) in slot order with the combine kernel.
 
 The planning helpers are device-agnostic torch index arithmetic so that the exchange logic
 can be tested on CPU ranks with the gloo backend and a stand-in for step 4.
@@ -218,7 +219,7 @@ class ExpertParallelMoE:
     memory with no host synchronisation; transport="nccl": NCCL all-to-all with host-side counts."""
 
     def __init__(self, shape, checkpoint, group=None, device="cuda", transport: str = "peer",
-                 max_tokens: int = 4096):
+                 max_tokens: int = 4096, fused_return: bool = True):
         from . import ops
         from .synth import scaled_shape
 
@@ -243,6 +244,8 @@ class ExpertParallelMoE:
             raise ValueError("transport must be 'peer' or 'nccl'")
         self.transport = transport
         self.max_tokens = max_tokens
+        self.fused_return = fused_return  # peer transport: FF2 writes its rows into the home ranks' buffers
+        self._row_dst = {}
         self.peer = PeerExchange(shape, self.e_local, max_tokens, torch.device(device), group) \
             if transport == "peer" else None
         # router state lives with the full expert count
@@ -311,12 +314,26 @@ class ExpertParallelMoE:
         _lib.check(lib.xmoe_ep_wait_data(px.ref, px.e_recv.data_ptr(), px.w_recv.data_ptr(), px.n_recv.data_ptr(), st),
                    "xmoe_ep_wait_data")
         tile, local = self._local_layer(n)
-        local.forward_routed_rows(px.recv_x, px.e_recv, px.w_recv, act_scale=self._scale, n_valid=px.n_recv)
-        ptrs = self._local_ptrs.get(tile)
-        if ptrs is None:
-            v = local.view(px.cap_rows)
-            ptrs = self._local_ptrs[tile] = (v["out_rows"].data_ptr(), v["topk_row"].data_ptr())
-        _lib.check(lib.xmoe_ep_return(px.ref, ptrs[0], ptrs[1], n * k, st), "xmoe_ep_return")
+        if self.fused_return:
+            # the FF2 epilogue stores each row at its home rank; no separate return copy
+            import ctypes as C
+
+            ws = local.workspace(px.cap_rows)
+            scratch = self._row_dst.get(tile)
+            if scratch is None:
+                rows = lib.xmoe_packed_rows(C.byref(local.cfg), px.cap_rows)
+                scratch = self._row_dst[tile] = torch.zeros(rows, dtype=torch.int64, device=x.device)
+            _lib.check(lib.xmoe_ep_forward_local(px.ref, C.byref(local.cfg), C.byref(local._wstruct),
+                                                 px.e_recv.data_ptr(), px.w_recv.data_ptr(), self._scale.data_ptr(),
+                                                 px.n_recv.data_ptr(), scratch.data_ptr(), ws.data_ptr(), ws.numel(),
+                                                 st), "xmoe_ep_forward_local")
+        else:
+            local.forward_routed_rows(px.recv_x, px.e_recv, px.w_recv, act_scale=self._scale, n_valid=px.n_recv)
+            ptrs = self._local_ptrs.get(tile)
+            if ptrs is None:
+                v = local.view(px.cap_rows)
+                ptrs = self._local_ptrs[tile] = (v["out_rows"].data_ptr(), v["topk_row"].data_ptr())
+            _lib.check(lib.xmoe_ep_return(px.ref, ptrs[0], ptrs[1], n * k, st), "xmoe_ep_return")
         k_eff = k
         if self.shared is not None:
             y_sh = self._shared(x)
