@@ -212,6 +212,8 @@ def main() -> int:
     if world > 1:
         import torch.distributed as dist
 
+        # stdout carries exactly one JSON line: NCCL's own messages (version banner, NCCL_DEBUG output) go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     ckpt = synth.make_weights(shape, seed=0, device=dev)
     x_cpu, logits_cpu = synth.make_inputs(shape, router_on_cpu(ckpt), n, seed=rank)
