@@ -185,7 +185,11 @@ def main() -> int:
     if args.impl == "reference":
         if rank != 0:
             return 0
-        w_cpu = synth.make_weights(shape, seed=0, device="cpu")
+        # same weights as the native arm; synthesised on the GPU when there is one (minutes faster), timed on the CPU
+        if torch.cuda.is_available():
+            w_cpu = to_cpu_weights(synth.make_weights(shape, seed=0, device=torch.device("cuda", local_rank)))
+        else:
+            w_cpu = synth.make_weights(shape, seed=0, device="cpu")
         sample = min(args.cpu_sample_tokens, n)
         tps, cores, med = cpu_oracle_tokens_per_s(shape, w_cpu, sample, max(1, min(args.steps, 3)), 1)
         line = {"metric": METRIC, "value": tps, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
