@@ -279,19 +279,38 @@ __global__ __launch_bounds__(256) void route_scatter_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int chunk = blockIdx.x;
 
-    // totals and this chunk's base (tokens of earlier chunks come first)
+    // per-warp histograms of this chunk (later turned into bases in place)
+    for (int e = threadIdx.x; e < e_tot; e += blockDim.x)
+        for (int w = 0; w < 8; ++w) warp_base[w][e] = 0;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int t_mine = chunk * kPackChunk + threadIdx.x;
+    if (t_mine < N) {
+        for (int k = 0; k < topk; ++k) {
+            const int e = topk_idx[(size_t)t_mine * idx_stride + k];
+            if (e >= 0 && e < E) atomicAdd(&warp_base[warp][e], 1);
+            else if (e != -1) atomicExch(status, 0x600u);  // expert id outside [0, E); -1 = slot not in use
+        }
+        for (int s = 0; s < n_shared; ++s) atomicAdd(&warp_base[warp][E + s], 1);
+    }
+    __syncthreads();
+
+    // totals and this chunk's base (tokens of earlier chunks come first). A single chunk is its own
+    // total: small batches skip the histogram kernel altogether.
     for (int e = threadIdx.x; e < e_tot; e += blockDim.x) {
         int tot = 0, before = 0;
-        for (int c = 0; c < n_chunks; ++c) {
-            const int h = chunk_hist[(size_t)c * e_tot + e];
-            tot += h;
-            if (c < chunk) before += h;
+        if (n_chunks == 1) {
+            for (int w = 0; w < 8; ++w) tot += warp_base[w][e];
+        } else {
+            for (int c = 0; c < n_chunks; ++c) {
+                const int h = chunk_hist[(size_t)c * e_tot + e];
+                tot += h;
+                if (c < chunk) before += h;
+            }
         }
         total[e] = tot;
         before_chunk[e] = before;
-        for (int w = 0; w < 8; ++w) warp_base[w][e] = 0;
     }
-    if (threadIdx.x == 0) carry = 0;
     __syncthreads();
 
     // exclusive scan of round_up(total, 128) -> start[]
@@ -321,18 +340,6 @@ __global__ __launch_bounds__(256) void route_scatter_kernel(
         }
         if (threadIdx.x == 0) offsets[e_tot] = start[e_tot];
     }
-
-    // per-warp histograms of this chunk (built in place, then turned into bases)
-    const int t_mine = chunk * kPackChunk + threadIdx.x;
-    if (t_mine < N) {
-        for (int k = 0; k < topk; ++k) {
-            const int e = topk_idx[(size_t)t_mine * idx_stride + k];
-            if (e >= 0 && e < E) atomicAdd(&warp_base[warp][e], 1);
-            else if (e != -1) atomicExch(status, 0x600u);  // expert id outside [0, E); -1 = slot not in use
-        }
-        for (int s = 0; s < n_shared; ++s) atomicAdd(&warp_base[warp][E + s], 1);
-    }
-    __syncthreads();
     for (int e = threadIdx.x; e < e_tot; e += blockDim.x) {
         int run = before_chunk[e];  // rows of earlier chunks
         for (int w = 0; w < 8; ++w) {
@@ -409,8 +416,9 @@ int launch_route_pack(const PackArgs& a, cudaStream_t stream) {
     if (a.N <= 0) return XMOE_OK;
     if (a.E + a.n_shared > kMaxEtot || a.topk + a.n_shared > 32) return XMOE_ERR_SHAPE;
     const int chunks = route_pack_chunks(a.N);
-    route_hist_kernel<<<chunks, 256, 0, stream>>>(a.topk_idx, a.N, a.E, a.topk, a.idx_stride, a.n_shared,
-                                                  a.chunk_hist);
+    if (chunks > 1)  // a single chunk builds its totals inside the scatter kernel
+        route_hist_kernel<<<chunks, 256, 0, stream>>>(a.topk_idx, a.N, a.E, a.topk, a.idx_stride, a.n_shared,
+                                                      a.chunk_hist);
     route_scatter_kernel<<<chunks, 256, 0, stream>>>(a.topk_idx, (uint16_t*)a.topk_w, a.N, a.E, a.topk,
                                                      a.idx_stride, a.n_shared, a.chunk_hist, chunks, a.counts,
                                                      a.offsets, a.topk_off, a.topk_row, a.row_token,
