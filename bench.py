@@ -48,8 +48,8 @@ def measured_peaks() -> dict:
 
 class ClockSampler:
     """SM clock and clock-event reasons of one GPU, read through NVML every 10 ms by a thread while
-    the timed region runs (read-only queries; nothing is set). The samples are also written to
-    gpurun_out/clocks_rank<i>.csv."""
+    the timed region runs (read-only queries; nothing is set). The samples are also written to a CSV
+    file (one per rank) beside the other run outputs."""
 
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
