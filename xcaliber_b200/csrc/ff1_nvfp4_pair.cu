@@ -8,6 +8,11 @@
 // both halves, every CTA gets gate and up columns for its own 128 tokens, and weight traffic
 // per SM halves (38 KB per 16.8 MFLOP).
 //
+// The epilogue warps hold their whole accumulator slice in registers (setmaxnreg moves registers to
+// them from the single-thread roles) and release the accumulator right after copying it: SwiGLU and
+// the stores of tile t overlap the MMAs of tile t + 1 (un-overlapped, the epilogue was 27 % of the
+// kernel). What bounds the kernel now is L2 -> SM delivery of 38 KB per K 256 stage.
+//
 // Scale factors: each CTA needs the token scales of its own rows and the weight scales of ALL 256
 // N rows in its tensor memory, so both CTAs load both (2 KB each per stage). Three threads of the
 // leader (tokens / gate / up) issue the cta_group::2 tcgen05.cp that copy from each CTA's shared
@@ -27,6 +32,15 @@
 
 namespace xmoe {
 
+#ifdef XMOE_TRACE
+__device__ long long g_ff1p_trace[148 * 8];
+#define XMOE_T0() const long long t0__ = clock64()
+#define XMOE_TACC(var) var += clock64() - t0__
+#else
+#define XMOE_T0() do {} while (0)
+#define XMOE_TACC(var) do {} while (0)
+#endif
+
 namespace {
 
 constexpr int kTokHalf = 128;          // token rows per CTA
@@ -39,8 +53,17 @@ constexpr int kABytes = kTokHalf * kStageKBytes;   // 16 KiB: my tokens
 constexpr int kBBytes = kWTile * kStageKBytes;     // 16 KiB: my half of the weight tile
 constexpr int kStageBytes = kABytes + kBBytes + 3 * kSfBytes;  // 38 KiB
 constexpr int kStages = 5;
-constexpr int kThreads = 416;          // producer, MMA / relay, 8 epilogue warps, 3 scale-factor copy warps
-constexpr int kFirstSfWarp = 10;
+// Warp roles, arranged so that register reallocation (setmaxnreg, per group of 4 consecutive warps)
+// can move registers from the single-thread roles to the epilogue:
+//   warps 0-3  : TMA producer, MMA issuer (peer: relay), scale-factor copies of tokens / gate rows
+//   warps 4-11 : epilogue (two per tensor-memory lane quadrant)
+//   warp 12    : scale-factor copies of the up rows; warps 13-15 idle
+constexpr int kThreads = 512;
+constexpr int kFirstEpiWarp = 4;
+constexpr int kLastSfWarp = 12;
+constexpr int kRegsFew = 40;    // single-thread roles
+constexpr int kRegsEpi = 208;   // epilogue: 128 accumulator values in flight per thread
+static_assert(2 * 128 * (kRegsEpi - 128) <= 2 * 128 * (128 - kRegsFew), "register pool: 512 threads x 128 at launch");
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = 256;
 constexpr int kSfSlotCols = 48;
@@ -95,114 +118,17 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_pair_kernel(const __gri
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = prefix[a.E_tot];
 
-    if (warp == 0) {
-        // ---- producer: my 128 tokens, my half of the weight tile, all scale factors ----
-        if (lane == 0) {
-            uint32_t s = 0, ph = 0;
-            bool ok = true;
-            for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
-                const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
-                const int tok_row = t.row0 + (int)rank * kTokHalf;
-                const int w_row = t.e * 2 * a.I + (int)rank * a.I + t.wt * kWTile;  // leader: gate rows, peer: up rows
-                const uint8_t* sfw_g = a.sfw + ((size_t)(t.e * 2 + 0) * a.mb + t.wt) * a.kb_pad * 512;
-                const uint8_t* sfw_u = a.sfw + ((size_t)(t.e * 2 + 1) * a.mb + t.wt) * a.kb_pad * 512;
-                const uint8_t* sfx = a.sfx + (size_t)(tok_row / kTokHalf) * a.kb_pad * 512;
-                for (int ks = 0; ks < k_stages; ++ks) {
-                    if (!mbar_wait_cluster(&empty_bar[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
-                        ok = false;
-                        break;
-                    }
-                    uint8_t* st = smem + (size_t)s * kStageBytes;
-                    mbar_expect_tx(&full_bar[s], kStageBytes);
-                    tma_load_2d(st, &a.tm_x, ks * kStageKBytes, tok_row, &full_bar[s]);
-                    tma_load_2d(st + kABytes, &a.tm_w, ks * kStageKBytes, w_row, &full_bar[s]);
-                    uint8_t* sf = st + kABytes + kBBytes;
-                    tma_load_1d(sf, sfx + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
-                    tma_load_1d(sf + kSfBytes, sfw_g + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
-                    tma_load_1d(sf + 2 * kSfBytes, sfw_u + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
-                    if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
-                }
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0 && leader) {
-            // ---- MMA issuer (leader) ----
-            constexpr uint32_t idesc = umma_idesc_nvfp4(2 * kTokHalf, 2 * kWTile);
-            constexpr uint32_t kStage16 = kStageBytes >> 4;
-            const uint32_t a_lo0 = umma_desc_lo_sw128(smem_u32(smem));
-            const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(smem + kABytes));
-            uint32_t tile_n = 0, s = 0, ph = 0;
-            bool ok = true;
-            for (int item = cluster_id; item < total_tiles && ok; item += n_clusters, ++tile_n) {
-                if (!mbar_wait_cluster(acc_empty, (tile_n & 1u) ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
-                tc_fence_after();
-                for (int ks = 0; ks < k_stages; ++ks) {
-                    if (!mbar_wait_cluster(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
-                        !mbar_wait(&sf_ready[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t sf_tmem = tmem_base + kAccCols + s * kSfSlotCols;
-                    const uint32_t a_lo = a_lo0 + s * kStage16;
-                    const uint32_t b_lo = b_lo0 + s * kStage16;
-#pragma unroll
-                    for (int kb = 0; kb < 4; ++kb)
-                        mma_nvfp4_pair(tmem_base, a_lo + kb * 2, b_lo + kb * 2, idesc, sf_tmem + kb * 4,
-                                       sf_tmem + 16 + kb * 8, (ks | kb) ? 1u : 0u);
-                    tc_commit_pair_mask(smem_u32(&empty_bar[s]), 3);
-                    if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
-                }
-                if (ok) tc_commit_pair_mask(smem_u32(acc_full), 3);
-            }
-        } else if (lane == 0) {
-            // ---- relay (peer): report landed stages to the leader ----
-            const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[0]), 0);
-            uint32_t s = 0, ph = 0;
-            bool ok = true;
-            for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
-                for (int ks = 0; ks < k_stages; ++ks) {
-                    if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
-                        ok = false;
-                        break;
-                    }
-                    mbar_arrive_cluster(leader_full + s * 8u);
-                    if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
-                }
-            }
-        }
-    } else if (warp >= kFirstSfWarp) {
-        // ---- scale-factor copies (leader): one thread per operand; a cta_group::2 copy moves each
-        // CTA's shared-memory tile into that CTA's tensor memory. A stage's copies may start once
-        // BOTH CTAs' bytes have landed (the leader's full barrier counts the peer's report).
-        if (lane == 0 && leader) {
-            const int which = warp - kFirstSfWarp;  // 0 my tokens, 1 gate rows, 2 up rows
-            constexpr uint32_t kStage16 = kStageBytes >> 4;
-            const uint32_t sf_lo0 = umma_desc_lo_sf(smem_u32(smem + kABytes + kBBytes)) + which * (kSfBytes >> 4);
-            const uint32_t col0 = which == 0 ? 0u : (which == 1 ? 16u : 20u);
-            const uint32_t col_step = which == 0 ? 4u : 8u;
-            uint32_t s = 0, ph = 0;
-            bool ok = true;
-            for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
-                for (int ks = 0; ks < k_stages; ++ks) {
-                    if (!mbar_wait_cluster(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t sf_lo = sf_lo0 + s * kStage16;
-                    const uint32_t sf_tmem = tmem_base + kAccCols + s * kSfSlotCols + col0;
-#pragma unroll
-                    for (int kb = 0; kb < 4; ++kb) tmem_cp_sf_pair(sf_tmem + kb * col_step, sf_lo + kb * 32);
-                    tc_commit_pair(smem_u32(&sf_ready[s]));
-                    if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
-                }
-            }
-        }
-    } else {
-        // ---- epilogue: my 128 tokens x (128 gate | 128 up) columns, 8 warps ----
+    // Register reallocation by groups of four warps (all threads of a group take the same branch): the
+    // epilogue keeps a whole accumulator slice in registers so that it can hand the accumulator back
+    // before doing its arithmetic and stores; the single-thread roles give their registers up.
+    if (warp >= kFirstEpiWarp && warp < kFirstEpiWarp + 8) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpi));
+        // ---- epilogue: my 128 tokens x (128 gate | 128 up) columns, 8 warps. Each warp first copies its
+        // whole slice (64 gate + 64 up columns) to registers and releases the accumulator: the next tile's
+        // MMAs run while this one's SwiGLU and stores are done (the un-overlapped epilogue was 27 % of
+        // the kernel).
         const int q = warp & 3;
-        const int col_half = (warp - 2) >> 2;
+        const int col_half = (warp - kFirstEpiWarp) >> 2;
         const float xgs_inv = a.scale->xgs_inv;
         uint16_t* yact = reinterpret_cast<uint16_t*>(a.yact);
         const uint16_t* row_w = reinterpret_cast<const uint16_t*>(a.row_weight);
@@ -220,32 +146,163 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_pair_kernel(const __gri
             if (!mbar_wait_cluster(acc_full, tile_n & 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
             tc_fence_after();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + col_half * 64;
-#pragma unroll 1
-            for (int c0 = 0; c0 < 64; c0 += 32) {
-                if (i0 + c0 >= a.I) break;
-                uint32_t g[32], u[32];
-                tmem_ld32(lane_addr + c0, g);
-                tmem_ld32(lane_addr + kWTile + c0, u);
-                tmem_ld_wait();
-                if (row_ok) {
-                    uint32_t o[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float y0 = glu_apply(ACT, __uint_as_float(g[2 * j]), __uint_as_float(u[2 * j]), sg, su,
-                                                   a.alpha, a.limit, w);
-                        const float y1 = glu_apply(ACT, __uint_as_float(g[2 * j + 1]), __uint_as_float(u[2 * j + 1]), sg,
-                                                   su, a.alpha, a.limit, w);
-                        o[j] = pack_bf16x2(y0, y1);
-                    }
-                    uint4* dst = reinterpret_cast<uint4*>(yact + (size_t)r * a.I + i0 + c0);
-#pragma unroll
-                    for (int v = 0; v < 4; ++v)
-                        if (i0 + c0 + v * 8 < a.I) dst[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
-                }
-            }
+            uint32_t g[64], u[64];
+            tmem_ld32(lane_addr, g);
+            tmem_ld32(lane_addr + 32, g + 32);
+            tmem_ld32(lane_addr + kWTile, u);
+            tmem_ld32(lane_addr + kWTile + 32, u + 32);
+            tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+            if (lane == 0) mbar_arrive_cluster(leader_acc_empty);  // the accumulator is free again
+            if (row_ok) {
+#pragma unroll
+                for (int c0 = 0; c0 < 64; c0 += 32) {
+                    if (i0 + c0 < a.I) {
+                        uint32_t o[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float y0 = glu_apply(ACT, __uint_as_float(g[c0 + 2 * j]), __uint_as_float(u[c0 + 2 * j]),
+                                                       sg, su, a.alpha, a.limit, w);
+                            const float y1 = glu_apply(ACT, __uint_as_float(g[c0 + 2 * j + 1]),
+                                                       __uint_as_float(u[c0 + 2 * j + 1]), sg, su, a.alpha, a.limit, w);
+                            o[j] = pack_bf16x2(y0, y1);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(yact + (size_t)r * a.I + i0 + c0);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            if (i0 + c0 + v * 8 < a.I) dst[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                    }
+                }
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsFew));
+        if (warp == 0) {
+            // ---- producer: my 128 tokens, my half of the weight tile, all scale factors ----
+            if (lane == 0) {
+                uint32_t s = 0, ph = 0;
+                bool ok = true;
+                for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
+                    const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
+                    const int tok_row = t.row0 + (int)rank * kTokHalf;
+                    const int w_row = t.e * 2 * a.I + (int)rank * a.I + t.wt * kWTile;  // leader: gate rows, peer: up rows
+                    const uint8_t* sfw_g = a.sfw + ((size_t)(t.e * 2 + 0) * a.mb + t.wt) * a.kb_pad * 512;
+                    const uint8_t* sfw_u = a.sfw + ((size_t)(t.e * 2 + 1) * a.mb + t.wt) * a.kb_pad * 512;
+                    const uint8_t* sfx = a.sfx + (size_t)(tok_row / kTokHalf) * a.kb_pad * 512;
+                    for (int ks = 0; ks < k_stages; ++ks) {
+                        if (!mbar_wait_cluster(&empty_bar[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
+                            ok = false;
+                            break;
+                        }
+                        uint8_t* st = smem + (size_t)s * kStageBytes;
+                        mbar_expect_tx(&full_bar[s], kStageBytes);
+                        tma_load_2d(st, &a.tm_x, ks * kStageKBytes, tok_row, &full_bar[s]);
+                        tma_load_2d(st + kABytes, &a.tm_w, ks * kStageKBytes, w_row, &full_bar[s]);
+                        uint8_t* sf = st + kABytes + kBBytes;
+                        tma_load_1d(sf, sfx + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                        tma_load_1d(sf + kSfBytes, sfw_g + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                        tma_load_1d(sf + 2 * kSfBytes, sfw_u + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                        if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            if (lane == 0 && leader) {
+                // ---- MMA issuer (leader) ----
+                constexpr uint32_t idesc = umma_idesc_nvfp4(2 * kTokHalf, 2 * kWTile);
+                constexpr uint32_t kStage16 = kStageBytes >> 4;
+                const uint32_t a_lo0 = umma_desc_lo_sw128(smem_u32(smem));
+                const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(smem + kABytes));
+                uint32_t tile_n = 0, s = 0, ph = 0;
+                bool ok = true;
+                long long tw_acc = 0, tw_full = 0, tw_sf = 0, t_issue = 0;
+                (void)tw_acc; (void)tw_full; (void)tw_sf; (void)t_issue;
+                const long long t_start = clock64();
+                (void)t_start;
+                for (int item = cluster_id; item < total_tiles && ok; item += n_clusters, ++tile_n) {
+                    {
+                        XMOE_T0();
+                        if (!mbar_wait_cluster(acc_empty, (tile_n & 1u) ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
+                        XMOE_TACC(tw_acc);
+                    }
+                    tc_fence_after();
+                    for (int ks = 0; ks < k_stages; ++ks) {
+                        {
+                            XMOE_T0();
+                            if (!mbar_wait_cluster(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
+                            XMOE_TACC(tw_full);
+                        }
+                        {
+                            XMOE_T0();
+                            if (!mbar_wait(&sf_ready[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
+                            XMOE_TACC(tw_sf);
+                        }
+                        XMOE_T0();
+                        tc_fence_after();
+                        const uint32_t sf_tmem = tmem_base + kAccCols + s * kSfSlotCols;
+                        const uint32_t a_lo = a_lo0 + s * kStage16;
+                        const uint32_t b_lo = b_lo0 + s * kStage16;
+    #pragma unroll
+                        for (int kb = 0; kb < 4; ++kb)
+                            mma_nvfp4_pair(tmem_base, a_lo + kb * 2, b_lo + kb * 2, idesc, sf_tmem + kb * 4,
+                                           sf_tmem + 16 + kb * 8, (ks | kb) ? 1u : 0u);
+                        tc_commit_pair_mask(smem_u32(&empty_bar[s]), 3);
+                        if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+                        XMOE_TACC(t_issue);
+                    }
+                    if (ok) tc_commit_pair_mask(smem_u32(acc_full), 3);
+                }
+    #ifdef XMOE_TRACE
+                if (cluster_id < 148) {
+                    long long* o = g_ff1p_trace + cluster_id * 8;
+                    o[0] = tw_full; o[1] = tw_sf; o[2] = tw_acc; o[3] = t_issue; o[4] = clock64() - t_start; o[5] = tile_n;
+                }
+    #endif
+            } else if (lane == 0) {
+                // ---- relay (peer): report landed stages to the leader ----
+                const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[0]), 0);
+                uint32_t s = 0, ph = 0;
+                bool ok = true;
+                for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
+                    for (int ks = 0; ks < k_stages; ++ks) {
+                        if (!mbar_wait(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_cluster(leader_full + s * 8u);
+                        if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+                    }
+                }
+            }
+        } else if (warp == 2 || warp == 3 || warp == kLastSfWarp) {
+            // ---- scale-factor copies (leader): one thread per operand; a cta_group::2 copy moves each
+            // CTA's shared-memory tile into that CTA's tensor memory. A stage's copies may start once
+            // BOTH CTAs' bytes have landed (the leader's full barrier counts the peer's report).
+            if (lane == 0 && leader) {
+                const int which = warp == kLastSfWarp ? 2 : warp - 2;  // 0 my tokens, 1 gate rows, 2 up rows
+                constexpr uint32_t kStage16 = kStageBytes >> 4;
+                const uint32_t sf_lo0 = umma_desc_lo_sf(smem_u32(smem + kABytes + kBBytes)) + which * (kSfBytes >> 4);
+                const uint32_t col0 = which == 0 ? 0u : (which == 1 ? 16u : 20u);
+                const uint32_t col_step = which == 0 ? 4u : 8u;
+                uint32_t s = 0, ph = 0;
+                bool ok = true;
+                for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
+                    for (int ks = 0; ks < k_stages; ++ks) {
+                        if (!mbar_wait_cluster(&full_bar[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t sf_lo = sf_lo0 + s * kStage16;
+                        const uint32_t sf_tmem = tmem_base + kAccCols + s * kSfSlotCols + col0;
+    #pragma unroll
+                        for (int kb = 0; kb < 4; ++kb) tmem_cp_sf_pair(sf_tmem + kb * col_step, sf_lo + kb * 32);
+                        tc_commit_pair(smem_u32(&sf_ready[s]));
+                        if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+                    }
+                }
+            }
         }
     }
 
@@ -296,6 +353,12 @@ int launch_pair_act(const Ff1Args& a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+#ifdef XMOE_TRACE
+extern "C" int xmoe_ff1_pair_trace_dump(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_ff1p_trace, sizeof(g_ff1p_trace));
+}
+#endif
 
 int launch_ff1_pair(const Ff1Args& a, cudaStream_t stream) {
     switch (a.activation) {
