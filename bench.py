@@ -156,7 +156,27 @@ def router_on_cpu(w):
                               None if w.logit_bias is None else w.logit_bias.cpu())
 
 
+_REAL_STDOUT = None
+
+
+def claim_stdout() -> None:
+    """stdout carries exactly one JSON line. Libraries print there too (NCCL's version banner, for one):
+    keep the real stdout for the result and point file descriptor 1 at stderr for everything else."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    out = _REAL_STDOUT or sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def main() -> int:
+    claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -202,12 +222,12 @@ def main() -> int:
                 "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "note": "the reference project has no CPU path and its GPU kernels do not assemble for sm_100a; "
                         "this arm times the CPU restatement of its algorithm (oracle/) on the host cores"}
-        print(json.dumps(line))
+        emit(line)
         return 0
 
     # ------------------------------------------------------------------ native arm
     if not torch.cuda.is_available():
-        print(json.dumps({"error": "no CUDA device: the native arm has no CPU fallback"}))
+        emit({"error": "no CUDA device: the native arm has no CPU fallback"})
         return 1
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -216,8 +236,6 @@ def main() -> int:
     if world > 1:
         import torch.distributed as dist
 
-        # stdout carries exactly one JSON line: NCCL's own messages (version banner, NCCL_DEBUG output) go to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     ckpt = synth.make_weights(shape, seed=0, device=dev)
     x_cpu, logits_cpu = synth.make_inputs(shape, router_on_cpu(ckpt), n, seed=rank)
@@ -413,7 +431,7 @@ def main() -> int:
                 "device_status": statuses, **extra}
         if decode is not None:
             line["decode"] = decode
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
     return 0
