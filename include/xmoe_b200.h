@@ -276,10 +276,20 @@ int xmoe_ep_return(const xmoe_ep_buffers* b, const void* out_rows, const int32_t
  * on recv_x[rank] (cfg: the rank's experts, top_k = 1, no shared experts), where the FF2 epilogue stores
  * every output row straight into its home rank's ret_rows slot and a last tiny kernel raises the return
  * flags. Replaces xmoe_forward_routed_bounded + xmoe_ep_return. row_dst_scratch: 8 bytes per packed row
- * (xmoe_packed_rows(cfg, cap_rows)). */
+ * (xmoe_packed_rows(cfg, cap_rows)). quantised_input: 0 = recv_x holds bf16 rows (xmoe_ep_dispatch),
+ * 1 = NVFP4 packets (xmoe_ep_dispatch_quantised); act_scale is required in both cases. */
 int xmoe_ep_forward_local(const xmoe_ep_buffers* b, const xmoe_config* cfg, const xmoe_weights* w,
                           const int32_t* e_recv, const void* w_recv, const float* act_scale, const int32_t* n_recv_dev,
-                          void* row_dst_scratch, void* workspace, size_t workspace_bytes, xmoe_stream_t stream);
+                          int32_t quantised_input, void* row_dst_scratch, void* workspace, size_t workspace_bytes,
+                          xmoe_stream_t stream);
+/* xmoe_ep_dispatch fused with the activation quantiser: each token is quantised once on its home GPU with
+ * the scale all ranks agree on, and NVFP4 packets travel instead of bf16 rows (3.6x fewer bytes). recv_x[r]
+ * then holds codes [cap_rows, hidden/2] followed by block scales [cap_rows, hidden/16]; the owner side runs
+ * xmoe_ep_forward_local with quantised_input = 1 (its quantiser becomes a copy). Same packets, bit for bit,
+ * as quantising on the owner. */
+int xmoe_ep_dispatch_quantised(const xmoe_ep_buffers* b, const void* x, const int32_t* topk_idx, const void* topk_w,
+                               const int32_t* topk_off, const int32_t* counts_global, int32_t n_tokens, int32_t top_k,
+                               int32_t idx_stride, float* amax_global, xmoe_stream_t stream);
 int xmoe_ep_wait_ret(const xmoe_ep_buffers* b, xmoe_stream_t stream);
 /* Synchronises the stream and returns the sticky XMOE_EP_* bits of this rank's control block (0 = fine). */
 int xmoe_ep_status(const xmoe_ep_buffers* b, xmoe_stream_t stream, uint32_t* bits_out);

@@ -32,15 +32,17 @@ def main():
             xs.append(x)
             ls.append(lg)
         ys = {}
-        for transport in ("peer", "peer-copy", "nccl"):  # peer: FF2 stores rows at their home rank; peer-copy: return kernel
+        # peer: NVFP4 dispatch + FF2 stores rows at their home rank; peer-bf16: bf16 dispatch; peer-copy: also a
+        # separate return kernel
+        for transport in ("peer", "peer-bf16", "peer-copy", "nccl"):
             ep = ExpertParallelMoE(shape, ck, device=dev, transport=transport.split("-")[0], max_tokens=128,
-                                   fused_return=transport == "peer")
+                                   fused_return=transport != "peer-copy", quantised_dispatch=transport == "peer")
             for _ in range(3):  # repeated calls reuse the exchange buffers and their flags
                 ys[transport] = ep.forward(xs[rank].to(dev), ls[rank].to(dev))
             torch.cuda.synchronize()
             if ep.peer is not None and ep.peer.status():
                 failures.append(f"{name}: rank {rank} peer exchange status {ep.peer.status():#x}")
-        if not (torch.equal(ys["peer"], ys["nccl"]) and torch.equal(ys["peer-copy"], ys["nccl"])):
+        if not all(torch.equal(ys[t], ys["nccl"]) for t in ("peer", "peer-bf16", "peer-copy")):
             failures.append(f"{name}: rank {rank} peer and nccl transports differ")
         y = ys["peer"]
         # single-GPU reference on the concatenation of all ranks' tokens (same global amax)

@@ -94,7 +94,8 @@ SIGNATURES = {
     "xmoe_ep_wait_data": (C.c_int, [C.POINTER(XMoEEpBuffers), _P, _P, _P, _P]),
     "xmoe_ep_return": (C.c_int, [C.POINTER(XMoEEpBuffers), _P, _P, _I, _P]),
     "xmoe_ep_forward_local": (C.c_int, [C.POINTER(XMoEEpBuffers), C.POINTER(XMoEConfig), C.POINTER(XMoEWeights), _P, _P,
-                                        _P, _P, _P, _P, _SZ, _P]),
+                                        _P, _P, _I, _P, _P, _SZ, _P]),
+    "xmoe_ep_dispatch_quantised": (C.c_int, [C.POINTER(XMoEEpBuffers), _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
     "xmoe_ep_wait_ret": (C.c_int, [C.POINTER(XMoEEpBuffers), _P]),
     "xmoe_ep_status": (C.c_int, [C.POINTER(XMoEEpBuffers), _P, C.POINTER(C.c_uint32)]),
     "xmoe_nvfp4_sf_bytes": (_SZ, [_I, _I, _I]),

@@ -13,6 +13,7 @@
 // token operand, whatever NT is; for NT < 128 the unused 4-byte groups are never read.
 #include "common.cuh"
 #include "kernels.h"
+#include "nvfp4_quant.cuh"
 
 namespace xmoe {
 
@@ -90,49 +91,6 @@ int launch_act_scale_from_amax(const float* amax, float* scale, cudaStream_t str
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 
-__device__ __forceinline__ uint32_t ue4m3_ceil(float x) {
-    if (!(x > 0.0f)) return 0u;
-    if (x >= 448.0f) return 0x7eu;
-    const uint32_t bits = __float_as_uint(x);
-    int e = int((bits >> 23) & 0xffu) - 120;
-    if (e <= 0) {
-        const uint32_t m = __float2uint_ru(x * 512.0f);
-        return m > 7u ? 7u : m;
-    }
-    uint32_t m = (bits >> 20) & 7u;
-    m += (bits & 0x000fffffu) != 0u;
-    if (m == 8u) {
-        m = 0u;
-        e++;
-    }
-    if (e >= 15) return m > 6u ? 0x7eu : (0x78u | m);
-    return (uint32_t(e) << 3) | m;
-}
-__device__ __forceinline__ float ue4m3_decode(uint32_t s) {
-    const uint32_t e = s >> 3, m = s & 7u;
-    if (!e) return float(m) * (1.0f / 512.0f);
-    return __uint_as_float(((e + 120u) << 23) | (m << 20));
-}
-// two bf16 (packed) times a packed bf16 scale, product rounded to bf16, then RN-satfinite E2M1.
-__device__ __forceinline__ uint32_t e2m1x2(uint32_t x2, uint32_t scale2) {
-    uint32_t q;
-    asm("{\n\t"
-        ".reg .b32 y;\n\t"
-        ".reg .b16 lo, hi;\n\t"
-        ".reg .f32 flo, fhi;\n\t"
-        ".reg .b8 z;\n\t"
-        "mul.rn.bf16x2 y, %1, %2;\n\t"
-        "mov.b32 {lo, hi}, y;\n\t"
-        "cvt.f32.bf16 flo, lo;\n\t"
-        "cvt.f32.bf16 fhi, hi;\n\t"
-        "cvt.rn.satfinite.e2m1x2.f32 z, fhi, flo;\n\t"
-        "cvt.u32.u8 %0, z;\n\t"
-        "}"
-        : "=r"(q)
-        : "r"(x2), "r"(scale2));
-    return q;
-}
-
 // One thread quantises 16 consecutive K of one token (one block scale, 8 packed bytes);
 // a warp covers 512 K. The packet is then stored to each of the token's k_eff rows.
 __global__ __launch_bounds__(256) void act_quant_pack_kernel(
@@ -159,19 +117,8 @@ __global__ __launch_bounds__(256) void act_quant_pack_kernel(
             w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
             w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
         }
-        uint32_t mx = 0u;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) mx = max(mx, max(w[j] & 0x7fffu, (w[j] >> 16) & 0x7fffu));
-        uint32_t sbyte = 0u, q_lo = 0u, q_hi = 0u;
-        if (mx) {
-            sbyte = ue4m3_ceil(bf16_bits_to_f32(mx) * xgs * (1.0f / 6.0f));
-            const uint32_t qs = f32_to_bf16_bits(xgs / ue4m3_decode(sbyte));
-            const uint32_t qs2 = qs | (qs << 16);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) q_lo |= e2m1x2(w[j], qs2) << (8 * j);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) q_hi |= e2m1x2(w[4 + j], qs2) << (8 * j);
-        }
+        uint32_t sbyte, q_lo, q_hi;
+        nvfp4_quantise16(w, xgs, sbyte, q_lo, q_hi);
         // four neighbouring lanes hold the four block scales of one K64 block
         uint32_t s4 = sbyte << (8 * (lane & 3u));
         s4 |= __shfl_xor_sync(0xffffffffu, s4, 1);
@@ -187,6 +134,44 @@ __global__ __launch_bounds__(256) void act_quant_pack_kernel(
             }
         }
     }
+}
+
+// Rows that arrive already quantised (an expert-parallel peer did it with the shared activation
+// scale): codes [n, H/2] and block scales [n, H/16] in arrival order -> packed rows and scale tiles.
+// One warp per row; the same destinations act_quant_pack_kernel writes.
+__global__ __launch_bounds__(256) void act_repack_kernel(const uint8_t* __restrict__ xq_in,
+                                                        const uint8_t* __restrict__ sf_in,
+                                                        const int32_t* __restrict__ topk_row, int N, int idx_stride, int H,
+                                                        uint8_t* __restrict__ xq, uint8_t* __restrict__ sfx, int kb_pad,
+                                                        int nt, const int32_t* __restrict__ n_valid) {
+    if (n_valid) N = min(N, max(*n_valid, 0));
+    const int lane = (int)lane_id();
+    const int code_vecs = H / 32;  // 16-byte pieces of one row of codes
+    const int groups = H / 64;     // 4 scale bytes per K64 block
+    for (int j = blockIdx.x * 8 + (threadIdx.x >> 5); j < N; j += gridDim.x * 8) {
+        const int r = topk_row[(size_t)j * idx_stride];
+        if (r < 0) continue;
+        const uint4* src = reinterpret_cast<const uint4*>(xq_in + (size_t)j * (H / 2));
+        uint4* dst = reinterpret_cast<uint4*>(xq + (size_t)r * (H / 2));
+        for (int i = lane; i < code_vecs; i += 32) dst[i] = src[i];
+        const uint32_t* s_in = reinterpret_cast<const uint32_t*>(sf_in + (size_t)j * (H / 16));
+        for (int g = lane; g < kb_pad; g += 32) {
+            const uint32_t s4 = g < groups ? s_in[g] : 0u;  // K blocks beyond H are padding: scale 0
+            const size_t blk = (size_t)(r / nt) * kb_pad + g;
+            *reinterpret_cast<uint32_t*>(sfx + blk * 512 + (r & 31) * 16 + ((r % nt) >> 5) * 4) = s4;
+        }
+    }
+}
+
+int launch_act_repack(const void* xq_in, const void* sf_in, const QuantArgs& a, cudaStream_t stream) {
+    if (a.N <= 0) return XMOE_OK;
+    if (a.H % 64 || a.k_eff != 1 || (a.nt != 32 && a.nt != 64 && a.nt != 128)) return XMOE_ERR_SHAPE;
+    int blocks = (a.N + 7) / 8;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    act_repack_kernel<<<blocks, 256, 0, stream>>>((const uint8_t*)xq_in, (const uint8_t*)sf_in, a.topk_row, a.N,
+                                                  a.idx_stride, a.H, (uint8_t*)a.xq, (uint8_t*)a.sfx, a.kb_pad, a.nt,
+                                                  a.n_valid);
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 
 int launch_act_amax(const AmaxArgs& a, cudaStream_t stream) {

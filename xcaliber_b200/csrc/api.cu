@@ -247,8 +247,10 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
 int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* logits,
                  const int32_t* ext_idx, const void* ext_w, const float* ext_scale, int n, void* y, void* ws,
                  size_t ws_bytes, cudaStream_t stream, const int32_t* n_valid_dev = nullptr,
-                 const xmoe_ep_buffers* ep_ret = nullptr, unsigned long long* row_dst = nullptr) {
+                 const xmoe_ep_buffers* ep_ret = nullptr, unsigned long long* row_dst = nullptr,
+                 bool prequantised = false) {
     int rc = check_cfg(cfg);
+    if (prequantised && (!ext_idx || !ext_scale || cfg->top_k + cfg->num_shared_experts != 1)) return XMOE_ERR_ARG;
     if (ep_ret && (!row_dst || !ext_idx || cfg->top_k + cfg->num_shared_experts != 1)) return XMOE_ERR_ARG;
     if (rc) return rc;
     if (n < 0) return XMOE_ERR_ARG;
@@ -357,7 +359,12 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     q.kb_pad = L.kb_pad;
     q.nt = L.nt;
     q.n_valid = n_valid_dev;
-    if ((rc = launch_act_quant(q, stream))) return rc;
+    if (prequantised) {
+        // x holds NVFP4 packets written by the sending ranks: codes [n, H/2], then block scales [n, H/16]
+        if ((rc = launch_act_repack(x, (const uint8_t*)x + (size_t)n * (H / 2), q, stream))) return rc;
+    } else if ((rc = launch_act_quant(q, stream))) {
+        return rc;
+    }
     prof_mark(4, stream);
 
     if ((rc = run_ff1(w->w13_packed, w->w13_sf, w->w13_gs, b + L.off_xq, b + L.off_sfx, (const float*)scale, counts,
@@ -730,11 +737,19 @@ int xmoe_ep_return(const xmoe_ep_buffers* b, const void* out_rows, const int32_t
 }
 int xmoe_ep_forward_local(const xmoe_ep_buffers* b, const xmoe_config* cfg, const xmoe_weights* w,
                           const int32_t* e_recv, const void* w_recv, const float* act_scale, const int32_t* n_recv_dev,
-                          void* row_dst_scratch, void* workspace, size_t workspace_bytes, xmoe_stream_t stream) {
+                          int32_t quantised_input, void* row_dst_scratch, void* workspace, size_t workspace_bytes,
+                          xmoe_stream_t stream) {
     if (!b || !e_recv || !w_recv || !row_dst_scratch || b->rank < 0 || b->rank >= XMOE_EP_MAX_WORLD) return XMOE_ERR_ARG;
     if (!cfg || cfg->hidden != b->hidden || cfg->num_experts != b->experts_per_rank) return XMOE_ERR_SHAPE;
     return forward_impl(cfg, w, b->recv_x[b->rank], nullptr, e_recv, w_recv, act_scale, b->cap_rows, nullptr, workspace,
-                        workspace_bytes, (cudaStream_t)stream, n_recv_dev, b, (unsigned long long*)row_dst_scratch);
+                        workspace_bytes, (cudaStream_t)stream, n_recv_dev, b, (unsigned long long*)row_dst_scratch,
+                        quantised_input != 0);
+}
+int xmoe_ep_dispatch_quantised(const xmoe_ep_buffers* b, const void* x, const int32_t* topk_idx, const void* topk_w,
+                               const int32_t* topk_off, const int32_t* counts_global, int32_t n_tokens, int32_t top_k,
+                               int32_t idx_stride, float* amax_global, xmoe_stream_t stream) {
+    return launch_ep_dispatch_q(b, x, topk_idx, topk_w, topk_off, counts_global, n_tokens, top_k, idx_stride, amax_global,
+                                (cudaStream_t)stream);
 }
 int xmoe_ep_wait_ret(const xmoe_ep_buffers* b, xmoe_stream_t stream) {
     return launch_ep_wait_ret(b, (cudaStream_t)stream);

@@ -126,6 +126,8 @@ int launch_route_pack_static(PackArgs a, cudaStream_t stream);  // scratch = a f
 int launch_act_amax(const AmaxArgs& a, cudaStream_t stream);
 int launch_act_scale_from_amax(const float* amax, float* scale, cudaStream_t stream);
 int launch_act_quant(const QuantArgs& a, cudaStream_t stream);
+// rows already quantised by a peer: codes [N, H/2] + block scales [N, H/16] -> a.xq / a.sfx (a.x and a.scale unused)
+int launch_act_repack(const void* xq_in, const void* sf_in, const QuantArgs& a, cudaStream_t stream);
 int launch_ff1(const Ff1Args& a, cudaStream_t stream);
 int launch_ff1_prefill(const Ff1Args& a, cudaStream_t stream);
 int launch_ff1_pair(const Ff1Args& a, cudaStream_t stream);  // 256-token tiles on CTA pairs (2-SM MMA)
@@ -141,6 +143,9 @@ int launch_ep_post_counts(const xmoe_ep_buffers* b, const int32_t* counts_global
 int launch_ep_dispatch(const xmoe_ep_buffers* b, const void* x, const int32_t* topk_idx, const void* topk_w,
                        const int32_t* topk_off, const int32_t* counts_global, int n, int top_k, int idx_stride,
                        float* amax_global, cudaStream_t stream);
+int launch_ep_dispatch_q(const xmoe_ep_buffers* b, const void* x, const int32_t* topk_idx, const void* topk_w,
+                         const int32_t* topk_off, const int32_t* counts_global, int n, int top_k, int idx_stride,
+                         float* amax_global, cudaStream_t stream);
 int launch_ep_wait_data(const xmoe_ep_buffers* b, int32_t* e_recv, void* w_recv, int32_t* n_recv, cudaStream_t stream);
 int launch_ep_return(const xmoe_ep_buffers* b, const void* out_rows, const int32_t* topk_row, int expected_rows,
                      cudaStream_t stream);

@@ -219,7 +219,7 @@ class ExpertParallelMoE:
     memory with no host synchronisation; transport="nccl": NCCL all-to-all with host-side counts."""
 
     def __init__(self, shape, checkpoint, group=None, device="cuda", transport: str = "peer",
-                 max_tokens: int = 4096, fused_return: bool = True):
+                 max_tokens: int = 4096, fused_return: bool = True, quantised_dispatch: bool = True):
         from . import ops
         from .synth import scaled_shape
 
@@ -245,6 +245,7 @@ class ExpertParallelMoE:
         self.transport = transport
         self.max_tokens = max_tokens
         self.fused_return = fused_return  # peer transport: FF2 writes its rows into the home ranks' buffers
+        self.quantised_dispatch = quantised_dispatch  # peer transport: tokens travel as NVFP4 packets
         self._row_dst = {}
         self.peer = PeerExchange(shape, self.e_local, max_tokens, torch.device(device), group) \
             if transport == "peer" else None
@@ -307,9 +308,10 @@ class ExpertParallelMoE:
                                        px.pack_status.data_ptr(), st), "xmoe_route_pack")
         _lib.check(lib.xmoe_ep_post_counts(px.ref, px.counts.data_ptr(), scale_local[2:3].data_ptr(), st),
                    "xmoe_ep_post_counts")
-        _lib.check(lib.xmoe_ep_dispatch(px.ref, x.data_ptr(), idx.data_ptr(), w.data_ptr(), px.topk_off.data_ptr(),
-                                        px.counts.data_ptr(), n, k, k, px.amax_global.data_ptr(), st),
-                   "xmoe_ep_dispatch")
+        quantised = self.fused_return and self.quantised_dispatch
+        dispatch = lib.xmoe_ep_dispatch_quantised if quantised else lib.xmoe_ep_dispatch
+        _lib.check(dispatch(px.ref, x.data_ptr(), idx.data_ptr(), w.data_ptr(), px.topk_off.data_ptr(),
+                            px.counts.data_ptr(), n, k, k, px.amax_global.data_ptr(), st), "xmoe_ep_dispatch")
         self._scale = ops.act_scale_from_amax(px.amax_global)
         _lib.check(lib.xmoe_ep_wait_data(px.ref, px.e_recv.data_ptr(), px.w_recv.data_ptr(), px.n_recv.data_ptr(), st),
                    "xmoe_ep_wait_data")
@@ -325,8 +327,8 @@ class ExpertParallelMoE:
                 scratch = self._row_dst[tile] = torch.zeros(rows, dtype=torch.int64, device=x.device)
             _lib.check(lib.xmoe_ep_forward_local(px.ref, C.byref(local.cfg), C.byref(local._wstruct),
                                                  px.e_recv.data_ptr(), px.w_recv.data_ptr(), self._scale.data_ptr(),
-                                                 px.n_recv.data_ptr(), scratch.data_ptr(), ws.data_ptr(), ws.numel(),
-                                                 st), "xmoe_ep_forward_local")
+                                                 px.n_recv.data_ptr(), int(quantised), scratch.data_ptr(), ws.data_ptr(),
+                                                 ws.numel(), st), "xmoe_ep_forward_local")
         else:
             local.forward_routed_rows(px.recv_x, px.e_recv, px.w_recv, act_scale=self._scale, n_valid=px.n_recv)
             ptrs = self._local_ptrs.get(tile)
