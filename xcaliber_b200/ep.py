@@ -244,8 +244,12 @@ class ExpertParallelMoE:
             raise ValueError("transport must be 'peer' or 'nccl'")
         self.transport = transport
         self.max_tokens = max_tokens
-        self.fused_return = fused_return  # peer transport: FF2 writes its rows into the home ranks' buffers
-        self.quantised_dispatch = quantised_dispatch  # peer transport: tokens travel as NVFP4 packets
+        import os
+
+        # peer transport: FF2 writes its rows into the home ranks' buffers / tokens travel as NVFP4 packets
+        # (XMOE_EP_FUSED_RETURN=0 / XMOE_EP_QUANTISED_DISPATCH=0 switch them off for comparisons)
+        self.fused_return = fused_return and os.environ.get("XMOE_EP_FUSED_RETURN", "1") != "0"
+        self.quantised_dispatch = quantised_dispatch and os.environ.get("XMOE_EP_QUANTISED_DISPATCH", "1") != "0"
         self._row_dst = {}
         self.peer = PeerExchange(shape, self.e_local, max_tokens, torch.device(device), group) \
             if transport == "peer" else None
