@@ -190,3 +190,25 @@ def test_tensor_pipe_probe_reports_plausible_rates():
     bf = ops.probe_mma_rate("bf16", 65536)
     # B200 nominal dense rates are 9000 / 2250 TFLOP/s; the probe must land in that neighbourhood
     assert 4000 < nv < 10000 and 1000 < bf < 2600 and 3.0 < nv / bf < 5.0, (nv, bf)
+
+
+@pytest.mark.parametrize("rows,inter,keep", [(300, 2048, 512), (200, 256, 64), (128, 1024, 100), (64, 2048, 1),
+                                             (64, 2048, 2047), (40, 4096, 1000)])
+def test_activation_topk_exact_with_ties(rows, inter, keep):
+    # few distinct magnitudes => many ties at the threshold: survivors must be the lowest indices
+    import ctypes as C
+
+    from xcaliber_b200 import _lib
+
+    g = torch.Generator().manual_seed(1)
+    y = (torch.randn(rows, inter, generator=g) * 4).round().clamp(-20, 20).to(torch.bfloat16)
+    cap = (rows + 127) // 128 * 128
+    counts = torch.tensor([rows], dtype=torch.int32, device="cuda")
+    offsets = torch.tensor([0, cap], dtype=torch.int32, device="cuda")
+    yd = torch.zeros(cap, inter, dtype=torch.bfloat16, device="cuda")
+    yd[:rows] = y.cuda()
+    _lib.check(_lib.lib().xmoe_act_topk(yd.data_ptr(), counts.data_ptr(), offsets.data_ptr(), 1, inter, keep, cap, None),
+               "xmoe_act_topk")
+    torch.cuda.synchronize()
+    ref = O.act_topk_rows(O.bf16_bits(y), keep)
+    np.testing.assert_array_equal(O.bf16_bits(yd[:rows].cpu()), ref)

@@ -58,7 +58,7 @@ int launch_combine(const CombineArgs& a, cudaStream_t stream) {
 // ------------------------------------------------------------------------------------
 constexpr int kTopkThreads = 256;
 
-__global__ __launch_bounds__(kTopkThreads) void act_topk_kernel(uint16_t* __restrict__ yact,
+__global__ __launch_bounds__(kTopkThreads) void act_topk_general_kernel(uint16_t* __restrict__ yact,
                                                                 const int32_t* __restrict__ counts,
                                                                 const int32_t* __restrict__ offsets, int e_tot, int I,
                                                                 int keep) {
@@ -140,10 +140,163 @@ __global__ __launch_bounds__(kTopkThreads) void act_topk_kernel(uint16_t* __rest
     }
 }
 
+
+// Suffix search over a shared-memory histogram by one warp: the largest bucket b (>= 1, or 0) such
+// that the entries in buckets above b number fewer than `keep` while including b reaches it.
+// n_bins = 32 * per_lane. Returns through (bucket, above); all lanes get the same values.
+template <int PER_LANE>
+__device__ __forceinline__ void topk_find_bucket(const int* hist, int keep, int above0, int& bucket, int& above) {
+    const int lane = threadIdx.x & 31;
+    int mine[PER_LANE], tot = 0;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) {
+        mine[j] = hist[lane * PER_LANE + j];
+        tot += mine[j];
+    }
+    // inclusive suffix sum over lanes (lane 31 first)
+    int suf = tot;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_down_sync(0xffffffffu, suf, d);
+        if (lane + d < 32) suf += o;
+    }
+    // the lane whose range holds the threshold: entries above its range < keep <= entries from its range up
+    const int above_lane = above0 + suf - tot;
+    const bool has = above_lane < keep && above_lane + tot >= keep;
+    const unsigned m = __ballot_sync(0xffffffffu, has);
+    int b = 0, ab = above0;
+    if (m) {
+        const int src = 31 - __clz(m);  // highest such lane (unique unless empty ranges tie; take the top one)
+        int b_l = 0, ab_l = above_lane;
+        if (lane == src) {
+            int j = PER_LANE - 1;
+            for (; j > 0; --j) {
+                if (ab_l + mine[j] >= keep) break;
+                ab_l += mine[j];
+            }
+            b_l = lane * PER_LANE + j;
+        }
+        b = __shfl_sync(0xffffffffu, b_l, src);
+        ab = __shfl_sync(0xffffffffu, ab_l, src);
+    } else {
+        // fewer than `keep` entries in all buckets above 0: the threshold is bucket 0
+        int total_above = above0 + __shfl_sync(0xffffffffu, suf, 0) - hist[0];
+        b = 0;
+        ab = total_above;
+    }
+    bucket = b;
+    above = ab;
+}
+
+// Fast path, I <= 2048 and I % 8 == 0: the row lives in registers (8 consecutive entries per thread, so
+// thread order = index order for the tie rule), histogram searches and prefix sums run on warps.
+__global__ __launch_bounds__(kTopkThreads) void act_topk_kernel(uint16_t* __restrict__ yact,
+                                                                const int32_t* __restrict__ counts,
+                                                                const int32_t* __restrict__ offsets, int e_tot, int I,
+                                                                int keep) {
+    __shared__ int hist[256];
+    __shared__ int sel[4];  // bucket, above, threshold, need_equal
+    __shared__ int warp_eq[8];
+    const int r = blockIdx.x;
+    int lo = 0, hi = e_tot;  // largest e with offsets[e] <= r
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (offsets[mid] <= r) lo = mid; else hi = mid;
+    }
+    if (r >= offsets[e_tot] || r - offsets[lo] >= counts[lo]) return;
+    uint4* row4 = reinterpret_cast<uint4*>(yact + (size_t)r * I);
+    const int n_vec = I / 8;
+    const bool mine = (int)threadIdx.x < n_vec;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (mine) v = row4[threadIdx.x];
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    int mag[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        mag[2 * j] = (int)(w[j] & 0x7fffu);
+        mag[2 * j + 1] = (int)((w[j] >> 16) & 0x7fffu);
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    hist[threadIdx.x] = 0;
+    __syncthreads();
+    if (mine) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(&hist[mag[j] >> 7], 1);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int b, ab;
+        topk_find_bucket<8>(hist, keep, 0, b, ab);
+        if (lane == 0) { sel[0] = b; sel[1] = ab; }
+    }
+    __syncthreads();
+    const int bucket = sel[0], above1 = sel[1];
+    __syncthreads();
+    hist[threadIdx.x] = 0;
+    __syncthreads();
+    if (mine) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if ((mag[j] >> 7) == bucket) atomicAdd(&hist[mag[j] & 127], 1);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int b, ab;
+        topk_find_bucket<4>(hist, keep, above1, b, ab);
+        if (lane == 0) { sel[2] = (bucket << 7) | b; sel[3] = keep - ab; }
+    }
+    __syncthreads();
+    const int thr = sel[2], need_equal = sel[3];
+    // entries equal to the threshold: the first need_equal in index order survive
+    int eq = 0;
+    if (mine) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) eq += mag[j] == thr;
+    }
+    int incl = eq;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += o;
+    }
+    if (lane == 31) warp_eq[warp] = incl;
+    __syncthreads();
+    int before = incl - eq;
+    for (int q = 0; q < warp; ++q) before += warp_eq[q];
+    if (!mine) return;
+    int quota = need_equal - before;
+    bool changed = false;
+    uint16_t out[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint16_t raw = (uint16_t)(j & 1 ? w[j >> 1] >> 16 : w[j >> 1] & 0xffffu);
+        bool keep_it = mag[j] > thr;
+        if (mag[j] == thr && quota > 0) {
+            --quota;
+            keep_it = true;
+        }
+        out[j] = keep_it ? raw : (uint16_t)0;
+        changed |= !keep_it && raw != 0;
+    }
+    if (changed) {
+        uint4 o;
+        o.x = out[0] | ((uint32_t)out[1] << 16);
+        o.y = out[2] | ((uint32_t)out[3] << 16);
+        o.z = out[4] | ((uint32_t)out[5] << 16);
+        o.w = out[6] | ((uint32_t)out[7] << 16);
+        row4[threadIdx.x] = o;
+    }
+}
+
 int launch_act_topk(const ActTopkArgs& a, cudaStream_t stream) {
     if (a.keep <= 0 || a.keep >= a.I || a.max_rows <= 0) return XMOE_OK;
-    act_topk_kernel<<<a.max_rows, kTopkThreads, 0, stream>>>((uint16_t*)a.yact, a.counts, a.offsets, a.E_tot, a.I,
-                                                             a.keep);
+    if (a.I <= 8 * kTopkThreads && a.I % 8 == 0)
+        act_topk_kernel<<<a.max_rows, kTopkThreads, 0, stream>>>((uint16_t*)a.yact, a.counts, a.offsets, a.E_tot, a.I,
+                                                                 a.keep);
+    else
+        act_topk_general_kernel<<<a.max_rows, kTopkThreads, 0, stream>>>((uint16_t*)a.yact, a.counts, a.offsets, a.E_tot,
+                                                                         a.I, a.keep);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 
