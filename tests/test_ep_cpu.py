@@ -98,3 +98,14 @@ def test_ep_rank_leaving_is_detected():
         results = mgr.dict()
         mp.spawn(_failing_worker, args=(world, port, results), nprocs=world, join=True)
         assert results[0].startswith("error")
+
+
+def test_local_token_tile_rule():
+    # the owner-side token tile follows the library's own rule applied to the rows a rank expects
+    from xcaliber_b200.ep import local_token_tile
+
+    assert local_token_tile(16 * 2, 4) == 32          # decode: 8 rows per expert
+    assert local_token_tile(128 * 2, 8) == 64         # 32 rows per expert
+    assert local_token_tile(4096 * 2, 4) == 128       # prefill
+    assert local_token_tile(40, 1) == 64              # 40 rows on one expert: between the 20- and 48-row marks
+    assert local_token_tile(60, 1) == 64              # above 48 rows per expert but at most 64 rows in all
