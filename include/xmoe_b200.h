@@ -294,6 +294,17 @@ int xmoe_ep_wait_ret(const xmoe_ep_buffers* b, xmoe_stream_t stream);
 /* Synchronises the stream and returns the sticky XMOE_EP_* bits of this rank's control block (0 = fine). */
 int xmoe_ep_status(const xmoe_ep_buffers* b, xmoe_stream_t stream, uint32_t* bits_out);
 
+/* The step before the layer, done outside the operator in the reference (method.py:255-257 receives
+ * router_logits): logits[n, E] = x[n, H] @ gate_w[E, H]^T, bf16 in, fp32 accumulate, bf16 out, on tcgen05.
+ * H % 64 == 0, E <= 256. status: a device status word as in the workspace (bounded waits report there). */
+int xmoe_gate_logits(const void* x, const void* gate_w, int32_t n_tokens, int32_t hidden, int32_t num_experts,
+                     void* logits, uint32_t* status, xmoe_stream_t stream);
+/* xmoe_forward with the gate GEMM inside: the caller passes x and the router weight; logits_scratch holds
+ * n_tokens * num_experts bf16. */
+int xmoe_forward_gated(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* gate_w,
+                       void* logits_scratch, int32_t n_tokens, void* y, void* workspace, size_t workspace_bytes,
+                       xmoe_stream_t stream);
+
 /* Measurement aid, no reference counterpart: the rate at which this GPU retires tcgen05.mma
  * instructions of the largest shape (M 128, N 256) with operands resident on chip, one issuing
  * thread per SM, n_mma instructions each (rounded down to a multiple of 64; ~100000 runs for a

@@ -212,3 +212,30 @@ def test_activation_topk_exact_with_ties(rows, inter, keep):
     torch.cuda.synchronize()
     ref = O.act_topk_rows(O.bf16_bits(y), keep)
     np.testing.assert_array_equal(O.bf16_bits(yd[:rows].cpu()), ref)
+
+
+@pytest.mark.parametrize("name,n", [("toy", 200), ("toy", 7), ("dsv3s", 300), ("qwen3s", 129)])
+def test_gate_gemm_and_gated_forward(name, n):
+    # the gate GEMM inside the library: logits against an fp32 matmul, then the gated forward must equal
+    # the plain forward fed with those logits, bit for bit
+    shape = {"toy": synth.SHAPES["toy"],
+             "dsv3s": synth.scaled_shape(synth.SHAPES["dsv3"], hidden=512, inter=256, num_experts=64, act_topk_keep=0),
+             "qwen3s": synth.scaled_shape(synth.SHAPES["qwen3"], hidden=512, inter=256, num_experts=128)}[name]
+    from xcaliber_b200 import ops
+
+    w, layer = Hh.build_layer(shape)
+    x, _ = synth.make_inputs(shape, w, n)
+    gw = w.router_weight.to(torch.bfloat16)
+    lg = ops.gate_logits(x.cuda(), gw.cuda()).cpu()
+    ref = (x.float() @ gw.float().T)
+    # bf16 rounding of sums accumulated in another order (and with the tensor core's fp32 alignment): within
+    # two bf16 steps of max(|ref|, rms), and mostly the same bits
+    step = torch.maximum(ref.abs(), ref.pow(2).mean().sqrt()) * 2.0 ** -7
+    assert ((lg.float() - ref).abs() <= step).all()
+    assert (lg == ref.to(torch.bfloat16)).float().mean() > 0.9
+    y = layer.forward_gated(x.cuda(), gw.cuda())
+    torch.cuda.synchronize()
+    assert layer.status(n) == 0
+    assert torch.equal(layer.last_logits.cpu(), lg)
+    y2 = layer.forward(x.cuda(), lg.cuda())
+    assert torch.equal(y, y2)

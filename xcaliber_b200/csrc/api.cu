@@ -63,6 +63,11 @@ int num_sms() {
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// The first KiB of a workspace holds scalars: status word of the layer (word 0), amax scratch, activation
+// scale; word 32 is the status of the gate GEMM when xmoe_forward_gated runs it. The host_io workspace of
+// xmoe_forward_host is read the same way (its gate word is never written and stays as allocated: zeroed here).
+constexpr int kGateStatusWord = 32;
+
 // ---- optional per-stage timing (CUDA events recorded on the caller's stream) -----------
 constexpr int kProfStages = 8;  // router, pack, amax, quant, ff1, act_topk, ff2, combine
 struct Profiler {
@@ -248,7 +253,7 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
                  const int32_t* ext_idx, const void* ext_w, const float* ext_scale, int n, void* y, void* ws,
                  size_t ws_bytes, cudaStream_t stream, const int32_t* n_valid_dev = nullptr,
                  const xmoe_ep_buffers* ep_ret = nullptr, unsigned long long* row_dst = nullptr,
-                 bool prequantised = false) {
+                 bool prequantised = false, bool scalars_precleared = false) {
     int rc = check_cfg(cfg);
     if (prequantised && (!ext_idx || !ext_scale || cfg->top_k + cfg->num_shared_experts != 1)) return XMOE_ERR_ARG;
     if (ep_ret && (!row_dst || !ext_idx || cfg->top_k + cfg->num_shared_experts != 1)) return XMOE_ERR_ARG;
@@ -274,7 +279,8 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     int32_t* offsets = (int32_t*)(b + L.off_offsets);
     const int H = cfg->hidden, I = cfg->inter, E = cfg->num_experts;
 
-    if (cudaMemsetAsync(b, 0, 64, stream) != cudaSuccess) return XMOE_ERR_CUDA;
+    // status words (layer and gate), amax scratch, activation scale
+    if (!scalars_precleared && cudaMemsetAsync(b, 0, 256, stream) != cudaSuccess) return XMOE_ERR_CUDA;
     prof_mark(0, stream);
 
     if (ext_idx) {
@@ -462,6 +468,37 @@ int xmoe_forward_routed_bounded(const xmoe_config* cfg, const xmoe_weights* w, c
                         (cudaStream_t)stream, n_valid_dev);
 }
 
+int xmoe_gate_logits(const void* x, const void* gate_w, int32_t n, int32_t H, int32_t E, void* logits, uint32_t* status,
+                     xmoe_stream_t stream) {
+    if (!x || !gate_w || !logits || !status || n < 0) return XMOE_ERR_ARG;
+    if (H <= 0 || H % 64 || E <= 0 || E > 256) return XMOE_ERR_SHAPE;
+    if (n == 0) return XMOE_OK;
+    const int n_pad = (E + 15) & ~15;
+    const int x_box = n < 128 ? n : 128;
+    const int w_box = E < n_pad ? E : n_pad;
+    CUtensorMap tm_x, tm_w;
+    int rc = make_tmap_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)H, (uint64_t)n, 64, (uint32_t)x_box,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, gate_w, (uint64_t)H, (uint64_t)E, 64, (uint32_t)w_box,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    return launch_gate_logits(tm_x, tm_w, logits, n, E, H, n_pad, x_box, w_box, status, (cudaStream_t)stream);
+}
+
+int xmoe_forward_gated(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* gate_w,
+                       void* logits_scratch, int32_t n, void* y, void* workspace, size_t workspace_bytes,
+                       xmoe_stream_t stream) {
+    if (!cfg || !gate_w || !logits_scratch || !workspace) return XMOE_ERR_ARG;
+    if (n == 0) return XMOE_OK;
+    uint32_t* gate_status = (uint32_t*)workspace + kGateStatusWord;
+    if (cudaMemsetAsync(workspace, 0, 256, (cudaStream_t)stream) != cudaSuccess) return XMOE_ERR_CUDA;
+    int rc = xmoe_gate_logits(x, gate_w, n, cfg->hidden, cfg->num_experts, logits_scratch, gate_status, stream);
+    if (rc) return rc;
+    return forward_impl(cfg, w, x, logits_scratch, nullptr, nullptr, nullptr, n, y, workspace, workspace_bytes,
+                        (cudaStream_t)stream, nullptr, nullptr, nullptr, false, /*scalars_precleared=*/true);
+}
+
 int xmoe_probe_mma_rate(int32_t kind, int32_t n_mma, double* tflops_out, xmoe_stream_t stream) {
     return probe_mma_rate(kind, n_mma, tflops_out, (cudaStream_t)stream);
 }
@@ -526,9 +563,13 @@ int xmoe_forward_host(const xmoe_config* cfg, const xmoe_weights* w, const void*
 int xmoe_read_status(const void* workspace, uint32_t* host_out, xmoe_stream_t stream) {
     if (!workspace || !host_out) return XMOE_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    if (cudaMemcpyAsync(host_out, workspace, 4, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+    // word 0: the layer's kernels; word kGateStatusWord: the gate GEMM of xmoe_forward_gated (the layer clears
+    // only its own word, so a gate failure stays visible)
+    uint32_t words[kGateStatusWord + 1];
+    if (cudaMemcpyAsync(words, workspace, sizeof(words), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
         cudaStreamSynchronize(s) != cudaSuccess)
         return XMOE_ERR_CUDA;
+    *host_out = words[0] ? words[0] : words[kGateStatusWord];
     if (*host_out >= 0x100u && *host_out < 0x600u) return XMOE_ERR_TIMEOUT;
     return XMOE_OK;
 }

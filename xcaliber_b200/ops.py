@@ -177,6 +177,22 @@ class FusedMoE:
                                       n, y.data_ptr(), ws.data_ptr(), ws.numel(), _stream()), "xmoe_forward")
         return y
 
+    def forward_gated(self, x: torch.Tensor, gate_weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """The layer with the router gate GEMM inside: gate_weight bf16 [num_experts, hidden]. The logits it
+        used stay in `self.last_logits` (bf16 [N, num_experts])."""
+        self._check_x(x, None)
+        n = x.shape[0]
+        y = torch.empty_like(x) if out is None else out
+        if n == 0:
+            return y
+        gw = gate_weight.to(torch.bfloat16).contiguous()
+        self.last_logits = torch.empty(n, self.shape.num_experts, dtype=torch.bfloat16, device=x.device)
+        ws = self.workspace(n)
+        check(_lib.lib().xmoe_forward_gated(C.byref(self.cfg), C.byref(self._wstruct), x.data_ptr(), gw.data_ptr(),
+                                            self.last_logits.data_ptr(), n, y.data_ptr(), ws.data_ptr(), ws.numel(),
+                                            _stream()), "xmoe_forward_gated")
+        return y
+
     def forward_routed(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
                        act_scale: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
         """Routing supplied by the caller (the reference's `operator(...)`, xR64ABSBinding.cu:8-121).
@@ -245,6 +261,19 @@ def router_topk(logits: torch.Tensor, shape: MoEShape, weights: "PreparedWeights
                                       _SCORE[shape.scoring], int(shape.renormalize), shape.n_group, shape.topk_group,
                                       shape.routed_scale, idx.data_ptr(), w.data_ptr(), _stream()), "xmoe_router_topk")
     return idx, w
+
+
+def gate_logits(x: torch.Tensor, gate_weight: torch.Tensor) -> torch.Tensor:
+    """Gate GEMM alone: bf16 [N, E] = x [N, H] @ gate_weight [E, H]^T (fp32 accumulation)."""
+    n, h = x.shape
+    e = gate_weight.shape[0]
+    out = torch.empty(n, e, dtype=torch.bfloat16, device=x.device)
+    status = torch.zeros(1, dtype=torch.int32, device=x.device)
+    check(_lib.lib().xmoe_gate_logits(x.data_ptr(), gate_weight.data_ptr(), n, h, e, out.data_ptr(), status.data_ptr(),
+                                      _stream()), "xmoe_gate_logits")
+    if int(status.item()):
+        raise RuntimeError(f"gate GEMM device status {int(status.item()):#x}")
+    return out
 
 
 def act_amax(x: torch.Tensor) -> torch.Tensor:
