@@ -86,7 +86,11 @@ size_t xmoe_workspace_bytes(const xmoe_config* cfg, int32_t n_tokens);
 size_t xmoe_workspace_bytes_host_io(const xmoe_config* cfg, int32_t n_tokens);
 
 /* Replaces _C.forward (xr64_abs_bridge.cu:81-232): router -> route pack -> activation
- * quantise+scatter -> FF1 -> FF2 -> combine, all on `stream`. N == 0 is a no-op. */
+ * quantise+scatter -> FF1 -> FF2 -> combine, ordered on `stream`. N == 0 is a no-op.
+ * For batches of at least 4 M elements the activation amax pass runs on a side stream owned by the
+ * library (one per device, created on the first such call outside stream capture) and is joined before the
+ * quantiser; XMOE_FORK=0 keeps every kernel on the caller's stream. Host threads that drive the same device
+ * concurrently must set it. */
 int xmoe_forward(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* router_logits,
                  int32_t n_tokens, void* y, void* workspace, size_t workspace_bytes, xmoe_stream_t stream);
 

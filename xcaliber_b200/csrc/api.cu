@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/xmoe_b200.h"
 #include "common.cuh"
@@ -62,6 +63,41 @@ int num_sms() {
 }
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// The activation amax pass does not depend on routing: it runs on a side stream of the library,
+// forked after the scalar block is cleared and joined before the quantiser, so that it overlaps the
+// router and the route pack (the reference plans the same overlap with CUDA-graph child graphs,
+// co-design.md:132-158). One non-blocking stream and two events per device, created on first use
+// outside stream capture; XMOE_FORK=0 keeps everything on the caller's stream.
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+SideStream* side_stream(cudaStream_t caller) {
+    static const bool enabled = [] {
+        const char* e = getenv("XMOE_FORK");
+        return !(e && e[0] == '0');
+    }();
+    if (!enabled) return nullptr;
+    constexpr int kMaxDevices = 64;
+    static SideStream per_device[kMaxDevices];
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    SideStream& s = per_device[dev];
+    if (!s.stream) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(caller, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+        if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+            s = SideStream();
+            return nullptr;
+        }
+    }
+    return &s;
+}
 
 // The first KiB of a workspace holds scalars: status word of the layer (word 0), amax scratch, activation
 // scale; word 32 is the status of the gate GEMM when xmoe_forward_gated runs it. The host_io workspace of
@@ -283,6 +319,24 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     if (!scalars_precleared && cudaMemsetAsync(b, 0, 256, stream) != cudaSuccess) return XMOE_ERR_CUDA;
     prof_mark(0, stream);
 
+    // fork: the amax of x overlaps routing (joined before the quantiser)
+    AmaxArgs am;
+    am.x = x;
+    am.n_elems = (size_t)n * H;
+    am.scratch = amax_scratch;
+    am.scale = scale;
+    // worth it only when the pass is long enough to hide: at decode sizes the cross-stream edges cost
+    // more than the few microseconds of amax (measured: 16 tokens 0.203 -> 0.207 ms with the fork)
+    const bool fork_pays = (size_t)n * H >= ((size_t)1 << 22);
+    SideStream* side = (ext_scale || prequantised || !fork_pays) ? nullptr : side_stream(stream);
+    if (side) {
+        if (cudaEventRecord(side->fork, stream) != cudaSuccess ||
+            cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess)
+            return XMOE_ERR_CUDA;
+        if ((rc = launch_act_amax(am, side->stream))) return rc;
+        if (cudaEventRecord(side->join, side->stream) != cudaSuccess) return XMOE_ERR_CUDA;
+    }
+
     if (ext_idx) {
         // caller-supplied routing: widen [N, top_k] to the [N, k_eff] workspace arrays
         if (L.k_eff == cfg->top_k) {  // same row pitch: one flat copy each (a pitched copy of 4-byte rows is slow)
@@ -339,15 +393,12 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     }
     prof_mark(2, stream);
 
-    AmaxArgs am;
-    am.x = x;
-    am.n_elems = (size_t)n * H;
-    am.scratch = amax_scratch;
-    am.scale = scale;
     if (ext_scale) {
         if (cudaMemcpyAsync(scale, ext_scale, 12, cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
             return XMOE_ERR_CUDA;
-    } else if ((rc = launch_act_amax(am, stream))) {
+    } else if (side) {
+        if (cudaStreamWaitEvent(stream, side->join, 0) != cudaSuccess) return XMOE_ERR_CUDA;  // join
+    } else if (!prequantised && (rc = launch_act_amax(am, stream))) {
         return rc;
     }
     prof_mark(3, stream);
