@@ -93,11 +93,43 @@ int launch_act_scale_from_amax(const float* amax, float* scale, cudaStream_t str
 
 // One thread quantises 16 consecutive K of one token (one block scale, 8 packed bytes);
 // a warp covers 512 K. The packet is then stored to each of the token's k_eff rows.
+// FUSED_AMAX (small batches only): every block first takes the amax of the whole of x itself (a few
+// hundred KB, from L2) instead of reading the scale a separate amax kernel left: one launch fewer, same
+// bits (the maximum does not depend on the order). Block 0 publishes {XGS, XGSINV, amax} for FF1.
+template <bool FUSED_AMAX>
 __global__ __launch_bounds__(256) void act_quant_pack_kernel(
-    const uint16_t* __restrict__ x, const ActScale* __restrict__ scale, const int32_t* __restrict__ topk_row,
+    const uint16_t* __restrict__ x, ActScale* __restrict__ scale, const int32_t* __restrict__ topk_row,
     int N, int H, int k_eff, int idx_stride, uint8_t* __restrict__ xq, uint8_t* __restrict__ sfx, int kb_pad,
     int units_per_token, int nt, const int32_t* __restrict__ n_valid) {
-    const float xgs = scale->xgs;
+    float xgs;
+    if (FUSED_AMAX) {
+        __shared__ uint32_t warp_max[8];
+        const size_t n_vec = (size_t)N * H / 8;  // H is a multiple of 16
+        const uint4* xv = reinterpret_cast<const uint4*>(x);
+        uint32_t mx2 = 0u;
+        for (size_t i = threadIdx.x; i < n_vec; i += blockDim.x) {
+            const uint4 v = xv[i];
+            mx2 = __vmaxu2(mx2, v.x & 0x7fff7fffu);
+            mx2 = __vmaxu2(mx2, v.y & 0x7fff7fffu);
+            mx2 = __vmaxu2(mx2, v.z & 0x7fff7fffu);
+            mx2 = __vmaxu2(mx2, v.w & 0x7fff7fffu);
+        }
+        uint32_t mx = max(mx2 & 0xffffu, mx2 >> 16);
+        mx = __reduce_max_sync(0xffffffffu, mx);
+        if (lane_id() == 0) warp_max[threadIdx.x >> 5] = mx;
+        __syncthreads();
+#pragma unroll
+        for (int w = 0; w < 8; ++w) mx = max(mx, warp_max[w]);
+        const float amax = bf16_bits_to_f32(mx);
+        xgs = mx ? 2688.0f / amax : 0.f;
+        if (blockIdx.x == 0 && threadIdx.x == 0) {  // as act_amax_kernel's last block
+            scale->xgs = xgs;
+            scale->xgs_inv = mx ? bf16_bits_to_f32(f32_to_bf16_bits(amax * (1.0f / 2688.0f))) : 0.f;
+            reinterpret_cast<float*>(scale)[2] = amax;
+        }
+    } else {
+        xgs = scale->xgs;
+    }
     const uint32_t lane = lane_id();
     if (n_valid) N = min(N, max(*n_valid, 0));
     const size_t total_units = (size_t)N * units_per_token;
@@ -191,9 +223,14 @@ int launch_act_quant(const QuantArgs& a, cudaStream_t stream) {
     const size_t total = (size_t)a.N * units_per_token;
     size_t blocks = (total + 7) / 8;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    act_quant_pack_kernel<<<(int)blocks, 256, 0, stream>>>((const uint16_t*)a.x, a.scale, a.topk_row, a.N, a.H,
-                                                           a.k_eff, a.idx_stride, (uint8_t*)a.xq, (uint8_t*)a.sfx,
-                                                           a.kb_pad, units_per_token, a.nt, a.n_valid);
+    if (a.fused_amax)
+        act_quant_pack_kernel<true><<<(int)blocks, 256, 0, stream>>>(
+            (const uint16_t*)a.x, const_cast<ActScale*>(a.scale), a.topk_row, a.N, a.H, a.k_eff, a.idx_stride,
+            (uint8_t*)a.xq, (uint8_t*)a.sfx, a.kb_pad, units_per_token, a.nt, a.n_valid);
+    else
+        act_quant_pack_kernel<false><<<(int)blocks, 256, 0, stream>>>(
+            (const uint16_t*)a.x, const_cast<ActScale*>(a.scale), a.topk_row, a.N, a.H, a.k_eff, a.idx_stride,
+            (uint8_t*)a.xq, (uint8_t*)a.sfx, a.kb_pad, units_per_token, a.nt, a.n_valid);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 

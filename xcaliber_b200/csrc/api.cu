@@ -328,6 +328,8 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     // worth it only when the pass is long enough to hide: at decode sizes the cross-stream edges cost
     // more than the few microseconds of amax (measured: 16 tokens 0.203 -> 0.207 ms with the fork)
     const bool fork_pays = (size_t)n * H >= ((size_t)1 << 22);
+    // tiny batches: every block of the quantiser takes the amax of x itself (one launch fewer)
+    const bool fuse_amax = !ext_scale && !prequantised && (size_t)n * H <= ((size_t)1 << 18);
     SideStream* side = (ext_scale || prequantised || !fork_pays) ? nullptr : side_stream(stream);
     if (side) {
         if (cudaEventRecord(side->fork, stream) != cudaSuccess ||
@@ -398,7 +400,7 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
             return XMOE_ERR_CUDA;
     } else if (side) {
         if (cudaStreamWaitEvent(stream, side->join, 0) != cudaSuccess) return XMOE_ERR_CUDA;  // join
-    } else if (!prequantised && (rc = launch_act_amax(am, stream))) {
+    } else if (!prequantised && !fuse_amax && (rc = launch_act_amax(am, stream))) {
         return rc;
     }
     prof_mark(3, stream);
@@ -416,6 +418,7 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     q.kb_pad = L.kb_pad;
     q.nt = L.nt;
     q.n_valid = n_valid_dev;
+    q.fused_amax = fuse_amax;
     if (prequantised) {
         // x holds NVFP4 packets written by the sending ranks: codes [n, H/2], then block scales [n, H/16]
         if ((rc = launch_act_repack(x, (const uint8_t*)x + (size_t)n * (H / 2), q, stream))) return rc;
@@ -770,6 +773,7 @@ int xmoe_act_quant_pack(const void* x, const float* act_scale, const int32_t* to
     q.kb_pad = (int)align_up((size_t)H / 64, 4);
     q.nt = token_tile;
     q.n_valid = nullptr;
+    q.fused_amax = false;
     return launch_act_quant(q, (cudaStream_t)stream);
 }
 

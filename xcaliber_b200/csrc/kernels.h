@@ -62,6 +62,7 @@ struct QuantArgs {
     int kb_pad; // K blocks of 64 per row, rounded up to a multiple of 4
     int nt;     // token tile the scale-factor tiles are laid out for: 32, 64 or 128
     const int32_t* n_valid;  // optional, device: tokens at and beyond *n_valid have no rows and are not scanned
+    bool fused_amax;         // small batches: the kernel takes the amax of x itself and writes *scale (no amax kernel)
 };
 
 struct Ff1Args {
