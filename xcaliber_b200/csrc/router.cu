@@ -133,6 +133,9 @@ __device__ __forceinline__ float unordered_f32(uint32_t o) {
     return __uint_as_float(b);
 }
 
+// J = ceil(E / 32) slots per lane, as a template parameter: the loops over a lane's experts are fully
+// unrolled (keys live in registers), and the DeepSeek-V3 shape (E = 256) needs 8 of them, not 32.
+template <int J>
 __global__ __launch_bounds__(256) void router_topk_grouped_kernel(
     const uint16_t* __restrict__ logits, const float* __restrict__ lut, const float* __restrict__ bias,
     const uint16_t* __restrict__ expert_scale, int32_t* __restrict__ topk_idx, uint16_t* __restrict__ topk_w,
@@ -144,10 +147,10 @@ __global__ __launch_bounds__(256) void router_topk_grouped_kernel(
     const uint32_t gs = (uint32_t)E / (uint32_t)n_group;
 
     // key = {ordered choice score, ~expert}; 0 = absent / dead.
-    uint64_t keys[32];
-    float score[32];
+    uint64_t keys[J];
+    float score[J];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < J; ++j) {
         const uint32_t e = lane + 32u * j;
         keys[j] = 0ull;
         score[j] = 0.f;
@@ -166,14 +169,14 @@ __global__ __launch_bounds__(256) void router_topk_grouped_kernel(
         for (int g = 0; g < n_group; ++g) {
             uint64_t b1 = 0ull;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
+            for (int j = 0; j < J; ++j) {
                 const uint32_t e = lane + 32u * j;
                 if (e < (uint32_t)E && e / gs == (uint32_t)g) b1 = keys[j] > b1 ? keys[j] : b1;
             }
             const uint64_t w1 = warp_max_u64(b1);
             uint64_t b2 = 0ull;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
+            for (int j = 0; j < J; ++j) {
                 const uint32_t e = lane + 32u * j;
                 if (e < (uint32_t)E && e / gs == (uint32_t)g && keys[j] != w1) b2 = keys[j] > b2 ? keys[j] : b2;
             }
@@ -192,7 +195,7 @@ __global__ __launch_bounds__(256) void router_topk_grouped_kernel(
             if (lane == g) gkey = 0ull;
         }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < J; ++j) {
             const uint32_t e = lane + 32u * j;
             if (e < (uint32_t)E && !((allowed >> (e / gs)) & 1u)) keys[j] = 0ull;
         }
@@ -203,13 +206,13 @@ __global__ __launch_bounds__(256) void router_topk_grouped_kernel(
     for (int r = 0; r < topk; ++r) {
         uint64_t best = 0ull;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) best = keys[j] > best ? keys[j] : best;
+        for (int j = 0; j < J; ++j) best = keys[j] > best ? keys[j] : best;
         const uint64_t winner = warp_max_u64(best);
         const uint32_t e = 0xffffffffu - (uint32_t)winner;
         float s = 0.f;
         if ((e & 31u) == lane) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
+            for (int j = 0; j < J; ++j)
                 if ((uint32_t)j == (e >> 5)) {
                     keys[j] = 0ull;
                     s = score[j];
@@ -397,7 +400,12 @@ int launch_router_topk(const RouterArgs& a, cudaStream_t stream) {
         if (a.n_group > 1 && (a.E / a.n_group < 2 || a.topk_group < 1 || a.topk_group > a.n_group ||
                               a.topk > a.topk_group * (a.E / a.n_group)))
             return XMOE_ERR_SHAPE;
-        router_topk_grouped_kernel<<<grid, block, 0, stream>>>(logits, a.lut, a.bias, es, a.topk_idx,
+        if (a.E <= 256)
+            router_topk_grouped_kernel<8><<<grid, block, 0, stream>>>(logits, a.lut, a.bias, es, a.topk_idx,
+                                                               (uint16_t*)a.topk_w, a.N, a.E, a.topk, k_eff,
+                                                               a.n_group, a.topk_group, a.routed_scale, a.renorm);
+        else
+            router_topk_grouped_kernel<32><<<grid, block, 0, stream>>>(logits, a.lut, a.bias, es, a.topk_idx,
                                                                (uint16_t*)a.topk_w, a.N, a.E, a.topk, k_eff,
                                                                a.n_group, a.topk_group, a.routed_scale, a.renorm);
     } else if (a.scoring == 1) {
