@@ -52,6 +52,10 @@ __device__ long long g_ff2_trace[148 * 16];
 
 namespace {
 
+#ifndef XMOE_EXP_DQ
+#define XMOE_EXP_DQ 1
+#endif
+
 constexpr int kBlockM = 128;
 constexpr int kMaxExperts = 1024 + 8;
 constexpr int kTmemCols = 512;
@@ -113,6 +117,24 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ uint4 lds_u128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -271,7 +293,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             constexpr uint32_t idesc = umma_idesc_bf16(kBlockM, NT);
             constexpr int kSlab16 = (NT * 128) >> 4;
             const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(b_base));
-            uint32_t tile_n = 0, it = 0;
+            uint32_t tile_n = 0;
             bool ok = true;
             long long tw_full = 0, tw_adq = 0, tw_acc = 0, t_issue = 0;
             (void)tw_full; (void)tw_adq; (void)tw_acc; (void)t_issue;
@@ -286,8 +308,10 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 tc_fence_after();
                 const uint32_t acc = tmem_base + kAccBase + (as * kIssuers + issuer) * NT;
                 uint32_t first = 1u;
-                for (int ks = 0; ks < k_stages; ++ks, ++it) {
-                    if (kIssuers > 1 && (ks % kIssuers) != issuer) continue;
+                // this thread's K stages of the tile: issuer, issuer + kIssuers, ...
+                const uint32_t tile_it0 = tile_n * (uint32_t)k_stages;
+                for (int ks = issuer; ks < k_stages; ks += kIssuers) {
+                    const uint32_t it = tile_it0 + (uint32_t)ks;
                     const uint32_t s = it % kBStages, ph = (it / kBStages) & 1u;
                     const uint32_t d = it % kARing, dph = (it / kARing) & 1u;
                     {
@@ -403,13 +427,27 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         const int w_stages_per_tile = (k_stages + Cfg::kWUnits - 1) / Cfg::kWUnits;
         uint32_t w_tile_base = 0;  // weight stages consumed by earlier tiles of this CTA
         const __nv_bfloat162 bias = bf162_from_bits(0x43084308u);  // 136.0 twice
-        uint32_t it = 0;
+#if XMOE_EXP_DQ >= 2
+        const uint32_t k_mask = a.nib_mask, k_magic = a.nib_magic;
+#else
+        const uint32_t k_mask = 0x000f000fu, k_magic = 0x43004300u;
+#endif
         bool ok = true;
         long long dq_wfull = 0, dq_wempty = 0, dq_work = 0;  // dq_work includes the wait for the slot
         (void)dq_wfull; (void)dq_wempty; (void)dq_work;
-        for (int item = first_tile; item < total_tiles && ok; item += tile_stride) {
-            for (int ks = 0; ks < k_stages; ++ks, ++it) {
-                if ((int)(it % kDqGroups) != group) continue;
+        // The K stages of all tiles of this CTA are numbered through (it); this group takes
+        // it = group, group + kDqGroups, ... and keeps the stage's position inside its tile (ks)
+        // alongside, so that no warp walks the stages of the other groups.
+        const int my_tiles = first_tile < total_tiles ? (total_tiles - 1 - first_tile) / tile_stride + 1 : 0;
+        const uint32_t total_it = (uint32_t)my_tiles * (uint32_t)k_stages;
+        const uint32_t w_base_u32 = smem_u32(w_base);
+        int ks = group;
+        for (uint32_t it = (uint32_t)group; it < total_it && ok; it += kDqGroups, ks += kDqGroups) {
+            {
+                while (ks >= k_stages) {
+                    ks -= k_stages;
+                    w_tile_base += (uint32_t)w_stages_per_tile;
+                }
                 const uint32_t w_it = w_tile_base + (uint32_t)(ks / Cfg::kWUnits);
                 const int unit = ks % Cfg::kWUnits;  // which K unit of the weight stage
                 const int s = w_it % kWStages;
@@ -422,8 +460,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     XMOE_TACC(dq_wfull);
                 }
                 XMOE_T0();
-                const uint8_t* st = w_base + (size_t)s * Cfg::kWStageBytes;
-                const uint32_t sraw = reinterpret_cast<const uint16_t*>(st + Cfg::kWRawBytes + unit * 256)[row];
+                const uint32_t st = w_base_u32 + (uint32_t)s * Cfg::kWStageBytes;
+                const uint32_t sraw = lds_u16(st + Cfg::kWRawBytes + unit * 256 + row * 2);
                 const __nv_bfloat162 s2 = bf162_from_bits(sraw | (sraw << 16));
                 const uint32_t a_lane = tmem_base + ((uint32_t)(quadrant * 32) << 16) + d * kACols;
 #pragma unroll
@@ -432,13 +470,19 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         const uint32_t chunk = (uint32_t)(unit * (kStageK / 32) + half * 2 + c) ^ swz;
-                        const uint4 r4 = *reinterpret_cast<const uint4*>(st + row * kWRowBytes + chunk * 16);
+                        const uint4 r4 = lds_u128(st + row * kWRowBytes + chunk * 16);
                         const uint32_t words[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
                         for (int w = 0; w < 4; ++w) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
+#if XMOE_EXP_DQ >= 1
+                                const uint32_t sh = j ? (words[w] >> (4 * j)) : words[w];
+                                uint32_t bits;
+                                asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(bits) : "r"(sh), "r"(k_mask), "r"(k_magic));
+#else
                                 const uint32_t bits = ((words[w] >> (4 * j)) & 0x000f000fu) | 0x43004300u;
+#endif
                                 o[(c * 4 + w) * 4 + j] =
                                     bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(bits), bias), s2));
                             }
@@ -450,7 +494,12 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                         if (!mbar_wait(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
                         tc_fence_after();
                     }
+#if XMOE_EXP_DQ >= 3
+                    tmem_st16(a_lane + half * 32, o);
+                    tmem_st16(a_lane + half * 32 + 16, o + 16);
+#else
                     tmem_st32(a_lane + half * 32, o);
+#endif
                 }
                 if (!ok) break;
                 tmem_st_wait();
@@ -465,7 +514,6 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 }
                 XMOE_TACC(dq_work);
             }
-            w_tile_base += (uint32_t)w_stages_per_tile;
         }
         if (warp == Cfg::kFirstDq && lane == 0) {
             XMOE_TDUMP(6, dq_wfull);
@@ -493,7 +541,10 @@ int launch_ff2_nt(const Ff2Args& a, cudaStream_t stream) {
             return XMOE_ERR_CUDA;
         attr_set = true;
     }
-    ff2_w4a16_kernel<NT><<<a.num_sms, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(a);
+    Ff2Args b = a;
+    b.nib_mask = 0x000f000fu;
+    b.nib_magic = 0x43004300u;
+    ff2_w4a16_kernel<NT><<<a.num_sms, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(b);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 
