@@ -52,10 +52,6 @@ __device__ long long g_ff2_trace[148 * 16];
 
 namespace {
 
-#ifndef XMOE_EXP_DQ
-#define XMOE_EXP_DQ 1
-#endif
-
 constexpr int kBlockM = 128;
 constexpr int kMaxExperts = 1024 + 8;
 constexpr int kTmemCols = 512;
@@ -129,13 +125,12 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
+// (x & 0x000f000f) | 0x43004300 as ONE logic instruction: the two bf16 values 128 + nibble. Left
+// to the compiler, the and and the or came out as two instructions per pair.
+__device__ __forceinline__ uint32_t nib_pair_to_bf16_bits(uint32_t x) {
+    uint32_t bits;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(bits) : "r"(x), "r"(0x000f000fu), "r"(0x43004300u));
+    return bits;
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -427,11 +422,6 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         const int w_stages_per_tile = (k_stages + Cfg::kWUnits - 1) / Cfg::kWUnits;
         uint32_t w_tile_base = 0;  // weight stages consumed by earlier tiles of this CTA
         const __nv_bfloat162 bias = bf162_from_bits(0x43084308u);  // 136.0 twice
-#if XMOE_EXP_DQ >= 2
-        const uint32_t k_mask = a.nib_mask, k_magic = a.nib_magic;
-#else
-        const uint32_t k_mask = 0x000f000fu, k_magic = 0x43004300u;
-#endif
         bool ok = true;
         long long dq_wfull = 0, dq_wempty = 0, dq_work = 0;  // dq_work includes the wait for the slot
         (void)dq_wfull; (void)dq_wempty; (void)dq_work;
@@ -476,13 +466,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                         for (int w = 0; w < 4; ++w) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-#if XMOE_EXP_DQ >= 1
-                                const uint32_t sh = j ? (words[w] >> (4 * j)) : words[w];
-                                uint32_t bits;
-                                asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(bits) : "r"(sh), "r"(k_mask), "r"(k_magic));
-#else
-                                const uint32_t bits = ((words[w] >> (4 * j)) & 0x000f000fu) | 0x43004300u;
-#endif
+                                const uint32_t bits = nib_pair_to_bf16_bits(j ? (words[w] >> (4 * j)) : words[w]);
                                 o[(c * 4 + w) * 4 + j] =
                                     bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(bits), bias), s2));
                             }
@@ -494,12 +478,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                         if (!mbar_wait(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
                         tc_fence_after();
                     }
-#if XMOE_EXP_DQ >= 3
-                    tmem_st16(a_lane + half * 32, o);
-                    tmem_st16(a_lane + half * 32 + 16, o + 16);
-#else
                     tmem_st32(a_lane + half * 32, o);
-#endif
                 }
                 if (!ok) break;
                 tmem_st_wait();
@@ -541,10 +520,7 @@ int launch_ff2_nt(const Ff2Args& a, cudaStream_t stream) {
             return XMOE_ERR_CUDA;
         attr_set = true;
     }
-    Ff2Args b = a;
-    b.nib_mask = 0x000f000fu;
-    b.nib_magic = 0x43004300u;
-    ff2_w4a16_kernel<NT><<<a.num_sms, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(b);
+    ff2_w4a16_kernel<NT><<<a.num_sms, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(a);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 

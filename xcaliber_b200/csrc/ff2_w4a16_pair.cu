@@ -81,6 +81,23 @@ __device__ __forceinline__ uint32_t bits_from_bf162(__nv_bfloat162 v) {
     memcpy(&bits, &v, 4);
     return bits;
 }
+__device__ __forceinline__ uint4 lds_u128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+// (x & 0x000f000f) | 0x43004300 as ONE logic instruction: the two bf16 values 128 + nibble. Left
+// to the compiler, the and and the or came out as two instructions per pair.
+__device__ __forceinline__ uint32_t nib_pair_to_bf16_bits(uint32_t x) {
+    uint32_t bits;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(bits) : "r"(x), "r"(0x000f000fu), "r"(0x43004300u));
+    return bits;
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -342,23 +359,23 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
         const uint32_t swz = (uint32_t)(row >> 1) & 3u;  // 64-byte TMA swizzle: 16-byte chunk ^= (row / 2) % 4
         const __nv_bfloat162 bias = bf162_from_bits(0x43084308u);  // 136.0 twice
         const uint32_t leader_adq_full = map_to_cta(smem_u32(&adq_full[0]), 0);
-        uint32_t it = 0;
-        bool ok = true;
-        for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
-            for (int ks = 0; ks < k_stages; ++ks, ++it) {
-                if ((int)(it % kDqGroups) != group) continue;
+        // the K stages of all tiles of this cluster are numbered through; this group takes
+        // it = group, group + kDqGroups, ... without walking the stages of the other groups
+        const int my_tiles = cluster_id < total_tiles ? (total_tiles - 1 - cluster_id) / n_clusters + 1 : 0;
+        const uint32_t total_it = (uint32_t)my_tiles * (uint32_t)k_stages;
+        const uint32_t w_base_u32 = smem_u32(w_base);
+        {
+            for (uint32_t it = (uint32_t)group; it < total_it; it += kDqGroups) {
                 const int s = it % kWStages;
                 const uint32_t ph = (it / kWStages) & 1u;
                 const int d = it % kARing;
                 const uint32_t dph = (it / kARing) & 1u;
                 if (!mbar_wait(&w_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA) ||
-                    !mbar_wait_cluster(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) {
-                    ok = false;
+                    !mbar_wait_cluster(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ))
                     break;
-                }
                 tc_fence_after();
-                const uint8_t* st = w_base + (size_t)s * kWStageBytes;
-                const uint32_t sraw = reinterpret_cast<const uint16_t*>(st + kRawBytes)[row];
+                const uint32_t st = w_base_u32 + (uint32_t)s * kWStageBytes;
+                const uint32_t sraw = lds_u16(st + kRawBytes + row * 2);
                 const __nv_bfloat162 s2 = bf162_from_bits(sraw | (sraw << 16));
                 const uint32_t a_lane = tmem_base + ((uint32_t)(quadrant * 32) << 16) + d * kACols;
 #pragma unroll
@@ -367,13 +384,13 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         const uint32_t chunk = (uint32_t)(half * 2 + c) ^ swz;
-                        const uint4 r4 = *reinterpret_cast<const uint4*>(st + row * 64 + chunk * 16);
+                        const uint4 r4 = lds_u128(st + row * 64 + chunk * 16);
                         const uint32_t words[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
                         for (int w = 0; w < 4; ++w) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-                                const uint32_t bits = ((words[w] >> (4 * j)) & 0x000f000fu) | 0x43004300u;
+                                const uint32_t bits = nib_pair_to_bf16_bits(j ? (words[w] >> (4 * j)) : words[w]);
                                 o[(c * 4 + w) * 4 + j] =
                                     bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(bits), bias), s2));
                             }

@@ -102,7 +102,6 @@ struct Ff2Args {
     int E_tot, H, I, groups;  // groups = ceil(I / 128)
     int nt;
     int num_sms;
-    uint32_t nib_mask, nib_magic;  // set by the launcher (see the dequantiser in ff2_w4a16.cu)
 };
 
 struct CombineArgs {
