@@ -79,8 +79,18 @@ struct Ff2Cfg {
     static constexpr int kWStages = NT == 128 ? 12 : (NT == 64 ? 8 : (NT == 32 ? 10 : 16));  // weight ring (HBM latency)
     static constexpr int kBStages = NT >= 256 ? 4 : (NT >= 128 ? 3 : 4);  // token ring (L2 latency)
     static constexpr int kIssuers = NT <= 64 ? 4 : 1;         // MMA-issuing threads (K stages round-robin)
-    static constexpr int kARing = NT >= 256 ? 8 : (NT >= 64 ? 4 : 6);   // expanded-weight buffers in tensor memory
-    static constexpr int kDqGroups = NT >= 128 ? 4 : 5;                 // independent dequant groups of 4 warps
+    static constexpr int kARing = NT >= 256 ? 8 : 4;          // expanded-weight buffers in tensor memory
+    static constexpr int kDqGroups = 4;                       // independent dequant groups of 4 warps
+    // Ring ownership. The waits are parity waits, and a parity only tells a phase from its
+    // neighbours: a role may wait on a slot only if it took part in that slot's previous phase
+    // (or something else orders it after that phase), otherwise a role that runs ahead reads
+    // "complete" from the phase before last. So every slot of a ring always belongs to the same
+    // role instance: kARing and the weight ring are multiples of kDqGroups (group = stage % 4 owns
+    // tensor-memory slot stage % kARing and always meets the same weight slots), the token ring
+    // and kARing are multiples of kIssuers (issuer = stage-in-tile % 4; tiles whose K stage count
+    // is not a multiple of 4 shift the pairing, but with one accumulator stage every tile starts
+    // with all earlier stages consumed). An earlier build ran 5 groups over 6 slots with 4
+    // issuers: an issuer could pass a slot one phase early when weight stages landed out of order.
     static constexpr int kAccStages = NT == 128 ? 2 : 1;
     static constexpr int kFirstDq = kFirstDqWarp + (kIssuers - 1);
     static constexpr int kThreads = 32 * (kFirstDq + 4 * kDqGroups);
@@ -88,6 +98,10 @@ struct Ff2Cfg {
     static_assert(kAccBase + kAccStages * kIssuers * NT <= kTmemCols, "TMEM budget");
     static_assert(kWStages <= 16 && kBStages <= 8 && kARing <= 8, "barrier arrays");
     static_assert(kThreads <= 1024, "block size");
+    static_assert(kARing % kDqGroups == 0 && (kIssuers == 1 || (kARing % kIssuers == 0 && kBStages % kIssuers == 0)),
+                  "ring ownership");
+    static_assert((kWStages * kWUnits) % kDqGroups == 0, "weight ring ownership");
+    static_assert(kIssuers == 1 || kAccStages == 1, "issuer/slot pairing relies on the per-tile drain");
     static constexpr size_t kSmemBytes =
         1024 + (size_t)kBStages * kBStageBytes + (size_t)kWStages * kWStageBytes + kTailBytes;
     static_assert(kSmemBytes <= 232448, "shared memory");

@@ -51,12 +51,13 @@ constexpr int kStageK = 128;             // one int4 group
 constexpr int kRawBytes = kBlockM * kStageK / 2;
 constexpr int kWStageBytes = kRawBytes + 512;
 constexpr int kBStageBytes = kTokHalf * kStageK * 2;   // 32 KiB: two 128-byte-swizzle slabs
-constexpr int kWStages = 5;
+constexpr int kWStages = 4;  // a multiple of kDqGroups: every weight slot always meets the same group (parity waits)
 constexpr int kBStages = 5;
 constexpr int kACols = kStageK / 2;      // 64
 constexpr int kARing = 4;
 constexpr int kDqGroups = 4;
 constexpr int kAccBase = kARing * kACols;  // 256
+static_assert(kWStages % kDqGroups == 0 && kARing % kDqGroups == 0, "ring slots must stay with one dequant group");
 constexpr int kTmemCols = 512;
 constexpr int kFirstDqWarp = 7;
 constexpr int kThreads = 32 * (kFirstDqWarp + 4 * kDqGroups);  // 736
