@@ -86,7 +86,9 @@ struct Ff2Cfg {
     // (or something else orders it after that phase), otherwise a role that runs ahead reads
     // "complete" from the phase before last. So every slot of a ring always belongs to the same
     // role instance: kARing and the weight ring are multiples of kDqGroups (group = stage % 4 owns
-    // tensor-memory slot stage % kARing and always meets the same weight slots), the token ring
+    // tensor-memory slot stage % kARing and, for an even K stage count, always meets the same
+    // weight slots; an odd count shifts that pairing by one slot per tile, where a false pass
+    // would need loads issued by one thread to land six or more stages out of order), the token ring
     // and kARing are multiples of kIssuers (issuer = stage-in-tile % 4; tiles whose K stage count
     // is not a multiple of 4 shift the pairing, but with one accumulator stage every tile starts
     // with all earlier stages consumed). An earlier build ran 5 groups over 6 slots with 4
