@@ -30,7 +30,10 @@
 
 // A waiting thread parks inside mbarrier.try_wait for up to XMOE_WAIT_HINT_NS (it wakes as soon
 // as the phase completes), so idle roles do not compete for issue slots with the working warps.
-// The number of such parked polls is bounded: worst case ~ XMOE_SPIN_LIMIT * hint = 2.6 s.
+// The number of such parked polls is bounded: at most XMOE_SPIN_LIMIT * hint = 2.6 s. The hint is an
+// upper limit: on B200 a failed try_wait was seen to return after ~0.5 us, so a wait that is never
+// satisfied gives up after ~65 ms at the earliest (the longest legitimate wait, an epilogue warp
+// waiting for a whole decode tile, is ~50 us, a few ms under an instrumenting profiler).
 #ifndef XMOE_WAIT_HINT_NS
 #define XMOE_WAIT_HINT_NS 20000u
 #endif
