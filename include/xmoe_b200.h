@@ -89,8 +89,9 @@ size_t xmoe_workspace_bytes_host_io(const xmoe_config* cfg, int32_t n_tokens);
  * quantise+scatter -> FF1 -> FF2 -> combine, ordered on `stream`. N == 0 is a no-op.
  * For batches of at least 4 M elements the activation amax pass runs on a side stream owned by the
  * library (one per device, created on the first such call outside stream capture) and is joined before the
- * quantiser; XMOE_FORK=0 keeps every kernel on the caller's stream. Host threads that drive the same device
- * concurrently must set it. */
+ * quantiser; XMOE_FORK=0 keeps every kernel on the caller's stream. The side stream and its two events exist
+ * once per device: forward calls on one device must be serialised by the caller (one host thread, or a lock
+ * around the call), or XMOE_FORK=0 must be set. An error return after the fork still joins the side stream. */
 int xmoe_forward(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* router_logits,
                  int32_t n_tokens, void* y, void* workspace, size_t workspace_bytes, xmoe_stream_t stream);
 
@@ -246,7 +247,10 @@ int xmoe_repack_int4_kmajor(const void* w_in, void* out, size_t n_words, xmoe_st
  * stream with no host synchronisation:
  *   xmoe_ep_post_counts -> xmoe_ep_dispatch -> xmoe_ep_wait_data -> xmoe_forward_routed_bounded (y = NULL, n =
  *   cap_rows, top_k = 1, on recv_x[rank]) -> xmoe_ep_return -> xmoe_ep_wait_ret -> xmoe_combine on
- *   ret_rows[rank]. All device-side waits are bounded; xmoe_ep_status reports what went wrong. */
+ *   ret_rows[rank]. All device-side waits are bounded (a few seconds; the environment variable
+ *   XMOE_EP_SPIN_LIMIT, read at every call, gives a smaller number of ~200 ns polls); a wait that runs out
+ *   records XMOE_EP_TIMEOUT and the kernel carries on, so the stream always drains; xmoe_ep_status
+ *   reports what went wrong. */
 #define XMOE_EP_MAX_WORLD 8
 #define XMOE_EP_CTL_BYTES 512
 #define XMOE_EP_TIMEOUT 1u   /* a peer's flag did not arrive within the spin limit */

@@ -32,6 +32,7 @@ import numpy as np
 import torch
 
 E2M1 = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], dtype=np.float32)
+E2M1_SIGNED = np.concatenate([E2M1, -E2M1]).astype(np.float32)   # indexed by the 4-bit code (bit 3 = sign)
 
 
 # ---------------------------------------------------------------------------------------
@@ -266,7 +267,7 @@ def act_quant(x: torch.Tensor, xgs: np.float32):
 
 
 def act_dequant(codes: np.ndarray, s: np.ndarray, xgs_inv: np.float32, with_global: bool = True) -> np.ndarray:
-    val = E2M1[codes & 7] * np.where(codes & 8, -1.0, 1.0).astype(np.float32)
+    val = E2M1_SIGNED[codes & 15]
     n, h = codes.shape
     out = val.reshape(n, h // 16, 16) * ue4m3_decode(s)[:, :, None]
     out = out.reshape(n, h).astype(np.float32)
@@ -306,7 +307,7 @@ def nvfp4_dequant(packed: np.ndarray, scale: np.ndarray, gs=None) -> np.ndarray:
     codes = np.empty((rows, kh * 2), dtype=np.uint8)
     codes[:, 0::2] = packed & 0xF
     codes[:, 1::2] = packed >> 4
-    val = E2M1[codes & 7] * np.where(codes & 8, -1.0, 1.0).astype(np.float32)
+    val = E2M1_SIGNED[codes & 15]
     s = e4m3_decode(scale)
     out = (val.reshape(rows, kh // 8, 16) * s[:, :, None]).reshape(rows, kh * 2).astype(np.float32)
     return out if gs is None else out * np.float32(gs)
@@ -362,6 +363,24 @@ def ff1_rows(w13_packed: np.ndarray, w13_scale: np.ndarray, gs, codes: np.ndarra
     return f32_to_bf16_bits(y.float().numpy())
 
 
+def expert_ff1(xa: torch.Tensor, w13: torch.Tensor, gs, xgs_inv, row_weight: torch.Tensor, shape) -> np.ndarray:
+    """FF1 rows of one expert from dequantised operands, fp32 (xR64FF1.cu:110-130, 356-386): xa f32 [rows, H]
+    (activation codes times block scales, without XGSINV), w13 f32 [2I, H] (without the tensor scales gs) ->
+    bf16 bits [rows, I] of glu(G, U) * routing weight, BEFORE any activation top-k."""
+    i = w13.shape[0] // 2
+    g = (xa @ w13[:i].t()) * (np.float32(gs[0]) * np.float32(xgs_inv))
+    u = (xa @ w13[i:].t()) * (np.float32(gs[1]) * np.float32(xgs_inv))
+    y = glu(g, u, shape.activation, shape.swiglu_alpha, shape.swiglu_limit) * row_weight[:, None]
+    return f32_to_bf16_bits(y.float().numpy())
+
+
+def expert_ff2(yact_bits: np.ndarray, w2: torch.Tensor) -> np.ndarray:
+    """FF2 rows of one expert: bf16 activations [rows, I] (bits) times the bf16-exact weights w2 f32 [H, I],
+    fp32 accumulation, one bf16 round -> bits [rows, H]."""
+    ya = torch.from_numpy(bits_to_f32(yact_bits))
+    return f32_to_bf16_bits((ya @ w2.t()).float().numpy())
+
+
 def act_topk_rows(y_bits: np.ndarray, keep: int) -> np.ndarray:
     """Keep the `keep` largest |y| per row (bf16 magnitudes, ties to the lower index), zero the rest."""
     mag = (y_bits & np.uint16(0x7FFF)).astype(np.int64)
@@ -373,13 +392,41 @@ def act_topk_rows(y_bits: np.ndarray, keep: int) -> np.ndarray:
     return np.where(mask, y_bits, 0).astype(np.uint16)
 
 
+def dense_expert_weights(weights, shape, device=None):
+    """Every expert dequantised once to bf16, as a CPU deployment of the dequantise-then-bf16-matmul path does
+    at load time: list of (w_gate [I,H], w_up [I,H], w_down [H,I]) bf16 CPU tensors with the tensor scales
+    folded in. The arithmetic is plain torch and may run on `device` (e.g. the GPU that synthesised the
+    weights) before the result is moved to the CPU; the values do not depend on where it runs (every product
+    is rounded once, to bf16)."""
+    dev = torch.device(device) if device is not None else weights.w13_packed.device
+    lut = torch.from_numpy(E2M1_SIGNED).to(dev)
+    i = shape.inter
+    out = []
+    for ex in range(shape.e_tot):
+        pk = weights.w13_packed[ex].to(dev)
+        rows, kh = pk.shape
+        val = torch.stack([lut[(pk & 15).long()], lut[(pk >> 4).long()]], dim=-1).reshape(rows, kh // 8, 16)
+        sc = weights.w13_scale[ex].to(dev).contiguous().view(torch.float8_e4m3fn).float()
+        w13 = (val * sc[:, :, None]).reshape(rows, kh * 2)
+        gs = weights.w13_gs[ex].to(dev).float()
+        wg = (w13[:i] * gs[0]).to(torch.bfloat16).cpu()
+        wu = (w13[i:] * gs[1]).to(torch.bfloat16).cpu()
+        q = weights.w2_qweight[ex].to(dev)
+        k8, o = q.shape
+        nib = torch.stack([(q >> (4 * j)) & 0xF for j in range(8)], dim=1).reshape(k8 * 8, o).float() - 8.0
+        s2 = weights.w2_scales[ex].to(dev).float().repeat_interleave(128, dim=0)[: k8 * 8]
+        w2 = (nib * s2).to(torch.bfloat16).t().contiguous().cpu()
+        out.append((wg, wu, w2))
+    return out
+
+
 def layer_forward(x: torch.Tensor, logits: torch.Tensor | None, weights, shape, *, precision: str = "f32",
-                  routing=None, threads: int | None = None):
+                  routing=None, threads: int | None = None, expert_scale: torch.Tensor | None = None, dense=None):
     """Whole layer on the CPU. `weights` is a synth.LayerWeights (checkpoint formats), `shape` a
     synth.MoEShape. precision "f32": exact dequantised values, fp32 matmuls (parity oracle).
     precision "bf16": dequantise to bf16 and use bf16 matmuls (the dequantise-then-bf16-matmul
-    path; used for the timed CPU baseline). Returns dict(y bf16 [N,H], plus routing / packing
-    intermediates)."""
+    path; used for the timed CPU baseline; `dense` = dense_expert_weights(...) skips the per-call
+    dequantisation). Returns dict(y bf16 [N,H], plus routing / packing intermediates)."""
     if threads:
         torch.set_num_threads(threads)
     n, h = x.shape
@@ -388,9 +435,9 @@ def layer_forward(x: torch.Tensor, logits: torch.Tensor | None, weights, shape, 
         idx, w_bits = routing
     elif shape.n_group > 1 or weights.router_bias is not None:
         idx, w_bits, _ = router_topk_grouped(logits, k, shape.n_group, shape.topk_group, weights.router_bias,
-                                             shape.renormalize, shape.routed_scale)
+                                             shape.renormalize, shape.routed_scale, expert_scale)
     else:
-        idx, w_bits, _ = router_topk(logits, k, shape.scoring, shape.renormalize, shape.routed_scale)
+        idx, w_bits, _ = router_topk(logits, k, shape.scoring, shape.renormalize, shape.routed_scale, expert_scale)
     pk = route_pack(idx, w_bits, e, shape.num_shared_experts)
     xgs, xgs_inv = act_scale(x)
     codes, sx = act_quant(x, xgs)
@@ -398,11 +445,14 @@ def layer_forward(x: torch.Tensor, logits: torch.Tensor | None, weights, shape, 
     rows = int(pk["offsets"][-1])
     yact_bits = np.zeros((rows, i), dtype=np.uint16)
     out_rows = np.zeros((rows, h), dtype=np.uint16)
-    w13p = weights.w13_packed.cpu().numpy()
-    w13s = weights.w13_scale.cpu().numpy()
-    w13g = weights.w13_gs.cpu().numpy()
-    w2q = weights.w2_qweight.cpu().numpy()
-    w2s = bf16_bits(weights.w2_scales)
+    if dense is None:
+        w13p = weights.w13_packed.cpu().numpy()
+        w13s = weights.w13_scale.cpu().numpy()
+        w13g = weights.w13_gs.cpu().numpy()
+        w2q = weights.w2_qweight.cpu().numpy()
+        w2s = bf16_bits(weights.w2_scales)
+    else:
+        assert precision == "bf16"
     mm_dtype = torch.bfloat16 if precision == "bf16" else torch.float32
     for ex in range(shape.e_tot):
         c = int(pk["counts"][ex])
@@ -411,23 +461,26 @@ def layer_forward(x: torch.Tensor, logits: torch.Tensor | None, weights, shape, 
         r0 = int(pk["offsets"][ex])
         tok = torch.from_numpy(pk["row_token"][r0:r0 + c].astype(np.int64))
         rw = torch.from_numpy(bits_to_f32(pk["row_weight"][r0:r0 + c]))
-        w13 = torch.from_numpy(nvfp4_dequant(w13p[ex], w13s[ex]))                 # [2I,H] without gs
         xa = xdq[tok]
+        if dense is None:
+            w13 = torch.from_numpy(nvfp4_dequant(w13p[ex], w13s[ex]))             # [2I,H] without gs
         if precision == "bf16":
-            wg = (w13[:i] * float(w13g[ex, 0])).to(mm_dtype)
-            wu = (w13[i:] * float(w13g[ex, 1])).to(mm_dtype)
+            if dense is None:
+                wg = (w13[:i] * float(w13g[ex, 0])).to(mm_dtype)
+                wu = (w13[i:] * float(w13g[ex, 1])).to(mm_dtype)
+            else:
+                wg, wu, _ = dense[ex]
             xb = (xa * float(xgs_inv)).to(mm_dtype)
             g = (xb @ wg.t()).float()
             u = (xb @ wu.t()).float()
+            y = glu(g, u, shape.activation, shape.swiglu_alpha, shape.swiglu_limit) * rw[:, None]
+            yb = f32_to_bf16_bits(y.float().numpy())
         else:
-            g = (xa @ w13[:i].t()) * (np.float32(w13g[ex, 0]) * xgs_inv)
-            u = (xa @ w13[i:].t()) * (np.float32(w13g[ex, 1]) * xgs_inv)
-        y = glu(g, u, shape.activation, shape.swiglu_alpha, shape.swiglu_limit) * rw[:, None]
-        yb = f32_to_bf16_bits(y.float().numpy())
+            yb = expert_ff1(xa, w13, w13g[ex], xgs_inv, rw, shape)
         if shape.act_topk_keep and shape.act_topk_keep < i:
             yb = act_topk_rows(yb, shape.act_topk_keep)
         yact_bits[r0:r0 + c] = yb
-        w2 = torch.from_numpy(int4_dequant_gptq(w2q[ex], w2s[ex]))                # [H, I] bf16-exact
+        w2 = dense[ex][2] if dense is not None else torch.from_numpy(int4_dequant_gptq(w2q[ex], w2s[ex]))  # [H, I]
         ya = torch.from_numpy(bits_to_f32(yb))
         o = (ya.to(mm_dtype) @ w2.to(mm_dtype).t()).float()
         out_rows[r0:r0 + c] = f32_to_bf16_bits(o.numpy())

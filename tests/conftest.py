@@ -13,6 +13,18 @@ ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
+# The oracle allocates and frees many large numpy temporaries. Keep freed blocks inside the heap instead of
+# returning them to the kernel (no mmap for large blocks, no trimming): on hosts where first touch of a page
+# is slow the CPU suite otherwise spends most of its time in page faults.
+try:
+    import ctypes
+
+    _libc = ctypes.CDLL("libc.so.6")
+    _libc.mallopt(-4, 0)          # M_MMAP_MAX = 0
+    _libc.mallopt(-1, 1 << 40)    # M_TRIM_THRESHOLD
+except OSError:
+    pass
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")

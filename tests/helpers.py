@@ -3,6 +3,7 @@ import numpy as np
 import torch
 
 from oracle import moe_oracle as O
+from oracle import stagewise as S
 from xcaliber_b200 import ops, synth
 
 
@@ -10,10 +11,10 @@ def small_shape(name="toy", **kw):
     return synth.scaled_shape(synth.SHAPES[name], **kw)
 
 
-def build_layer(shape, seed=0, token_tile=0):
+def build_layer(shape, seed=0, token_tile=0, expert_scale=None):
     w = synth.make_weights(shape, seed=seed, device="cpu")
     pw = ops.PreparedWeights.from_checkpoint(shape, w.w13_packed, w.w13_scale, w.w13_gs, w.w2_qweight, w.w2_scales,
-                                             router_bias=w.router_bias, device="cuda")
+                                             router_bias=w.router_bias, expert_scale=expert_scale, device="cuda")
     return w, ops.FusedMoE(shape, pw, token_tile=token_tile)
 
 
@@ -21,21 +22,9 @@ def bits(t):
     return O.bf16_bits(t)
 
 
-def assert_routing_equal(view, ref, n):
+def assert_routing_equal(view, ref, n=None):
     """Routing indices, packed rows and counts must be bit-exact."""
-    pk = ref["pack"]
-    np.testing.assert_array_equal(view["topk_idx"].cpu().numpy(), pk["idx"])
-    np.testing.assert_array_equal(view["counts"].cpu().numpy(), pk["counts"])
-    np.testing.assert_array_equal(view["offsets"].cpu().numpy(), pk["offsets"])
-    np.testing.assert_array_equal(view["topk_off"].cpu().numpy(), pk["topk_off"])
-    np.testing.assert_array_equal(view["topk_row"].cpu().numpy(), pk["topk_row"])
-    rows = int(pk["offsets"][-1])
-    live = pk["row_token"] >= 0
-    np.testing.assert_array_equal(view["row_token"].cpu().numpy()[:rows][live], pk["row_token"][live])
-    # gate weights: the reference's own check allows 2^-8 absolute (benchmark.cu:622-624)
-    gw = O.bits_to_f32(bits(view["topk_w"]))
-    ew = O.bits_to_f32(pk["w_bits"])
-    assert np.abs(gw - ew).max() <= 2.0 ** -8
+    S.assert_routing_equal(view, ref["pack"])
 
 
 def valid_row_mask(pk):
@@ -44,3 +33,46 @@ def valid_row_mask(pk):
     for e, c in enumerate(pk["counts"]):
         m[pk["offsets"][e]: pk["offsets"][e] + c] = True
     return m
+
+
+# ---------------------------------------------------------------------------------------
+# Stage-wise parity at checkpoint sizes (the checks themselves live in oracle/stagewise.py)
+# ---------------------------------------------------------------------------------------
+def router_only(w):
+    return synth.LayerWeights(None, None, None, None, None, w.router_weight.cpu(),
+                              None if w.router_bias is None else w.router_bias.cpu(),
+                              None if w.logit_bias is None else w.logit_bias.cpu())
+
+
+def oracle_routing(shape, rw, logits):
+    return S.oracle_routing(shape, rw, logits)
+
+
+def build_layer_on_gpu(shape, seed=0, token_tile=0):
+    """Weights synthesised on the GPU (the same generator bench.py uses); returns (checkpoint tensors on the
+    GPU, router parts on the CPU, layer)."""
+    ckpt = synth.make_weights(shape, seed=seed, device="cuda")
+    pw = ops.PreparedWeights.from_checkpoint(shape, ckpt.w13_packed, ckpt.w13_scale, ckpt.w13_gs, ckpt.w2_qweight,
+                                             ckpt.w2_scales, router_bias=ckpt.router_bias, device="cuda")
+    return ckpt, router_only(ckpt), ops.FusedMoE(shape, pw, token_tile=token_tile)
+
+
+def stagewise_case(shape, ckpt, rw, layer, n, *, seed=0, dense_layer=None, **caps):
+    """One batch of n tokens through `layer`, every stage checked by oracle.stagewise.check_layer_stages.
+    dense_layer: the same weights with the activation top-k off (needed when shape.act_topk_keep > 0)."""
+    x, logits = synth.make_inputs(shape, rw, n, seed=seed)
+    xd, ld = x.cuda(), logits.cuda()
+    y = layer.forward(xd, ld)
+    torch.cuda.synchronize()
+    assert layer.status(n) == 0
+    dview = None
+    if 0 < shape.act_topk_keep < shape.inter:
+        assert dense_layer is not None
+        dense_layer.forward(xd, ld)
+        torch.cuda.synchronize()
+        assert dense_layer.status(n) == 0
+        dview = dense_layer.view(n)
+    view = layer.view(n)
+    res = S.check_layer_stages(shape, ckpt, rw, x, logits, y, view, dense_view=dview, seed=seed, **caps)
+    res.update(y=y, view=view)
+    return res

@@ -91,19 +91,6 @@ def test_qwen3_like_skewed():
     check_stages(shape, 300, y, ref, view)
 
 
-def test_dsv3_like_grouped_shared_topk():
-    shape = synth.scaled_shape(synth.SHAPES["dsv3"], hidden=512, inter=256, num_experts=64, act_topk_keep=64)
-    _, _, _, _, y, ref, view = run_case(shape, 96)
-    pk = ref["pack"]
-    Hh.assert_routing_equal(view, ref, 96)
-    m = Hh.valid_row_mask(pk)
-    ya = Hh.bits(view["yact"])[: len(m)][m]
-    # the kept set can differ where FF1 values tie within rounding; compare support size and values
-    assert ((ya & 0x7FFF) != 0).sum(axis=1).max() <= shape.act_topk_keep
-    mx, mean = O.rel_errors(y.float().cpu(), ref["y"].float())
-    assert mean <= 2 * MEAN_REL, f"layer rel err max {mx:.4g} mean {mean:.4g}"
-
-
 def test_forward_host_matches_device():
     shape = synth.SHAPES["toy"]
     w, layer = Hh.build_layer(shape)

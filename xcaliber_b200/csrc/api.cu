@@ -52,13 +52,12 @@ int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const
     return r == CUDA_SUCCESS ? XMOE_OK : XMOE_ERR_CUDA;
 }
 
-int num_sms() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    }
+int num_sms() {  // of the current device
+    static int n_dev[kMaxDevices] = {};
+    const int dev = device_slot();
+    if (dev < 0) return 148;
+    int& n = n_dev[dev];
+    if (!n && (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)) n = 148;
     return n;
 }
 
@@ -79,7 +78,6 @@ SideStream* side_stream(cudaStream_t caller) {
         return !(e && e[0] == '0');
     }();
     if (!enabled) return nullptr;
-    constexpr int kMaxDevices = 64;
     static SideStream per_device[kMaxDevices];
     static std::mutex mu;
     int dev = -1;
@@ -326,15 +324,30 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     am.scratch = amax_scratch;
     am.scale = scale;
     // worth it only when the pass is long enough to hide: at decode sizes the cross-stream edges cost
-    // more than the few microseconds of amax (measured: 16 tokens 0.203 -> 0.207 ms with the fork)
+    // more than the few microseconds of amax
     const bool fork_pays = (size_t)n * H >= ((size_t)1 << 22);
     // tiny batches: every block of the quantiser takes the amax of x itself (one launch fewer)
     const bool fuse_amax = !ext_scale && !prequantised && (size_t)n * H <= ((size_t)1 << 18);
     SideStream* side = (ext_scale || prequantised || !fork_pays) ? nullptr : side_stream(stream);
+    // Once the side stream has been forked off it is joined again on every way out of this function, error
+    // returns included: a caller that is capturing `stream` into a graph must not be left with an unjoined fork.
+    struct JoinOnExit {
+        SideStream* side = nullptr;
+        cudaStream_t caller = nullptr;
+        void join() {
+            if (!side) return;
+            cudaEventRecord(side->join, side->stream);
+            cudaStreamWaitEvent(caller, side->join, 0);
+            side = nullptr;
+        }
+        ~JoinOnExit() { join(); }
+    } forked;
     if (side) {
         if (cudaEventRecord(side->fork, stream) != cudaSuccess ||
             cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess)
             return XMOE_ERR_CUDA;
+        forked.side = side;
+        forked.caller = stream;
         if ((rc = launch_act_amax(am, side->stream))) return rc;
         if (cudaEventRecord(side->join, side->stream) != cudaSuccess) return XMOE_ERR_CUDA;
     }
@@ -399,7 +412,8 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
         if (cudaMemcpyAsync(scale, ext_scale, 12, cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
             return XMOE_ERR_CUDA;
     } else if (side) {
-        if (cudaStreamWaitEvent(stream, side->join, 0) != cudaSuccess) return XMOE_ERR_CUDA;  // join
+        forked.side = nullptr;  // joined here
+        if (cudaStreamWaitEvent(stream, side->join, 0) != cudaSuccess) return XMOE_ERR_CUDA;
     } else if (!prequantised && !fuse_amax && (rc = launch_act_amax(am, stream))) {
         return rc;
     }

@@ -26,6 +26,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -37,7 +38,7 @@ namespace {
 
 constexpr int kMaxWorld = 8;
 constexpr int kMaxEpExperts = 1024;
-constexpr uint32_t kSpinLimit = 1u << 24;  // x ~200 ns: a few seconds
+constexpr uint32_t kSpinLimit = 1u << 24;  // polls of ~200 ns each: a few seconds (XMOE_EP_SPIN_LIMIT overrides)
 
 struct EpCtl {  // 512 bytes, zero-initialised by the host before the first call
     int32_t counts[kMaxWorld][kMaxWorld];  // [source rank][destination rank] rows
@@ -66,8 +67,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     return v;
 }
 // Bounded wait until *flag has reached `epoch` (wrap-safe).
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* error) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* error, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
         __nanosleep(200);
     }
@@ -81,6 +82,7 @@ struct EpCtx {
     int4* recv_meta[kMaxWorld];   // [cap_rows]: local expert, gate weight bits, home slot, 0
     uint4* ret_rows[kMaxWorld];   // bf16 [ret_cap, H]
     int world, rank, H, experts_per_rank, cap_rows, ret_cap;
+    uint32_t spin_limit;  // polls a flag wait makes before it records XMOE_EP_TIMEOUT and carries on
 };
 
 __global__ __launch_bounds__(256) void ep_post_counts_kernel(EpCtx c, const int32_t* __restrict__ counts_global,
@@ -122,7 +124,7 @@ __global__ __launch_bounds__(256) void ep_dispatch_kernel(EpCtx c, const uint4* 
     __shared__ int pre[kMaxEpExperts];      // rows of earlier experts of the same owner rank (mine only)
     EpCtl* me = c.ctl[c.rank];
     const uint32_t epoch = me->epoch;
-    if (threadIdx.x < c.world) wait_flag(&me->flag_counts[threadIdx.x], epoch, &me->error);
+    if (threadIdx.x < c.world) wait_flag(&me->flag_counts[threadIdx.x], epoch, &me->error, c.spin_limit);
     __syncthreads();
     const int E = c.world * c.experts_per_rank;
     if (threadIdx.x < c.world) {
@@ -191,7 +193,7 @@ __global__ __launch_bounds__(256) void ep_dispatch_q_kernel(EpCtx c, const uint1
     __shared__ float xgs_s;
     EpCtl* me = c.ctl[c.rank];
     const uint32_t epoch = me->epoch;
-    if (threadIdx.x < c.world) wait_flag(&me->flag_counts[threadIdx.x], epoch, &me->error);
+    if (threadIdx.x < c.world) wait_flag(&me->flag_counts[threadIdx.x], epoch, &me->error, c.spin_limit);
     __syncthreads();
     const int E = c.world * c.experts_per_rank;
     if (threadIdx.x < c.world) {
@@ -274,7 +276,7 @@ __global__ __launch_bounds__(256) void ep_wait_data_kernel(EpCtx c, int32_t* __r
     __shared__ int total;
     EpCtl* me = c.ctl[c.rank];
     const uint32_t epoch = me->epoch;
-    if (threadIdx.x < c.world) wait_flag(&me->flag_data[threadIdx.x], epoch, &me->error);
+    if (threadIdx.x < c.world) wait_flag(&me->flag_data[threadIdx.x], epoch, &me->error, c.spin_limit);
     __syncthreads();
     if (threadIdx.x == 0) {
         int s = 0;
@@ -379,7 +381,7 @@ __global__ void ep_signal_ret_kernel(EpCtx c) {
 
 __global__ void ep_wait_ret_kernel(EpCtx c) {
     EpCtl* me = c.ctl[c.rank];
-    if (threadIdx.x < c.world) wait_flag(&me->flag_ret[threadIdx.x], me->epoch, &me->error);
+    if (threadIdx.x < c.world) wait_flag(&me->flag_ret[threadIdx.x], me->epoch, &me->error, c.spin_limit);
 }
 
 int make_ctx(const xmoe_ep_buffers* b, EpCtx* c) {
@@ -400,6 +402,13 @@ int make_ctx(const xmoe_ep_buffers* b, EpCtx* c) {
     c->experts_per_rank = b->experts_per_rank;
     c->cap_rows = b->cap_rows;
     c->ret_cap = b->ret_cap;
+    // XMOE_EP_SPIN_LIMIT (polls, read at every call): lets an operator shorten the few-second default, and
+    // lets a test make a wait on a flag that nobody posts run out within a millisecond
+    c->spin_limit = kSpinLimit;
+    if (const char* env = getenv("XMOE_EP_SPIN_LIMIT")) {
+        const long v = atol(env);
+        if (v > 0 && v <= (long)kSpinLimit) c->spin_limit = (uint32_t)v;
+    }
     return XMOE_OK;
 }
 

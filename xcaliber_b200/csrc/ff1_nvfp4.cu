@@ -260,7 +260,10 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_kernel(const __grid_con
 template <int NT>
 int launch_ff1_nt(const Ff1Args& a, cudaStream_t stream) {
     using Cfg = Ff1Cfg<NT>;
-    static bool attr_set = false;
+    static bool attr_set_dev[kMaxDevices] = {};
+    const int dev = device_slot();
+    if (dev < 0) return XMOE_ERR_CUDA;
+    bool& attr_set = attr_set_dev[dev];
     if (!attr_set) {
         if (cudaFuncSetAttribute(ff1_nvfp4_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)Cfg::kSmemBytes) != cudaSuccess)

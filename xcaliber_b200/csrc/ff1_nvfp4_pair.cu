@@ -317,7 +317,10 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_pair_kernel(const __gri
 
 template <int ACT>
 int launch_pair_act(const Ff1Args& a, cudaStream_t stream) {
-    static bool attr_set = false;
+    static bool attr_set_dev[kMaxDevices] = {};
+    const int dev = device_slot();
+    if (dev < 0) return XMOE_ERR_CUDA;
+    bool& attr_set = attr_set_dev[dev];
     if (!attr_set) {
         if (cudaFuncSetAttribute(ff1_nvfp4_pair_kernel<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kSmemBytes) != cudaSuccess)
@@ -339,7 +342,8 @@ int launch_pair_act(const Ff1Args& a, cudaStream_t stream) {
     // Persistent kernel: launch exactly as many clusters as can be resident at once. Pairs must sit
     // inside one GPC, so this can be fewer than num_sms / 2; extra clusters would run as a second
     // wave and double the kernel time.
-    static int resident_clusters = 0;
+    static int resident_clusters_dev[kMaxDevices] = {};
+    int& resident_clusters = resident_clusters_dev[dev];
     if (!resident_clusters) {
         int n = 0;
         if (cudaOccupancyMaxActiveClusters(&n, ff1_nvfp4_pair_kernel<ACT>, &cfg) != cudaSuccess || n <= 0) n = a.num_sms / 2;

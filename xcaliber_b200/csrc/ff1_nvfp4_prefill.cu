@@ -247,7 +247,10 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_prefill_kernel(const __
 
 template <int ACT>
 int launch_prefill_act(const Ff1Args& a, cudaStream_t stream) {
-    static bool attr_set = false;
+    static bool attr_set_dev[kMaxDevices] = {};
+    const int dev = device_slot();
+    if (dev < 0) return XMOE_ERR_CUDA;
+    bool& attr_set = attr_set_dev[dev];
     if (!attr_set) {
         if (cudaFuncSetAttribute(ff1_nvfp4_prefill_kernel<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kSmemBytes) != cudaSuccess)

@@ -19,9 +19,8 @@
 //               SHORT ring (the activations come from L2)
 //   warps 7..   dequantise (groups of 4 warps, stages round-robin): thread = weight row; the
 //               bf16 pairs go straight to tensor memory with tcgen05.st (lane = row, column =
-//               K pair). Expanded weights never touch shared memory: a first version that
-//               wrote a bf16 tile to shared memory cost 10 B of shared-memory traffic per
-//               weight byte.
+//               K pair). Expanded weights never touch shared memory (a bf16 tile written to
+//               shared memory costs 10 B of shared-memory traffic per weight byte).
 //   warp 1      tcgen05.mma kind::f16 with A from tensor memory, B from shared memory. Token
 //               tiles of 32 / 64 rows add three more issuing warps (7-9; the dequant warps then
 //               start at 10) that take the K stages round-robin into separate accumulators,
@@ -85,14 +84,15 @@ struct Ff2Cfg {
     // neighbours: a role may wait on a slot only if it took part in that slot's previous phase
     // (or something else orders it after that phase), otherwise a role that runs ahead reads
     // "complete" from the phase before last. So every slot of a ring always belongs to the same
-    // role instance: kARing and the weight ring are multiples of kDqGroups (group = stage % 4 owns
-    // tensor-memory slot stage % kARing and, for an even K stage count, always meets the same
-    // weight slots; an odd count shifts that pairing by one slot per tile, where a false pass
-    // would need loads issued by one thread to land six or more stages out of order), the token ring
-    // and kARing are multiples of kIssuers (issuer = stage-in-tile % 4; tiles whose K stage count
-    // is not a multiple of 4 shift the pairing, but with one accumulator stage every tile starts
-    // with all earlier stages consumed). An earlier build ran 5 groups over 6 slots with 4
-    // issuers: an issuer could pass a slot one phase early when weight stages landed out of order.
+    // role instance. All roles number the K stages of a CTA's tiles through with one counter in
+    // which every tile takes k_walk = K stages rounded up to kWUnits slots: with two K units per
+    // weight stage and an odd stage count the last slot of a tile is a PHANTOM stage, walked by
+    // every role with its barrier hand-offs but without loads, expansion or MMAs. Then stage
+    // number = 2 * weight stage + unit, group = stage % 4 owns tensor-memory slot stage % kARing
+    // and always meets the same weight slots (kARing and the weight ring are multiples of
+    // kDqGroups). The token ring and kARing are multiples of kIssuers (issuer = stage-in-tile % 4;
+    // tiles whose stage count is not a multiple of 4 shift that pairing, but with one accumulator
+    // stage every tile starts with all earlier stages consumed).
     static constexpr int kAccStages = NT == 128 ? 2 : 1;
     static constexpr int kFirstDq = kFirstDqWarp + (kIssuers - 1);
     static constexpr int kThreads = 32 * (kFirstDq + 4 * kDqGroups);
@@ -179,6 +179,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
     const int lane = threadIdx.x & 31;
     const int mt_tiles = (a.H + kBlockM - 1) / kBlockM;
     const int k_stages = (a.I + kStageK - 1) / kStageK;
+    // slots per tile in the CTA-wide stage numbering (see "Ring ownership"): slots >= k_stages are phantoms
+    const int k_walk = (k_stages + Cfg::kWUnits - 1) / Cfg::kWUnits * Cfg::kWUnits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kWStages; ++s) {
@@ -274,7 +276,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     if (n_valid <= 8) { tm = &a.tm_y8; box_rows = 8; }
                     else if (n_valid <= 16) { tm = &a.tm_y16; box_rows = 16; }
                 }
-                for (int ks = 0; ks < k_stages; ++ks) {
+                for (int ks = 0; ks < k_walk; ++ks) {
                     {
                         XMOE_T0();
                         if (!mbar_wait(&b_empty[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
@@ -283,11 +285,15 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                         }
                         XMOE_TACC(tw_bprod);
                     }
-                    uint8_t* b = b_base + (size_t)s * Cfg::kBStageBytes;
-                    mbar_expect_tx(&b_full[s], (uint32_t)(box_rows * kStageK * 2));
+                    if (ks < k_stages) {
+                        uint8_t* b = b_base + (size_t)s * Cfg::kBStageBytes;
+                        mbar_expect_tx(&b_full[s], (uint32_t)(box_rows * kStageK * 2));
 #pragma unroll
-                    for (int slab = 0; slab < Cfg::kSlabs; ++slab)
-                        tma_load_2d(b + slab * NT * 128, tm, ks * kStageK + slab * 64, t.row0, &b_full[s]);
+                        for (int slab = 0; slab < Cfg::kSlabs; ++slab)
+                            tma_load_2d(b + slab * NT * 128, tm, ks * kStageK + slab * 64, t.row0, &b_full[s]);
+                    } else {
+                        mbar_arrive(&b_full[s]);  // phantom stage: the hand-off without a load
+                    }
                     if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -320,8 +326,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 const uint32_t acc = tmem_base + kAccBase + (as * kIssuers + issuer) * NT;
                 uint32_t first = 1u;
                 // this thread's K stages of the tile: issuer, issuer + kIssuers, ...
-                const uint32_t tile_it0 = tile_n * (uint32_t)k_stages;
-                for (int ks = issuer; ks < k_stages; ks += kIssuers) {
+                const uint32_t tile_it0 = tile_n * (uint32_t)k_walk;
+                for (int ks = issuer; ks < k_walk; ks += kIssuers) {
                     const uint32_t it = tile_it0 + (uint32_t)ks;
                     const uint32_t s = it % kBStages, ph = (it / kBStages) & 1u;
                     const uint32_t d = it % kARing, dph = (it / kARing) & 1u;
@@ -339,13 +345,15 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     tc_fence_after();
                     const uint32_t a_tmem = tmem_base + d * kACols;
                     const uint32_t b_lo = b_lo0 + s * (uint32_t)(Cfg::kBStageBytes >> 4);
+                    if (ks < k_stages) {  // a phantom stage only passes its slots on
 #pragma unroll
-                    for (int kk = 0; kk < kStageK / 16; ++kk) {
-                        // slab kk/4 (64 K each), 32 bytes of K per MMA inside the 128-byte swizzle row
-                        mma_bf16_ts_lo(acc, a_tmem + kk * 8, b_lo + (kk >> 2) * kSlab16 + (kk & 3) * 2, idesc,
-                                       (kk | (int)(first ^ 1u)) ? 1u : 0u);
+                        for (int kk = 0; kk < kStageK / 16; ++kk) {
+                            // slab kk/4 (64 K each), 32 bytes of K per MMA inside the 128-byte swizzle row
+                            mma_bf16_ts_lo(acc, a_tmem + kk * 8, b_lo + (kk >> 2) * kSlab16 + (kk & 3) * 2, idesc,
+                                           (kk | (int)(first ^ 1u)) ? 1u : 0u);
+                        }
+                        first = 0u;
                     }
-                    first = 0u;
                     tc_commit(&b_empty[s]);
                     tc_commit(&adq_empty[d]);
                     XMOE_TACC(t_issue);
@@ -435,7 +443,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         constexpr int kWRowBytes = Cfg::kWRowBytes;
         const uint32_t swz = kWRowBytes == 128 ? ((uint32_t)row & 7u)
                                                : (kWRowBytes == 64 ? ((uint32_t)(row >> 1) & 3u) : ((uint32_t)(row >> 2) & 1u));
-        const int w_stages_per_tile = (k_stages + Cfg::kWUnits - 1) / Cfg::kWUnits;
+        const int w_stages_per_tile = k_walk / Cfg::kWUnits;
         uint32_t w_tile_base = 0;  // weight stages consumed by earlier tiles of this CTA
         const __nv_bfloat162 bias = bf162_from_bits(0x43084308u);  // 136.0 twice
         bool ok = true;
@@ -445,13 +453,13 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         // it = group, group + kDqGroups, ... and keeps the stage's position inside its tile (ks)
         // alongside, so that no warp walks the stages of the other groups.
         const int my_tiles = first_tile < total_tiles ? (total_tiles - 1 - first_tile) / tile_stride + 1 : 0;
-        const uint32_t total_it = (uint32_t)my_tiles * (uint32_t)k_stages;
+        const uint32_t total_it = (uint32_t)my_tiles * (uint32_t)k_walk;
         const uint32_t w_base_u32 = smem_u32(w_base);
         int ks = group;
         for (uint32_t it = (uint32_t)group; it < total_it && ok; it += kDqGroups, ks += kDqGroups) {
             {
-                while (ks >= k_stages) {
-                    ks -= k_stages;
+                while (ks >= k_walk) {
+                    ks -= k_walk;
                     w_tile_base += (uint32_t)w_stages_per_tile;
                 }
                 const uint32_t w_it = w_tile_base + (uint32_t)(ks / Cfg::kWUnits);
@@ -464,6 +472,16 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     XMOE_T0();
                     if (!mbar_wait(&w_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
                     XMOE_TACC(dq_wfull);
+                }
+                if (ks >= k_stages) {
+                    // phantom stage (odd K-unit count): keep this group's place in both rings, expand nothing
+                    if (!mbar_wait(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&adq_full[d]);
+                        mbar_arrive(&w_empty[s]);
+                    }
+                    continue;
                 }
                 XMOE_T0();
                 const uint32_t st = w_base_u32 + (uint32_t)s * Cfg::kWStageBytes;
@@ -503,9 +521,6 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 if (lane == 0) {
                     mbar_arrive(&adq_full[d]);
                     mbar_arrive(&w_empty[s]);
-                    // an odd K-unit count leaves the tile's last weight stage half used: release
-                    // it on behalf of the unit that does not exist
-                    if (Cfg::kWUnits == 2 && ks == k_stages - 1 && unit == 0) mbar_arrive(&w_empty[s]);
                 }
                 XMOE_TACC(dq_work);
             }
@@ -529,7 +544,10 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
 template <int NT>
 int launch_ff2_nt(const Ff2Args& a, cudaStream_t stream) {
     using Cfg = Ff2Cfg<NT>;
-    static bool attr_set = false;
+    static bool attr_set_dev[kMaxDevices] = {};
+    const int dev = device_slot();
+    if (dev < 0) return XMOE_ERR_CUDA;
+    bool& attr_set = attr_set_dev[dev];
     if (!attr_set) {
         if (cudaFuncSetAttribute(ff2_w4a16_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)Cfg::kSmemBytes) != cudaSuccess)

@@ -429,7 +429,10 @@ extern "C" int xmoe_ff2_pair_trace_dump(long long* host_out) {
 #endif
 
 int launch_ff2_pair(const Ff2Args& a, cudaStream_t stream) {
-    static bool attr_set = false;
+    static bool attr_set_dev[kMaxDevices] = {};
+    const int dev = device_slot();
+    if (dev < 0) return XMOE_ERR_CUDA;
+    bool& attr_set = attr_set_dev[dev];
     if (!attr_set) {
         if (cudaFuncSetAttribute(ff2_w4a16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kSmemBytes) != cudaSuccess)
@@ -451,7 +454,8 @@ int launch_ff2_pair(const Ff2Args& a, cudaStream_t stream) {
     // Persistent kernel: launch exactly as many clusters as can be resident at once. Pairs must sit
     // inside one GPC, so this can be fewer than num_sms / 2; extra clusters would run as a second
     // wave and double the kernel time.
-    static int resident_clusters = 0;
+    static int resident_clusters_dev[kMaxDevices] = {};
+    int& resident_clusters = resident_clusters_dev[dev];
     if (!resident_clusters) {
         int n = 0;
         if (cudaOccupancyMaxActiveClusters(&n, ff2_w4a16_pair_kernel, &cfg) != cudaSuccess || n <= 0) n = a.num_sms / 2;

@@ -125,7 +125,10 @@ int launch_gate_logits(const CUtensorMap& tm_x, const CUtensorMap& tm_w, void* l
                        int x_box_rows, int w_box_rows, uint32_t* status, cudaStream_t stream) {
     if (n <= 0) return XMOE_OK;
     const size_t smem = 1024 + (size_t)kGateStages * (kGateABytes + (size_t)n_pad * 128) + 256;
-    static size_t configured = 0;
+    static size_t configured_dev[kMaxDevices] = {};
+    const int dev = device_slot();
+    if (dev < 0) return XMOE_ERR_CUDA;
+    size_t& configured = configured_dev[dev];
     if (smem > configured) {
         if (cudaFuncSetAttribute(gate_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return XMOE_ERR_CUDA;

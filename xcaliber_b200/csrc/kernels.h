@@ -12,6 +12,16 @@
 
 namespace xmoe {
 
+// Function attributes, occupancy answers and SM counts belong to a DEVICE, not to the process: a host
+// that drives several GPUs sets and caches them once per device. Caches are arrays indexed by this slot
+// (-1: no current device or an ordinal beyond kMaxDevices, reported as XMOE_ERR_CUDA by the callers).
+constexpr int kMaxDevices = 64;
+inline int device_slot() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    return dev;
+}
+
 struct RouterArgs {
     const void* logits;        // bf16 [N, E]
     const float* lut;          // fp32 [65536] sigmoid table (grouped mode only)

@@ -1,55 +1,41 @@
 // NVFP4 activation quantisation, the arithmetic shared by the local quantise-and-pack kernel and
-// the expert-parallel dispatch that quantises on the sending GPU. Same operations, in the same
-// order, as the reference's moe_ue4m3_ceil / moe_ue4m3_f32 / moe_e2m1x2_bf16x2 and its packing loop
-// (sm120a/preamble.cuh:17-66, 567-599): block scale = round-up UE4M3 of amax * XGS / 6, values
-// multiplied by bf16(XGS / decoded scale) in bf16, then round-to-nearest saturating E2M1.
+// the expert-parallel dispatch that quantises on the sending GPU. The results are, bit for bit,
+// those of the reference's quantiser (sm120a/preamble.cuh:17-66, 567-599): block scale = UE4M3 of
+// amax * XGS / 6 rounded UP, values multiplied by bf16(XGS / decoded scale) with the product
+// rounded to bf16, then round-to-nearest-even saturating E2M1. The formulation is this library's:
+// the UE4M3 code is read off the fp32 bit pattern (a UE4M3 normal is an fp32 with the low 20
+// mantissa bits dropped and the exponent re-biased by 120, so code = (bits >> 20) - 960), and the
+// E2M1 conversion goes through the cuda_fp4.h conversion intrinsic.
 #pragma once
+
+#include <cuda_fp4.h>
 
 #include "common.cuh"
 
 namespace xmoe {
 
+constexpr uint32_t kUe4m3Rebias = 120u << 3;  // fp32 exponent 127 against UE4M3 bias 7, in units of 1/8 octave
+constexpr uint32_t kUe4m3Max = 0x7eu;         // 448
+
+// Smallest UE4M3 value >= x (x finite, fp32), saturating at 448. Below the normal range (x < 2^-6) the
+// code counts 1/512 steps and stops at 7, the largest subnormal.
 __device__ __forceinline__ uint32_t ue4m3_ceil(float x) {
     if (!(x > 0.0f)) return 0u;
-    if (x >= 448.0f) return 0x7eu;
     const uint32_t bits = __float_as_uint(x);
-    int e = int((bits >> 23) & 0xffu) - 120;
-    if (e <= 0) {
-        const uint32_t m = __float2uint_ru(x * 512.0f);
-        return m > 7u ? 7u : m;
-    }
-    uint32_t m = (bits >> 20) & 7u;
-    m += (bits & 0x000fffffu) != 0u;
-    if (m == 8u) {
-        m = 0u;
-        e++;
-    }
-    if (e >= 15) return m > 6u ? 0x7eu : (0x78u | m);
-    return (uint32_t(e) << 3) | m;
+    if (bits < (121u << 23)) return min(7u, (uint32_t)ceilf(x * 512.0f));
+    // adding the dropped bits' all-ones pattern before the shift rounds the 3-bit mantissa up and
+    // carries into the exponent on its own
+    return min(((bits + 0x000fffffu) >> 20) - kUe4m3Rebias, kUe4m3Max);
 }
 __device__ __forceinline__ float ue4m3_decode(uint32_t s) {
-    const uint32_t e = s >> 3, m = s & 7u;
-    if (!e) return float(m) * (1.0f / 512.0f);
-    return __uint_as_float(((e + 120u) << 23) | (m << 20));
+    return s < 8u ? (float)s * 0x1p-9f : __uint_as_float((s + kUe4m3Rebias) << 20);
 }
-// two bf16 (packed) times a packed bf16 scale, product rounded to bf16, then RN-satfinite E2M1.
+// Two packed bf16 values times a packed bf16 scale -> one byte of two E2M1 codes (low nibble = the low
+// half). The product is rounded to bf16 first, as the reference does with mul.rn.bf16x2.
 __device__ __forceinline__ uint32_t e2m1x2(uint32_t x2, uint32_t scale2) {
-    uint32_t q;
-    asm("{\n\t"
-        ".reg .b32 y;\n\t"
-        ".reg .b16 lo, hi;\n\t"
-        ".reg .f32 flo, fhi;\n\t"
-        ".reg .b8 z;\n\t"
-        "mul.rn.bf16x2 y, %1, %2;\n\t"
-        "mov.b32 {lo, hi}, y;\n\t"
-        "cvt.f32.bf16 flo, lo;\n\t"
-        "cvt.f32.bf16 fhi, hi;\n\t"
-        "cvt.rn.satfinite.e2m1x2.f32 z, fhi, flo;\n\t"
-        "cvt.u32.u8 %0, z;\n\t"
-        "}"
-        : "=r"(q)
-        : "r"(x2), "r"(scale2));
-    return q;
+    const __nv_bfloat162 prod = __hmul2(reinterpret_cast<const __nv_bfloat162&>(x2),
+                                        reinterpret_cast<const __nv_bfloat162&>(scale2));
+    return (uint32_t)__nv_cvt_float2_to_fp4x2(__bfloat1622float2(prod), __NV_E2M1, cudaRoundNearest);
 }
 
 // 16 consecutive bf16 values (8 packed words) of one token -> block-scale byte and 8 bytes of E2M1

@@ -370,7 +370,9 @@ __global__ __launch_bounds__(256) void route_scatter_kernel(
                 topk_idx[(size_t)t * idx_stride + lane] = e;
                 topk_w[(size_t)t * idx_stride + lane] = w;
             }
-            if (e >= 0 && e < e_tot) {
+            // a caller slot is valid under the same test as the histograms (ids in [E, e_tot) belong to the
+            // shared experts' own slots and were never counted for a caller slot)
+            if (e >= 0 && e < (lane < topk ? E : e_tot)) {
                 const int p = warp_base[warp][e];
                 warp_base[warp][e] = p + 1;
                 const int r = start[e] + p;
@@ -458,10 +460,9 @@ int launch_route_pack_static(PackArgs a, cudaStream_t stream) {
     if (a.E + a.n_shared > kMaxEtot) return XMOE_ERR_LIMIT;
     // In host code the array's name is not a device address. Ask the runtime for the address
     // once per device, with that device current, and hand the kernels the result.
-    constexpr int kMaxDevices = 64;
     static int32_t* device_ptr[kMaxDevices] = {};
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return XMOE_ERR_CUDA;
+    const int dev = device_slot();
+    if (dev < 0) return XMOE_ERR_CUDA;
     if (device_ptr[dev] == nullptr) {
         void* p = nullptr;
         if (cudaGetSymbolAddress(&p, g_static_pack_scratch) != cudaSuccess || p == nullptr) return XMOE_ERR_CUDA;

@@ -7,7 +7,8 @@ weight on the input, parallel sizes other than expert parallelism must be 1. Wei
 vLLM's compressed-tensors NVFP4 parameter set (w13_weight_packed u8 [E, 2I, H/2],
 w13_weight_scale e4m3 [E, 2I, H/16], w13_weight_global_scale f32 [E, 2], w2_* likewise); FF1
 uses them as they are, FF2 is converted once at load time to int4 group-128 for the W4A16
-down projection.
+down projection. At run time the layer goes through the registered PyTorch custom op
+`torch.ops.xmoe_b200.forward` (torch_ops.py), the counterpart of the reference's `_C.forward`.
 """
 from __future__ import annotations
 
@@ -16,7 +17,7 @@ from vllm.model_executor.layers.quantization.compressed_tensors.compressed_tenso
     CompressedTensorsW4A4Nvfp4MoEMethod,
 )
 
-from .. import ops, synth
+from .. import ops, synth, torch_ops
 
 _ACTIVATIONS = {"silu": "silu", "swigluoai": "swiglu_clamp", "gelu_tanh": "gelu_tanh"}
 
@@ -28,6 +29,22 @@ def _nvfp4_to_float(packed: torch.Tensor, scale_e4m3: torch.Tensor, dequant_gs: 
     vals = torch.stack([lut[lo], lut[hi]], dim=-1).reshape(packed.shape[0], -1)
     s = scale_e4m3.view(torch.float8_e4m3fn).float().repeat_interleave(16, dim=1)
     return vals * s * dequant_gs
+
+
+def convert_w2_nvfp4_to_int4(w2_packed: torch.Tensor, w2_scale: torch.Tensor, w2_dequant_gs: torch.Tensor):
+    """The down projection of an NVFP4 checkpoint -> the int4 group-128 contract of the W4A16 kernel (GPTQ
+    packing, xR64ABSRepack.cu:3-24): u8 [E, H, I/2] + e4m3 [E, H, I/16] + f32 [E] -> (qweight i32 [E, I/8, H],
+    scales bf16 [E, ceil(I/128), H]). One expert at a time (the float copy of an expert is transient)."""
+    e, h, half_i = w2_packed.shape
+    i = half_i * 2
+    dev = w2_packed.device
+    w2_q = torch.empty(e, i // 8, h, dtype=torch.int32, device=dev)
+    w2_s = torch.empty(e, (i + 127) // 128, h, dtype=torch.bfloat16, device=dev)
+    for ex in range(e):
+        wf = _nvfp4_to_float(w2_packed[ex], w2_scale[ex], w2_dequant_gs[ex])
+        q, s = synth.quantize_int4_g128(wf.unsqueeze(0))
+        w2_q[ex], w2_s[ex] = q[0], s[0]
+    return w2_q, w2_s
 
 
 class XCaliberB200NVFP4MoE(CompressedTensorsW4A4Nvfp4MoEMethod):
@@ -86,12 +103,7 @@ class XCaliberB200NVFP4MoE(CompressedTensorsW4A4Nvfp4MoEMethod):
         # compressed-tensors stores the quantisation multiplier; the kernels want the dequant one
         w13_gs = (1.0 / layer.w13_weight_global_scale.data.float()).reshape(e, 2)
         w2_gs = (1.0 / layer.w2_weight_global_scale.data.float()).reshape(e)
-        w2_q = torch.empty(e, i // 8, h, dtype=torch.int32, device=dev)
-        w2_s = torch.empty(e, (i + 127) // 128, h, dtype=torch.bfloat16, device=dev)
-        for ex in range(e):
-            wf = _nvfp4_to_float(layer.w2_weight_packed.data[ex], layer.w2_weight_scale.data[ex], w2_gs[ex])
-            q, s = synth.quantize_int4_g128(wf.unsqueeze(0))
-            w2_q[ex], w2_s[ex] = q[0], s[0]
+        w2_q, w2_s = convert_w2_nvfp4_to_int4(layer.w2_weight_packed.data, layer.w2_weight_scale.data, w2_gs)
         pw = ops.PreparedWeights.from_checkpoint(
             shape, layer.w13_weight_packed.data, layer.w13_weight_scale.data.view(torch.uint8), w13_gs, w2_q, w2_s,
             router_bias=None if bias is None else bias.data, expert_scale=getattr(layer, "_xcaliber_per_expert_scale", None),
@@ -107,9 +119,9 @@ class XCaliberB200NVFP4MoE(CompressedTensorsW4A4Nvfp4MoEMethod):
             raise RuntimeError("weights were not post-processed: process_weights_after_loading has not run")
         if x.numel() == 0:
             return torch.empty_like(x)
-        xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
-        y = self._xc_layer.forward(xb.contiguous(), router_logits.to(torch.bfloat16).contiguous())
-        return y if y.dtype == x.dtype else y.to(x.dtype)
+        # the registered custom op (torch.ops.xmoe_b200.forward): output and scratch come from torch's allocator
+        # inside the op, fp16 activations are served in bf16 there, as in the reference's bridge
+        return torch_ops.forward(self._xc_layer, x.contiguous(), router_logits.to(torch.bfloat16).contiguous())
 
     def apply(self, *args, **kwargs):
         raise RuntimeError("xcaliber_b200 fused MoE is monolithic: the runner must call apply_monolithic")
