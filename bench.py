@@ -357,33 +357,68 @@ def main() -> int:
     ms_step = ms_total / args.steps
     value = n * world / (ms_step * 1e-3)
 
-    # ---- end to end: host buffers in, host buffer out, copies inside the timed region
+    # ---- end to end: host buffers in, host buffer out, copies inside the timed region. Every step copies its
+    # inputs from pinned host memory and its result back. `serial`: one synchronous call after the other
+    # (xmoe_forward_host). `value`: the serving loop, E2E_DEPTH calls in flight, each on its own stream with its
+    # own workspace and host buffers (xmoe_forward_host_async), so that one call's PCIe copies overlap another's
+    # kernels; a slot is reused only after its previous call has been synchronised.
+    E2E_DEPTH = 3
     xh, lh = x_cpu.pin_memory(), logits_cpu.pin_memory()
     yh = torch.empty_like(x_cpu).pin_memory()
-    if world > 1:
-        def e2e_step():
-            x.copy_(xh, non_blocking=True)
-            logits.copy_(lh, non_blocking=True)
-            yh.copy_(layer.forward(x, logits), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-    else:
-        def e2e_step():
-            layer.forward_host(xh, lh, yh)
     e2e_steps = 0 if args.no_e2e else args.steps
-    for _ in range(3 if e2e_steps else 0):
-        e2e_step()
-    sync_all()
-    ev0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    ev1.record()
-    sync_all()
-    e2e_ms = ev0.elapsed_time(ev1) if e2e_steps else float("nan")
+
+    def timed(run_steps):
+        if not e2e_steps:
+            return float("nan")
+        sync_all()
+        ev0.record()
+        run_steps(e2e_steps)
+        ev1.record()
+        sync_all()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
     if world > 1:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+        def serial_steps(k):
+            for _ in range(k):
+                x.copy_(xh, non_blocking=True)
+                logits.copy_(lh, non_blocking=True)
+                yh.copy_(layer.forward(x, logits), non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+        pipelined_steps = None
+    else:
+        def serial_steps(k):
+            for _ in range(k):
+                layer.forward_host(xh, lh, yh)
+
+        slots = [(torch.cuda.Stream(device=dev), x_cpu.pin_memory(), logits_cpu.pin_memory(),
+                  torch.empty_like(x_cpu).pin_memory()) for _ in range(E2E_DEPTH)]
+
+        def pipelined_steps(k):
+            cur = torch.cuda.current_stream()
+            for st, *_ in slots:
+                st.wait_stream(cur)
+            for i in range(k):
+                st, xs, ls, ys = slots[i % E2E_DEPTH]
+                st.synchronize()  # the slot's previous call is complete: its result may be read, its buffers reused
+                layer.forward_host_async(xs, ls, ys, slot=i % E2E_DEPTH, stream=st)
+            for st, *_ in slots:
+                cur.wait_stream(st)
+
+    if e2e_steps:
+        serial_steps(3)
+        if pipelined_steps:
+            pipelined_steps(2 * E2E_DEPTH)
+    e2e_serial_ms = timed(serial_steps)
+    e2e_ms = timed(pipelined_steps) if pipelined_steps else e2e_serial_ms
     e2e_value = n * world / (e2e_ms / args.steps * 1e-3) if e2e_steps else None
+    e2e_serial_value = n * world / (e2e_serial_ms / args.steps * 1e-3) if e2e_steps else None
+    if e2e_steps and pipelined_steps and not torch.equal(slots[0][3], yh):
+        raise RuntimeError("pipelined host-buffer calls returned a different result than the synchronous call")
     h2d = x_cpu.numel() * 2 + logits_cpu.numel() * 2
     d2h = x_cpu.numel() * 2
 
@@ -495,7 +530,8 @@ def main() -> int:
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "nvfp4 x nvfp4 (FF1), int4 x bf16 (FF2), fp32 accumulate",
                 "data": "synthetic", "config": config, "clocks": clocks,
-                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "calls_in_flight": E2E_DEPTH if world == 1 else 1, "serial_value": e2e_serial_value},
                 "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline,
                 "device_status": statuses, **parity, **extra}
         if decode is not None:

@@ -68,6 +68,7 @@ SIGNATURES = {
     "xmoe_workspace_bytes_host_io": (_SZ, [C.POINTER(XMoEConfig), _I]),
     "xmoe_forward": (C.c_int, [C.POINTER(XMoEConfig), C.POINTER(XMoEWeights), _P, _P, _I, _P, _P, _SZ, _P]),
     "xmoe_forward_host": (C.c_int, [C.POINTER(XMoEConfig), C.POINTER(XMoEWeights), _P, _P, _I, _P, _P, _SZ, _P]),
+    "xmoe_forward_host_async": (C.c_int, [C.POINTER(XMoEConfig), C.POINTER(XMoEWeights), _P, _P, _I, _P, _P, _SZ, _P]),
     "xmoe_read_status": (C.c_int, [_P, C.POINTER(C.c_uint32), _P]),
     "xmoe_forward_routed": (C.c_int, [C.POINTER(XMoEConfig), C.POINTER(XMoEWeights), _P, _P, _P, _P, _I, _P, _P, _SZ,
                                       _P]),

@@ -52,6 +52,22 @@ int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const
     return r == CUDA_SUCCESS ? XMOE_OK : XMOE_ERR_CUDA;
 }
 
+// The same row-major tensor [rows, inner] seen as [inner / 64][rows][64] (inner % 64 == 0): box [kblocks][box_rows][64].
+// One copy then lands `kblocks` consecutive 128-byte-swizzle slabs of box_rows x 64 elements.
+int make_tmap_kslabs(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner,
+                     uint64_t rows, uint32_t box_rows, uint32_t kblocks) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return XMOE_ERR_CUDA;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((inner * elem_bytes) & 15u) || inner % 64) return XMOE_ERR_SHAPE;
+    cuuint64_t dims[3] = {64, rows, inner / 64};
+    cuuint64_t strides[2] = {inner * (uint64_t)elem_bytes, 64 * (uint64_t)elem_bytes};
+    cuuint32_t box[3] = {64, box_rows, kblocks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
 int num_sms() {  // of the current device
     static int n_dev[kMaxDevices] = {};
     const int dev = device_slot();
@@ -258,10 +274,19 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
                           wide ? CU_TENSOR_MAP_SWIZZLE_128B
                                : (k64 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B));
     if (rc) return rc;
-    rc = make_tmap_2d(&a.tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64,
-                      (uint32_t)(pair ? 128 : nt), CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc) return rc;
-    if (nt <= 64) {
+    a.tok3d = (nt <= 64 && I % 64 == 0) ? 1 : 0;
+    if (a.tok3d) {
+        // small token tiles: one copy per two K units (K 256 = four slabs), for the full tile and for 8 / 16 rows
+        if ((rc = make_tmap_kslabs(&a.tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, (uint32_t)nt, 4)) ||
+            (rc = make_tmap_kslabs(&a.tm_y8, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 8, 4)) ||
+            (rc = make_tmap_kslabs(&a.tm_y16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 16, 4)))
+            return rc;
+    } else {
+        rc = make_tmap_2d(&a.tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64,
+                          (uint32_t)(pair ? 128 : nt), CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+    }
+    if (nt <= 64 && !a.tok3d) {
         rc = make_tmap_2d(&a.tm_y8, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64, 8,
                           CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
@@ -606,8 +631,24 @@ int xmoe_profile_read(float* stage_ms_sum, int32_t* steps_out) {
     return XMOE_OK;
 }
 
+namespace {
+int forward_host_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x_host, const void* logits_host,
+                      int32_t n, void* y_host, void* workspace, size_t workspace_bytes, xmoe_stream_t stream, bool sync);
+}
+
 int xmoe_forward_host(const xmoe_config* cfg, const xmoe_weights* w, const void* x_host, const void* logits_host,
                       int32_t n, void* y_host, void* workspace, size_t workspace_bytes, xmoe_stream_t stream) {
+    return forward_host_impl(cfg, w, x_host, logits_host, n, y_host, workspace, workspace_bytes, stream, true);
+}
+
+int xmoe_forward_host_async(const xmoe_config* cfg, const xmoe_weights* w, const void* x_host, const void* logits_host,
+                            int32_t n, void* y_host, void* workspace, size_t workspace_bytes, xmoe_stream_t stream) {
+    return forward_host_impl(cfg, w, x_host, logits_host, n, y_host, workspace, workspace_bytes, stream, false);
+}
+
+namespace {
+int forward_host_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x_host, const void* logits_host,
+                      int32_t n, void* y_host, void* workspace, size_t workspace_bytes, xmoe_stream_t stream, bool sync) {
     int rc = check_cfg(cfg);
     if (rc) return rc;
     if (n < 0 || !x_host || !logits_host || !y_host || !workspace) return XMOE_ERR_ARG;
@@ -624,9 +665,10 @@ int xmoe_forward_host(const xmoe_config* cfg, const xmoe_weights* w, const void*
                       workspace, workspace_bytes, s);
     if (rc) return rc;
     if (cudaMemcpyAsync(y_host, b + L.off_y_out, xb, cudaMemcpyDeviceToHost, s) != cudaSuccess) return XMOE_ERR_CUDA;
-    if (cudaStreamSynchronize(s) != cudaSuccess) return XMOE_ERR_CUDA;
+    if (sync && cudaStreamSynchronize(s) != cudaSuccess) return XMOE_ERR_CUDA;
     return XMOE_OK;
 }
+}  // namespace
 
 int xmoe_read_status(const void* workspace, uint32_t* host_out, xmoe_stream_t stream) {
     if (!workspace || !host_out) return XMOE_ERR_ARG;

@@ -42,10 +42,14 @@ namespace xmoe {
 __device__ long long g_ff2_trace[148 * 16];
 #define XMOE_T0() const long long t0__ = clock64()
 #define XMOE_TACC(var) var += clock64() - t0__
+#define XMOE_T1() const long long t1__ = clock64()
+#define XMOE_TACC1(var) var += clock64() - t1__
 #define XMOE_TDUMP(slot, var) do { if (blockIdx.x < 148) g_ff2_trace[blockIdx.x * 16 + (slot)] = (var); } while (0)
 #else
 #define XMOE_T0() do {} while (0)
 #define XMOE_TACC(var) do {} while (0)
+#define XMOE_T1() do {} while (0)
+#define XMOE_TACC1(var) do {} while (0)
 #define XMOE_TDUMP(slot, var) do {} while (0)
 #endif
 
@@ -74,11 +78,34 @@ struct Ff2Cfg {
     static constexpr int kWStageBytes = kWRawBytes + 512 * kWUnits;  // + 128 bf16 scales per unit, padded
     static constexpr int kACols = kStageK / 2;                // TMEM columns of one expanded stage
     static constexpr int kSlabs = kStageK / 64;               // 128-byte-swizzle slabs of the token tile
-    static constexpr int kBStageBytes = NT * kStageK * 2;
-    static constexpr int kWStages = NT == 128 ? 12 : (NT == 64 ? 8 : (NT == 32 ? 10 : 16));  // weight ring (HBM latency)
-    static constexpr int kBStages = NT >= 256 ? 4 : (NT >= 128 ? 3 : 4);  // token ring (L2 latency)
+    // a token stage spans the same K units as a weight stage (small tiles: two, fetched by ONE copy through a
+    // 3-D view of the activations): the copy engine takes ~100-200 cycles per request whatever its size, and with
+    // two slab copies per K unit the token producer alone set the pace of the decode kernel
+    static constexpr int kBStageBytes = NT * kStageK * 2 * kWUnits;
+#ifndef XMOE_FF2_WS32
+#define XMOE_FF2_WS32 8
+#endif
+#ifndef XMOE_FF2_BS32
+#define XMOE_FF2_BS32 4
+#endif
+#ifndef XMOE_FF2_WS64
+#define XMOE_FF2_WS64 8
+#endif
+#ifndef XMOE_FF2_BS64
+#define XMOE_FF2_BS64 2
+#endif
+#ifndef XMOE_FF2_SPLIT
+#define XMOE_FF2_SPLIT 1
+#endif
+    static constexpr int kWStages = NT == 128 ? 12 : (NT == 64 ? XMOE_FF2_WS64 : (NT == 32 ? XMOE_FF2_WS32 : 16));  // weight ring (HBM latency)
+    static constexpr int kBStages = NT >= 256 ? 4 : (NT >= 128 ? 3 : (NT == 32 ? XMOE_FF2_BS32 : XMOE_FF2_BS64));  // token ring (L2 latency)
     static constexpr int kIssuers = NT <= 64 ? 4 : 1;         // MMA-issuing threads (K stages round-robin)
     static constexpr int kARing = NT >= 256 ? 8 : 4;          // expanded-weight buffers in tensor memory
+    // Small token tiles hand a buffer over in two halves (K 64 each, own barriers): the issuer starts on the
+    // first half while the second is still being expanded, and the dequant group gets the first half back
+    // before it has finished the second, so expansion and MMA issue of one group overlap instead of taking
+    // turns on the buffer (tensor memory has no room for a second whole buffer per group).
+    static constexpr int kSplit = NT <= 64 ? XMOE_FF2_SPLIT : 1;
     static constexpr int kDqGroups = 4;                       // independent dequant groups of 4 warps
     // Ring ownership. The waits are parity waits, and a parity only tells a phase from its
     // neighbours: a role may wait on a slot only if it took part in that slot's previous phase
@@ -98,9 +125,11 @@ struct Ff2Cfg {
     static constexpr int kThreads = 32 * (kFirstDq + 4 * kDqGroups);
     static constexpr int kAccBase = kARing * kACols;          // accumulators follow the A ring
     static_assert(kAccBase + kAccStages * kIssuers * NT <= kTmemCols, "TMEM budget");
-    static_assert(kWStages <= 16 && kBStages <= 8 && kARing <= 8, "barrier arrays");
+    static_assert(kWStages <= 16 && kBStages <= 16 && kARing * kSplit <= 8, "barrier arrays");
+    static_assert(kSplit == 1 || (kStageK / 32) % kSplit == 0, "halves are whole 16-column stores");
     static_assert(kThreads <= 1024, "block size");
-    static_assert(kARing % kDqGroups == 0 && (kIssuers == 1 || (kARing % kIssuers == 0 && kBStages % kIssuers == 0)),
+    static_assert(kARing % kDqGroups == 0 &&
+                      (kIssuers == 1 || (kARing % kIssuers == 0 && (kBStages * kWUnits) % kIssuers == 0)),
                   "ring ownership");
     static_assert((kWStages * kWUnits) % kDqGroups == 0, "weight ring ownership");
     static_assert(kIssuers == 1 || kAccStages == 1, "issuer/slot pairing relies on the per-tile drain");
@@ -120,17 +149,6 @@ __device__ __forceinline__ uint32_t bits_from_bf162(__nv_bfloat162 v) {
     return bits;
 }
 
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
 __device__ __forceinline__ uint4 lds_u128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -149,6 +167,23 @@ __device__ __forceinline__ uint32_t nib_pair_to_bf16_bits(uint32_t x) {
     return bits;
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+// One 32-bit word of the prepared layout (8 weights: nibble j = K 2j, nibble 4 + j = K 2j + 1) -> four bf16x2
+// registers bf16((u4 - 8) * scale), K ascending: per pair one logic op, one subtract, one multiply, and a shift
+// for three of the four.
+__device__ __forceinline__ void expand_word(uint32_t w, uint32_t* o, __nv_bfloat162 bias, __nv_bfloat162 s2) {
+    o[0] = bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(nib_pair_to_bf16_bits(w)), bias), s2));
+    o[1] = bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(nib_pair_to_bf16_bits(w >> 4)), bias), s2));
+    o[2] = bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(nib_pair_to_bf16_bits(w >> 8)), bias), s2));
+    o[3] = bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(nib_pair_to_bf16_bits(w >> 12)), bias), s2));
+}
 
 template <int NT>
 __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(const __grid_constant__ Ff2Args a) {
@@ -164,15 +199,15 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
     uint8_t* tail = w_base + (size_t)kWStages * Cfg::kWStageBytes;
     uint64_t* w_full = reinterpret_cast<uint64_t*>(tail);  // [16] raw weights + scales landed
     uint64_t* w_empty = w_full + 16;                       // [16] the 4 warps of a dequant group are done with them
-    uint64_t* b_full = w_empty + 16;                       // [8]  token tile landed
-    uint64_t* b_empty = b_full + 8;                        // [8]  MMAs reading it retired
-    uint64_t* adq_full = b_empty + 8;                      // [8]  expanded weights are in tensor memory
+    uint64_t* b_full = w_empty + 16;                       // [16] token tile landed
+    uint64_t* b_empty = b_full + 16;                       // [16] MMAs reading it retired
+    uint64_t* adq_full = b_empty + 16;                     // [8]  expanded weights are in tensor memory
     uint64_t* adq_empty = adq_full + 8;                    // [8]  MMAs reading them retired
     uint64_t* acc_full = adq_empty + 8;                    // [2]
     uint64_t* acc_empty = acc_full + 2;                    // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    int* prefix = reinterpret_cast<int*>(tail + 640);
+    int* prefix = reinterpret_cast<int*>(tail + 768);
     uint16_t* transpose = reinterpret_cast<uint16_t*>(tail + 5120);  // 4 warps x 32 x 32 bf16
 
     const int warp = threadIdx.x >> 5;
@@ -189,9 +224,9 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         }
         for (int s = 0; s < kBStages; ++s) {
             mbar_init(&b_full[s], 1);
-            mbar_init(&b_empty[s], 1);
+            mbar_init(&b_empty[s], Cfg::kWUnits);  // one commit per K unit of the stage (each from the unit's issuer)
         }
-        for (int s = 0; s < kARing; ++s) {
+        for (int s = 0; s < kARing * Cfg::kSplit; ++s) {  // index: buffer * kSplit + half
             mbar_init(&adq_full[s], 4);
             mbar_init(&adq_empty[s], 1);
         }
@@ -276,7 +311,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     if (n_valid <= 8) { tm = &a.tm_y8; box_rows = 8; }
                     else if (n_valid <= 16) { tm = &a.tm_y16; box_rows = 16; }
                 }
-                for (int ks = 0; ks < k_walk; ++ks) {
+                const uint32_t slab_bytes = (uint32_t)box_rows * 128u;  // one slab: box_rows x 64 K
+                for (int ks = 0; ks < k_walk; ks += Cfg::kWUnits) {
                     {
                         XMOE_T0();
                         if (!mbar_wait(&b_empty[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
@@ -285,14 +321,19 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                         }
                         XMOE_TACC(tw_bprod);
                     }
-                    if (ks < k_stages) {
-                        uint8_t* b = b_base + (size_t)s * Cfg::kBStageBytes;
-                        mbar_expect_tx(&b_full[s], (uint32_t)(box_rows * kStageK * 2));
-#pragma unroll
-                        for (int slab = 0; slab < Cfg::kSlabs; ++slab)
-                            tma_load_2d(b + slab * NT * 128, tm, ks * kStageK + slab * 64, t.row0, &b_full[s]);
+                    uint8_t* b = b_base + (size_t)s * Cfg::kBStageBytes;
+                    if (Cfg::kWUnits > 1 && a.tok3d) {
+                        // both K units in one request: four slabs, zero-filled beyond I
+                        mbar_expect_tx(&b_full[s], slab_bytes * (uint32_t)(Cfg::kWUnits * Cfg::kSlabs));
+                        tma_load_3d(b, tm, 0, t.row0, (ks * kStageK) >> 6, &b_full[s]);
                     } else {
-                        mbar_arrive(&b_full[s]);  // phantom stage: the hand-off without a load
+                        const int units = min(Cfg::kWUnits, k_stages - ks);  // the phantom unit of an odd count is not fetched
+                        mbar_expect_tx(&b_full[s], slab_bytes * (uint32_t)(units * Cfg::kSlabs));
+                        for (int u = 0; u < units; ++u)
+#pragma unroll
+                            for (int slab = 0; slab < Cfg::kSlabs; ++slab)
+                                tma_load_2d(b + (u * Cfg::kSlabs + slab) * slab_bytes, tm, (ks + u) * kStageK + slab * 64,
+                                            t.row0, &b_full[s]);
                     }
                     if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
                 }
@@ -325,38 +366,53 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 tc_fence_after();
                 const uint32_t acc = tmem_base + kAccBase + (as * kIssuers + issuer) * NT;
                 uint32_t first = 1u;
+                // slab stride of this tile's token stages: the producer fetches 8 or 16 rows when the tile holds that few
+                uint32_t slab16 = (uint32_t)kSlab16;
+                if (NT <= 64) {
+                    const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
+                    const int n_valid = t.count - t.nt_idx * NT;
+                    slab16 = n_valid <= 8 ? 64u : (n_valid <= 16 ? 128u : (uint32_t)kSlab16);
+                }
                 // this thread's K stages of the tile: issuer, issuer + kIssuers, ...
                 const uint32_t tile_it0 = tile_n * (uint32_t)k_walk;
                 for (int ks = issuer; ks < k_walk; ks += kIssuers) {
                     const uint32_t it = tile_it0 + (uint32_t)ks;
-                    const uint32_t s = it % kBStages, ph = (it / kBStages) & 1u;
+                    const uint32_t bt = it / Cfg::kWUnits;  // token stage of this K unit
+                    const uint32_t s = bt % kBStages, ph = (bt / kBStages) & 1u;
+                    const uint32_t unit_slab = (it % Cfg::kWUnits) * Cfg::kSlabs;
                     const uint32_t d = it % kARing, dph = (it / kARing) & 1u;
                     {
                         XMOE_T0();
                         if (!mbar_wait(&b_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
                         XMOE_TACC(tw_full);
                     }
-                    {
-                        XMOE_T0();
-                        if (!mbar_wait(&adq_full[d], dph, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
-                        XMOE_TACC(tw_adq);
-                    }
-                    XMOE_T0();
-                    tc_fence_after();
                     const uint32_t a_tmem = tmem_base + d * kACols;
                     const uint32_t b_lo = b_lo0 + s * (uint32_t)(Cfg::kBStageBytes >> 4);
-                    if (ks < k_stages) {  // a phantom stage only passes its slots on
+                    constexpr int kMmaPerPart = kStageK / 16 / Cfg::kSplit;
 #pragma unroll
-                        for (int kk = 0; kk < kStageK / 16; ++kk) {
-                            // slab kk/4 (64 K each), 32 bytes of K per MMA inside the 128-byte swizzle row
-                            mma_bf16_ts_lo(acc, a_tmem + kk * 8, b_lo + (kk >> 2) * kSlab16 + (kk & 3) * 2, idesc,
-                                           (kk | (int)(first ^ 1u)) ? 1u : 0u);
+                    for (int part = 0; part < Cfg::kSplit; ++part) {
+                        {
+                            XMOE_T0();
+                            if (!mbar_wait(&adq_full[d * Cfg::kSplit + part], dph, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
+                            XMOE_TACC(tw_adq);
                         }
-                        first = 0u;
+                        XMOE_T0();
+                        tc_fence_after();
+                        if (ks < k_stages) {  // a phantom stage only passes its slots on
+#pragma unroll
+                            for (int k2 = 0; k2 < kMmaPerPart; ++k2) {
+                                const int kk = part * kMmaPerPart + k2;
+                                // slab kk/4 (64 K each), 32 bytes of K per MMA inside the 128-byte swizzle row
+                                mma_bf16_ts_lo(acc, a_tmem + kk * 8, b_lo + (unit_slab + (kk >> 2)) * slab16 + (kk & 3) * 2, idesc,
+                                               (kk | (int)(first ^ 1u)) ? 1u : 0u);
+                            }
+                        }
+                        tc_commit(&adq_empty[d * Cfg::kSplit + part]);
+                        XMOE_TACC(t_issue);
                     }
+                    if (!ok) break;
+                    if (ks < k_stages) first = 0u;
                     tc_commit(&b_empty[s]);
-                    tc_commit(&adq_empty[d]);
-                    XMOE_TACC(t_issue);
                 }
                 if (ok) tc_commit(&acc_full[as]);
             }
@@ -443,92 +499,104 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         constexpr int kWRowBytes = Cfg::kWRowBytes;
         const uint32_t swz = kWRowBytes == 128 ? ((uint32_t)row & 7u)
                                                : (kWRowBytes == 64 ? ((uint32_t)(row >> 1) & 3u) : ((uint32_t)(row >> 2) & 1u));
-        const int w_stages_per_tile = k_walk / Cfg::kWUnits;
-        uint32_t w_tile_base = 0;  // weight stages consumed by earlier tiles of this CTA
         const __nv_bfloat162 bias = bf162_from_bits(0x43084308u);  // 136.0 twice
-        bool ok = true;
         long long dq_wfull = 0, dq_wempty = 0, dq_work = 0;  // dq_work includes the wait for the slot
         (void)dq_wfull; (void)dq_wempty; (void)dq_work;
-        // The K stages of all tiles of this CTA are numbered through (it); this group takes
-        // it = group, group + kDqGroups, ... and keeps the stage's position inside its tile (ks)
-        // alongside, so that no warp walks the stages of the other groups.
+        // The K stages of all tiles of this CTA are numbered through (it, k_walk slots per tile); this group
+        // takes it = group, group + kDqGroups, ... Everything that follows from `it` is kept incrementally:
+        // the tensor-memory slot is always `group` (kARing == kDqGroups or a multiple handled below), the
+        // weight stage advances by kDqGroups / kWUnits slots per step and the K unit inside it never changes.
         const int my_tiles = first_tile < total_tiles ? (total_tiles - 1 - first_tile) / tile_stride + 1 : 0;
         const uint32_t total_it = (uint32_t)my_tiles * (uint32_t)k_walk;
         const uint32_t w_base_u32 = smem_u32(w_base);
+        constexpr int kWStep = kDqGroups / Cfg::kWUnits;        // weight stages per step of this group
+        const int unit = group % Cfg::kWUnits;                  // which K unit of the weight stage (k_walk is a multiple of kWUnits)
+        int s = (group / Cfg::kWUnits) % kWStages;              // weight slot of stage `it`
+        uint32_t ph = 0;
+        int d = group % kARing;
+        uint32_t dph = 0;
         int ks = group;
-        for (uint32_t it = (uint32_t)group; it < total_it && ok; it += kDqGroups, ks += kDqGroups) {
+#ifdef XMOE_TRACE
+        const long long dq_t_begin = clock64();
+#endif
+        const uint32_t row_off = (uint32_t)row * kWRowBytes;
+        const uint32_t scale_off = Cfg::kWRawBytes + unit * 256 + row * 2;
+        const uint32_t a_lane0 = tmem_base + ((uint32_t)(quadrant * 32) << 16);
+        for (uint32_t it = (uint32_t)group; it < total_it; it += kDqGroups) {
+            while (ks >= k_walk) ks -= k_walk;
             {
-                while (ks >= k_walk) {
-                    ks -= k_walk;
-                    w_tile_base += (uint32_t)w_stages_per_tile;
-                }
-                const uint32_t w_it = w_tile_base + (uint32_t)(ks / Cfg::kWUnits);
-                const int unit = ks % Cfg::kWUnits;  // which K unit of the weight stage
-                const int s = w_it % kWStages;
-                const uint32_t ph = (w_it / kWStages) & 1u;
-                const int d = it % kARing;
-                const uint32_t dph = (it / kARing) & 1u;
-                {
-                    XMOE_T0();
-                    if (!mbar_wait(&w_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) { ok = false; break; }
-                    XMOE_TACC(dq_wfull);
-                }
-                if (ks >= k_stages) {
-                    // phantom stage (odd K-unit count): keep this group's place in both rings, expand nothing
-                    if (!mbar_wait(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(&adq_full[d]);
-                        mbar_arrive(&w_empty[s]);
-                    }
-                    continue;
-                }
                 XMOE_T0();
-                const uint32_t st = w_base_u32 + (uint32_t)s * Cfg::kWStageBytes;
-                const uint32_t sraw = lds_u16(st + Cfg::kWRawBytes + unit * 256 + row * 2);
-                const __nv_bfloat162 s2 = bf162_from_bits(sraw | (sraw << 16));
-                const uint32_t a_lane = tmem_base + ((uint32_t)(quadrant * 32) << 16) + d * kACols;
+                if (!mbar_wait(&w_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) break;
+                XMOE_TACC(dq_wfull);
+            }
+            XMOE_T0();
+            if (ks >= k_stages) {
+                // phantom stage (odd K-unit count): keep this group's place in both rings, expand nothing
+                bool ok = true;
 #pragma unroll
-                for (int half = 0; half < kStageK / 64; ++half) {
-                    uint32_t o[32];
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        const uint32_t chunk = (uint32_t)(unit * (kStageK / 32) + half * 2 + c) ^ swz;
-                        const uint4 r4 = lds_u128(st + row * kWRowBytes + chunk * 16);
-                        const uint32_t words[4] = {r4.x, r4.y, r4.z, r4.w};
-#pragma unroll
-                        for (int w = 0; w < 4; ++w) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const uint32_t bits = nib_pair_to_bf16_bits(j ? (words[w] >> (4 * j)) : words[w]);
-                                o[(c * 4 + w) * 4 + j] =
-                                    bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(bits), bias), s2));
-                            }
-                        }
-                    }
-                    if (half == 0) {
-                        // the expansion above does not need the tensor-memory slot: wait for it
-                        // only now, just before the first store
-                        if (!mbar_wait(&adq_empty[d], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
-                        tc_fence_after();
-                    }
-                    tmem_st32(a_lane + half * 32, o);
-                }
+                for (int part = 0; part < Cfg::kSplit; ++part)
+                    ok = ok && mbar_wait(&adq_empty[d * Cfg::kSplit + part], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ);
                 if (!ok) break;
-                tmem_st_wait();
-                tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(&adq_full[d]);
-                    mbar_arrive(&w_empty[s]);
+#pragma unroll
+                    for (int part = 0; part < Cfg::kSplit; ++part) mbar_arrive(&adq_full[d * Cfg::kSplit + part]);
                 }
-                XMOE_TACC(dq_work);
+            } else {
+                const uint32_t st = w_base_u32 + (uint32_t)s * Cfg::kWStageBytes;
+                const uint32_t sraw = lds_u16(st + scale_off);
+                const __nv_bfloat162 s2 = bf162_from_bits(__byte_perm(sraw, sraw, 0x1010));
+                const uint32_t a_lane = a_lane0 + d * kACols;
+                bool ok = true;
+                // 16 bytes (32 weights) at a time: four words -> sixteen bf16x2 registers -> one 16-column store
+                constexpr int kChunksPerPart = kStageK / 32 / Cfg::kSplit;
+#pragma unroll
+                for (int q = 0; q < kStageK / 32; ++q) {
+                    const int part = q / kChunksPerPart;
+                    const uint32_t chunk = (uint32_t)(unit * (kStageK / 32) + q) ^ swz;
+                    const uint4 r4 = lds_u128(st + row_off + chunk * 16);
+                    uint32_t o[16];
+                    expand_word(r4.x, o, bias, s2);
+                    expand_word(r4.y, o + 4, bias, s2);
+                    expand_word(r4.z, o + 8, bias, s2);
+                    expand_word(r4.w, o + 12, bias, s2);
+                    if (q % kChunksPerPart == 0) {
+                        // the expansion above does not need the tensor-memory slot: wait for it only now
+                        XMOE_T1();
+                        if (!mbar_wait(&adq_empty[d * Cfg::kSplit + part], dph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_DQ)) { ok = false; break; }
+                        XMOE_TACC1(dq_wempty);
+                        tc_fence_after();
+                    }
+                    tmem_st16(a_lane + q * 16, o);
+                    if (q % kChunksPerPart == kChunksPerPart - 1) {  // this part is complete: hand it to the issuer
+                        tmem_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&adq_full[d * Cfg::kSplit + part]);
+                    }
+                }
+                if (!ok) break;
+            }
+            if (lane == 0) mbar_arrive(&w_empty[s]);
+            XMOE_TACC(dq_work);
+            ks += kDqGroups;
+            s += kWStep;
+            if (s >= kWStages) { s -= kWStages; ph ^= 1u; }
+            if (kARing == kDqGroups) {
+                dph ^= 1u;
+            } else {
+                d += kDqGroups;
+                if (d >= kARing) { d -= kARing; dph ^= 1u; }
             }
         }
         if (warp == Cfg::kFirstDq && lane == 0) {
             XMOE_TDUMP(6, dq_wfull);
             XMOE_TDUMP(7, dq_wempty);
             XMOE_TDUMP(8, dq_work);
+#ifdef XMOE_TRACE
+            XMOE_TDUMP(9, clock64() - dq_t_begin);
+            XMOE_TDUMP(10, (long long)total_it);
+#endif
         }
     }
 

@@ -99,18 +99,23 @@ __device__ __forceinline__ uint32_t nib_pair_to_bf16_bits(uint32_t x) {
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(bits) : "r"(x), "r"(0x000f000fu), "r"(0x43004300u));
     return bits;
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
     asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// One 32-bit word of the prepared layout (8 weights: nibble j = K 2j, nibble 4 + j = K 2j + 1) -> four bf16x2
+// registers bf16((u4 - 8) * scale), K ascending.
+__device__ __forceinline__ void expand_word(uint32_t w, uint32_t* o, __nv_bfloat162 bias, __nv_bfloat162 s2) {
+    o[0] = bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(nib_pair_to_bf16_bits(w)), bias), s2));
+    o[1] = bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(nib_pair_to_bf16_bits(w >> 4)), bias), s2));
+    o[2] = bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(nib_pair_to_bf16_bits(w >> 8)), bias), s2));
+    o[3] = bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(nib_pair_to_bf16_bits(w >> 12)), bias), s2));
+}
 
 // 2-SM MMA: D (256 x N, 128 rows in each CTA's tensor memory) (+)= A (each CTA's tensor memory)
 // * B (N/2 rows in each CTA's shared memory at the same offset).
@@ -377,27 +382,18 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
                 tc_fence_after();
                 const uint32_t st = w_base_u32 + (uint32_t)s * kWStageBytes;
                 const uint32_t sraw = lds_u16(st + kRawBytes + row * 2);
-                const __nv_bfloat162 s2 = bf162_from_bits(sraw | (sraw << 16));
+                const __nv_bfloat162 s2 = bf162_from_bits(__byte_perm(sraw, sraw, 0x1010));
                 const uint32_t a_lane = tmem_base + ((uint32_t)(quadrant * 32) << 16) + d * kACols;
+                // 16 bytes (32 weights) at a time: four words -> sixteen bf16x2 registers -> one 16-column store
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t o[32];
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        const uint32_t chunk = (uint32_t)(half * 2 + c) ^ swz;
-                        const uint4 r4 = lds_u128(st + row * 64 + chunk * 16);
-                        const uint32_t words[4] = {r4.x, r4.y, r4.z, r4.w};
-#pragma unroll
-                        for (int w = 0; w < 4; ++w) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const uint32_t bits = nib_pair_to_bf16_bits(j ? (words[w] >> (4 * j)) : words[w]);
-                                o[(c * 4 + w) * 4 + j] =
-                                    bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(bits), bias), s2));
-                            }
-                        }
-                    }
-                    tmem_st32(a_lane + half * 32, o);
+                for (int q = 0; q < 4; ++q) {
+                    const uint4 r4 = lds_u128(st + row * 64 + (((uint32_t)q ^ swz) * 16));
+                    uint32_t o[16];
+                    expand_word(r4.x, o, bias, s2);
+                    expand_word(r4.y, o + 4, bias, s2);
+                    expand_word(r4.z, o + 8, bias, s2);
+                    expand_word(r4.w, o + 12, bias, s2);
+                    tmem_st16(a_lane + q * 16, o);
                 }
                 tmem_st_wait();
                 tc_fence_before();

@@ -100,6 +100,9 @@ struct Ff2Args {
     // token tiles of NT <= 64 only: the same tensor with 8- and 16-row boxes, used when a tile holds
     // that few tokens (the MMA still reads NT rows; the columns of the stale ones are never stored)
     CUtensorMap tm_y8, tm_y16;
+    // NT <= 64 and I % 64 == 0: the three maps above are 3-D views [I/64][R_cap][64] of the same tensor with
+    // boxes of 4 x rows x 64, so that ONE copy fetches K 256 of a token tile as four 128-byte-swizzle slabs
+    int tok3d;
     const void* w2_scale;  // bf16 [E_tot, G, H]
     const int32_t* counts;
     const int32_t* offsets;

@@ -237,6 +237,24 @@ class FusedMoE:
                                            _stream()), "xmoe_forward_host")
         return y_host
 
+    def forward_host_async(self, x_host: torch.Tensor, logits_host: torch.Tensor, y_host: torch.Tensor, slot: int = 0,
+                           stream: "torch.cuda.Stream | None" = None) -> None:
+        """forward_host without the final synchronisation, on `stream` (default: the current one). `slot` selects
+        one of several independent workspaces so that calls on different streams can be in flight together;
+        y_host is valid after the caller has synchronised the stream. Buffers must be pinned."""
+        n = x_host.shape[0]
+        key = (n, ("host_io", slot))
+        ws = self._ws.get(key)
+        if ws is None:
+            nbytes = _lib.lib().xmoe_workspace_bytes_host_io(C.byref(self.cfg), n)
+            raw = torch.empty(nbytes + 1024, dtype=torch.uint8, device=self.weights.w13_packed.device)
+            off = (-raw.data_ptr()) % 1024
+            ws = self._ws[key] = raw[off:off + nbytes]
+        s = stream.cuda_stream if stream is not None else _stream()
+        check(_lib.lib().xmoe_forward_host_async(C.byref(self.cfg), C.byref(self._wstruct), x_host.data_ptr(),
+                                                 logits_host.data_ptr(), n, y_host.data_ptr(), ws.data_ptr(),
+                                                 ws.numel(), s), "xmoe_forward_host_async")
+
     def status(self, n: int, host_io: bool = False) -> int:
         """Device status word of the last forward with n tokens (0 = ok). Synchronises."""
         ws = self.workspace(n, host_io)
