@@ -196,3 +196,37 @@ def test_bounded_peer_wait_runs_out_and_reports(monkeypatch):
     assert bits.value & ~1 == 0, f"no other error expected, got {bits.value:#x}"
     torch.cuda.synchronize()  # the context is still usable
     assert float(x.float().sum().item()) == float(x.float().sum().item())
+
+
+def test_ff2_k_split_is_deterministic_and_matches_whole_tiles():
+    # few tiles per SM (here 3 experts x 2 weight tiles with a long K): the small-tile FF2 kernel cuts tiles along K
+    # across CTAs and adds the partial sums in a fixed order. Run to run the result must not change by a bit;
+    # against whole-tile scheduling (XMOE_FF2_SPLITK=0 is read once per process, so that run is a child process)
+    # it may differ by fp32 summation order only.
+    import os
+    import subprocess
+    import sys
+
+    shape = synth.scaled_shape(synth.SHAPES["mixtral"], hidden=256, inter=4096, num_experts=4)
+    w, layer = Hh.build_layer(shape)
+    x, logits = synth.make_inputs(shape, w, 6)
+    xd, ld = x.cuda(), logits.cuda()
+    y1 = layer.forward(xd, ld).clone()
+    y2 = layer.forward(xd, ld).clone()
+    torch.cuda.synchronize()
+    assert layer.status(6) == 0 and torch.equal(y1, y2)
+    ref = O.layer_forward(x, logits, w, shape)
+    check_stages(shape, 6, y1, ref, layer.view(6))
+    code = ("import sys, torch; sys.path.insert(0, %r)\n"
+            "from tests import helpers as Hh\nfrom xcaliber_b200 import synth\n"
+            "shape = synth.scaled_shape(synth.SHAPES['mixtral'], hidden=256, inter=4096, num_experts=4)\n"
+            "w, layer = Hh.build_layer(shape)\nx, logits = synth.make_inputs(shape, w, 6)\n"
+            "y = layer.forward(x.cuda(), logits.cuda()); torch.cuda.synchronize(); assert layer.status(6) == 0\n"
+            "torch.save(y.cpu(), sys.argv[1])\n") % str(Path(__file__).resolve().parent.parent)
+    out = Path(os.environ.get("TMPDIR", "/tmp")) / f"xmoe_nosplit_{os.getpid()}.pt"
+    env = dict(os.environ, XMOE_FF2_SPLITK="0")
+    subprocess.run([sys.executable, "-c", code, str(out)], check=True, env=env, timeout=600)
+    y0 = torch.load(out)
+    out.unlink()
+    mx, mean = O.rel_errors(y1.float().cpu(), y0.float())
+    assert mx <= 1e-2 and mean <= 1e-3, (mx, mean)

@@ -113,10 +113,16 @@ SideStream* side_stream(cudaStream_t caller) {
     return &s;
 }
 
-// The first KiB of a workspace holds scalars: status word of the layer (word 0), amax scratch, activation
-// scale; word 32 is the status of the gate GEMM when xmoe_forward_gated runs it. The host_io workspace of
-// xmoe_forward_host is read the same way (its gate word is never written and stays as allocated: zeroed here).
+// The first 4 KiB of a workspace are cleared at the start of every call. The first KiB holds scalars: status
+// word of the layer (word 0), amax scratch, activation scale; word 32 is the status of the gate GEMM when
+// xmoe_forward_gated runs it. The host_io workspace of xmoe_forward_host is read the same way (its gate word
+// is never written and stays as allocated: zeroed here). Bytes 1024.. hold the per-CTA flags of FF2's
+// K-split partial sums (zero at launch).
 constexpr int kGateStatusWord = 32;
+constexpr size_t kClearedBytes = 4096;
+constexpr size_t kFf2FlagsOffset = 1024;
+constexpr int kMaxSplitCtas = 192;  // flag words and partial-sum slots reserved (B200: 148 SMs)
+static_assert(kFf2FlagsOffset + kMaxSplitCtas * 4 <= 2048, "flag block");
 
 // ---- optional per-stage timing (CUDA events recorded on the caller's stream) -----------
 constexpr int kProfStages = 8;  // router, pack, amax, quant, ff1, act_topk, ff2, combine
@@ -163,7 +169,7 @@ struct Layout {
     int k_eff, e_tot, kb_pad, mb, groups, nt, chunks;
     size_t rows;  // packed-row capacity
     size_t off_status, off_amax, off_scale, off_topk_idx, off_topk_w, off_topk_off, off_topk_row, off_hist, off_counts,
-        off_offsets, off_row_token, off_row_weight, off_xq, off_sfx, off_yact, off_out, total;
+        off_offsets, off_row_token, off_row_weight, off_xq, off_sfx, off_yact, off_out, off_ff2_partial, total;
     size_t off_x_in, off_logits_in, off_y_out, total_host_io;
 };
 
@@ -191,7 +197,7 @@ Layout make_layout(const xmoe_config* c, int n) {
         o = align_up(o + bytes, 1024);
         return at;
     };
-    L.off_status = take(16);  // status word shares the first KiB with the scalars below
+    L.off_status = take(kClearedBytes);  // status word, scalars and flags (see kClearedBytes)
     L.off_amax = 16;
     L.off_scale = 32;
     L.off_topk_idx = take((size_t)n * L.k_eff * 4);
@@ -207,6 +213,8 @@ Layout make_layout(const xmoe_config* c, int n) {
     L.off_sfx = take((L.rows / L.nt) * (size_t)L.kb_pad * 512);
     L.off_yact = take(L.rows * (size_t)c->inter * 2);
     L.off_out = take(L.rows * (size_t)c->hidden * 2);
+    // small token tiles: one fp32 partial-sum slot [token tile][128] per CTA for FF2's K split
+    L.off_ff2_partial = take(ff2_token_tile(c, L.nt) <= 64 ? (size_t)kMaxSplitCtas * 64 * 128 * 4 : 0);
     L.total = o;
     L.off_x_in = take((size_t)n * c->hidden * 2);
     L.off_logits_in = take((size_t)n * c->num_experts * 2);
@@ -255,10 +263,28 @@ int run_ff1(const void* w13_packed, const void* w13_sf, const float* w13_gs, con
 
 int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int32_t* counts, const int32_t* offsets,
             void* out_rows, uint32_t* status, int e_tot, int H, int I, size_t rows, int nt, cudaStream_t stream,
-            const unsigned long long* row_dst = nullptr) {
+            const unsigned long long* row_dst = nullptr, float* split_partial = nullptr, uint32_t* split_flags = nullptr,
+            size_t max_rows_in_use = 0) {
     Ff2Args a;
     memset(&a, 0, sizeof(a));
     a.row_dst = row_dst;
+    // K split across CTAs (small token tiles): needs the caller's scratch and zeroed flags; XMOE_FF2_SPLITK=0 turns it off
+    static const bool splitk_enabled = [] {
+        const char* e = getenv("XMOE_FF2_SPLITK");
+        return !(e && e[0] == '0');
+    }();
+    // The K-split kernel is chosen here, from an upper bound of the tile count (the counts themselves are on the
+    // device): it can only pay when the tiles cannot fill two rounds of SMs. The kernel then looks at the real
+    // tile list and cuts tiles only if whole tiles would leave SM-rounds idle.
+    if (splitk_enabled && nt <= 64 && num_sms() <= kMaxSplitCtas && max_rows_in_use > 0) {
+        const size_t live_max = max_rows_in_use < (size_t)e_tot ? max_rows_in_use : (size_t)e_tot;
+        const size_t token_tiles_max = live_max + max_rows_in_use / (size_t)nt;  // sum over experts of ceil(count / nt)
+        const size_t tiles_max = token_tiles_max * (size_t)((H + 127) / 128);
+        if (tiles_max <= 2 * (size_t)num_sms()) {
+            a.split_partial = split_partial;
+            a.split_flags = split_flags;
+        }
+    }
     // 256-token tiles run on CTA pairs (2-SM MMA) unless XMOE_FF2_PAIR=0: each CTA stages 128 token
     // rows and K 128 (64-byte weight rows). The single-CTA 256 variant uses K 64 (32-byte rows).
     static const bool pair_enabled = [] {
@@ -339,7 +365,7 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     const int H = cfg->hidden, I = cfg->inter, E = cfg->num_experts;
 
     // status words (layer and gate), amax scratch, activation scale
-    if (!scalars_precleared && cudaMemsetAsync(b, 0, 256, stream) != cudaSuccess) return XMOE_ERR_CUDA;
+    if (!scalars_precleared && cudaMemsetAsync(b, 0, kClearedBytes, stream) != cudaSuccess) return XMOE_ERR_CUDA;
     prof_mark(0, stream);
 
     // fork: the amax of x overlaps routing (joined before the quantiser)
@@ -486,7 +512,8 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     prof_mark(6, stream);
 
     if ((rc = run_ff2(w->w2_q, w->w2_scale, b + L.off_yact, counts, offsets, b + L.off_out, status, L.e_tot, H, I,
-                      L.rows, ff2_token_tile(cfg, L.nt), stream, ep_ret ? row_dst : nullptr)))
+                      L.rows, ff2_token_tile(cfg, L.nt), stream, ep_ret ? row_dst : nullptr,
+                      (float*)(b + L.off_ff2_partial), (uint32_t*)(b + kFf2FlagsOffset), (size_t)n * L.k_eff)))
         return rc;
     if (ep_ret && (rc = launch_ep_signal_ret(ep_ret, stream))) return rc;
     prof_mark(7, stream);
@@ -585,7 +612,7 @@ int xmoe_forward_gated(const xmoe_config* cfg, const xmoe_weights* w, const void
     if (!cfg || !gate_w || !logits_scratch || !workspace) return XMOE_ERR_ARG;
     if (n == 0) return XMOE_OK;
     uint32_t* gate_status = (uint32_t*)workspace + kGateStatusWord;
-    if (cudaMemsetAsync(workspace, 0, 256, (cudaStream_t)stream) != cudaSuccess) return XMOE_ERR_CUDA;
+    if (cudaMemsetAsync(workspace, 0, kClearedBytes, (cudaStream_t)stream) != cudaSuccess) return XMOE_ERR_CUDA;
     int rc = xmoe_gate_logits(x, gate_w, n, cfg->hidden, cfg->num_experts, logits_scratch, gate_status, stream);
     if (rc) return rc;
     return forward_impl(cfg, w, x, logits_scratch, nullptr, nullptr, nullptr, n, y, workspace, workspace_bytes,

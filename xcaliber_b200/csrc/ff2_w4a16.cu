@@ -167,6 +167,13 @@ __device__ __forceinline__ uint32_t nib_pair_to_bf16_bits(uint32_t x) {
     return bits;
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// polls (~100 ns each) a finishing CTA spends on one helper's flag before it gives up: ~0.2 s
+constexpr uint32_t kPartialSpinLimit = 1u << 21;
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -185,8 +192,9 @@ __device__ __forceinline__ void expand_word(uint32_t w, uint32_t* o, __nv_bfloat
     o[3] = bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(nib_pair_to_bf16_bits(w >> 12)), bias), s2));
 }
 
-template <int NT>
+template <int NT, bool KSPLIT>
 __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(const __grid_constant__ Ff2Args a) {
+    static_assert(!KSPLIT || NT <= 64, "tiles are cut along K only for small token tiles");
     using Cfg = Ff2Cfg<NT>;
     constexpr int kARing = Cfg::kARing, kDqGroups = Cfg::kDqGroups, kAccBase = Cfg::kAccBase;
     constexpr int kStageK = Cfg::kStageK, kACols = Cfg::kACols;
@@ -253,8 +261,21 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = prefix[a.E_tot];
-    const int tile_stride = balanced_stride(total_tiles, (int)gridDim.x);
-    const int first_tile = (int)blockIdx.x < tile_stride ? (int)blockIdx.x : total_tiles;  // CTAs beyond the stride idle
+    // this CTA's share: whole tiles at a balanced stride, or (small token tiles with scratch for partial sums) an
+    // equal run of K units that may cut tiles (tile_sched.cuh: KWalk)
+    const int cta = (int)blockIdx.x;
+    KWalk walk;
+    {
+        // cutting tiles costs one more segment (one more accumulator drain) per CTA: worth it only when whole tiles
+        // would leave more than a tenth of the SM-rounds idle (256 tiles on 148 SMs: 13.5 %; 1173 tiles: 1 %) and a
+        // tile is long enough (>= 32 K units) for the extra drain to be small against it, or there are fewer
+        // tiles than SMs. KSPLIT is a separate instantiation: with the partial-sum code merely present, the
+        // epilogue of short tiles (6 K units) ran a fifth slower
+        const int grid = (int)gridDim.x;
+        const int rounds = (total_tiles + grid - 1) / grid;
+        const bool uneven = (k_walk >= 32 || total_tiles < grid) && total_tiles > 0 && total_tiles * 10 < grid * rounds * 9;
+        walk.init(total_tiles, k_walk, grid, cta, KSPLIT && uneven);
+    }
 
     if (warp == 0) {
         // ------------------------------ weight producer ---------------------------
@@ -264,13 +285,14 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             bool ok = true;
             long long tw_prod = 0;
             (void)tw_prod;
-            for (int item = first_tile; item < total_tiles && ok; item += tile_stride) {
-                const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
+            for (int si = 0; si < walk.n_seg && ok; ++si) {
+                const KSegment sg = walk.seg(si, cta);
+                const TileInfo t = tile_decode(sg.tile, prefix, a.counts, a.offsets, a.E_tot, NT);
                 const int h0 = t.wt * kBlockM;
                 const int w_row = t.e * a.H + h0;
                 const int rows_here = min(kBlockM, a.H - h0);
                 const uint32_t scale_bytes = (uint32_t)rows_here * 2u;  // H % 8 == 0 keeps this a multiple of 16
-                for (int ks = 0; ks < k_stages; ks += Cfg::kWUnits) {
+                for (int ks = sg.ks0; ks < sg.ks1 && ks < k_stages; ks += Cfg::kWUnits) {
                     {
                         XMOE_T0();
                         if (!mbar_wait(&w_empty[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
@@ -299,8 +321,9 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             bool ok = true;
             long long tw_bprod = 0;
             (void)tw_bprod;
-            for (int item = first_tile; item < total_tiles && ok; item += tile_stride) {
-                const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
+            for (int si = 0; si < walk.n_seg && ok; ++si) {
+                const KSegment sg = walk.seg(si, cta);
+                const TileInfo t = tile_decode(sg.tile, prefix, a.counts, a.offsets, a.E_tot, NT);
                 // Few tokens in the tile (decode): fetch only 8 or 16 rows. The token tile comes
                 // from L2 at the same bytes per K as the weights do from HBM, and the L2 -> SM
                 // path is shared by both.
@@ -312,7 +335,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     else if (n_valid <= 16) { tm = &a.tm_y16; box_rows = 16; }
                 }
                 const uint32_t slab_bytes = (uint32_t)box_rows * 128u;  // one slab: box_rows x 64 K
-                for (int ks = 0; ks < k_walk; ks += Cfg::kWUnits) {
+                for (int ks = sg.ks0; ks < sg.ks1; ks += Cfg::kWUnits) {
                     {
                         XMOE_T0();
                         if (!mbar_wait(&b_empty[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
@@ -355,7 +378,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             bool ok = true;
             long long tw_full = 0, tw_adq = 0, tw_acc = 0, t_issue = 0;
             (void)tw_full; (void)tw_adq; (void)tw_acc; (void)t_issue;
-            for (int item = first_tile; item < total_tiles && ok; item += tile_stride, ++tile_n) {
+            for (int si = 0; si < walk.n_seg && ok; ++si, ++tile_n) {
+                const KSegment sg = walk.seg(si, cta);
                 const uint32_t as = tile_n % kAccStages;
                 const uint32_t aph = (tile_n / kAccStages) & 1u;
                 {
@@ -369,14 +393,13 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 // slab stride of this tile's token stages: the producer fetches 8 or 16 rows when the tile holds that few
                 uint32_t slab16 = (uint32_t)kSlab16;
                 if (NT <= 64) {
-                    const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
+                    const TileInfo t = tile_decode(sg.tile, prefix, a.counts, a.offsets, a.E_tot, NT);
                     const int n_valid = t.count - t.nt_idx * NT;
                     slab16 = n_valid <= 8 ? 64u : (n_valid <= 16 ? 128u : (uint32_t)kSlab16);
                 }
-                // this thread's K stages of the tile: issuer, issuer + kIssuers, ...
-                const uint32_t tile_it0 = tile_n * (uint32_t)k_walk;
-                for (int ks = issuer; ks < k_walk; ks += kIssuers) {
-                    const uint32_t it = tile_it0 + (uint32_t)ks;
+                // this thread's K units of the segment: the issuer-th, then every kIssuers-th
+                for (int ks = sg.ks0 + issuer; ks < sg.ks1; ks += kIssuers) {
+                    const uint32_t it = (uint32_t)(sg.it0 + ks - sg.ks0);
                     const uint32_t bt = it / Cfg::kWUnits;  // token stage of this K unit
                     const uint32_t s = bt % kBStages, ph = (bt / kBStages) & 1u;
                     const uint32_t unit_slab = (it % Cfg::kWUnits) * Cfg::kSlabs;
@@ -429,14 +452,35 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         uint32_t tile_n = 0;
         uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
         uint16_t* tp = transpose + q * 1024;  // this warp's 32 tokens x 32 features
-        for (int item = first_tile; item < total_tiles; item += tile_stride, ++tile_n) {
-            const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, NT);
+        for (int si = 0; si < walk.n_seg; ++si, ++tile_n) {
+            const KSegment sg = walk.seg(si, cta);
+            const TileInfo t = tile_decode(sg.tile, prefix, a.counts, a.offsets, a.E_tot, NT);
             const uint32_t as = tile_n % kAccStages;
             const uint32_t aph = (tile_n / kAccStages) & 1u;
             if (!mbar_wait(&acc_full[as], aph, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
             tc_fence_after();
             const int h_base = t.wt * kBlockM + q * 32;  // first feature of this warp's 32 lanes
             const int n_valid = min(NT, t.count - t.nt_idx * NT);
+            const int real_units = min(sg.ks1, k_stages) - sg.ks0;  // K units of this segment that hold data
+            const bool takes_partials = KSPLIT && sg.finishes && sg.ks0 > 0;  // other CTAs summed the K units before ks0
+            const bool gives_partial = KSPLIT && !sg.finishes;                // this CTA only adds to the tile
+            if (takes_partials) {
+                // every helper's four epilogue warps have stored their quarter of the partial sum when its flag is 4
+                if (lane == 0) {
+                    for (int h = sg.first_helper; h < cta; ++h) {
+                        uint32_t spin = 0;
+                        while (ld_acquire_gpu(&a.split_flags[h]) < 4u) {
+                            if (++spin > kPartialSpinLimit || *abort_flag) {
+                                *abort_flag = 1u;
+                                atomicCAS(a.status, XMOE_DEV_OK, XMOE_DEV_TIMEOUT_ACC | (blockIdx.x & 0xffu));
+                                break;
+                            }
+                            __nanosleep(64);
+                        }
+                    }
+                }
+                __syncwarp();
+            }
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAccBase + as * kIssuers * NT;
             for (int c0 = 0; c0 < NT; c0 += 32) {
                 if (c0 >= n_valid) break;
@@ -446,7 +490,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 if (kIssuers > 1) {  // add the other issuers' partial sums, in issuer order
 #pragma unroll
                     for (int p = 1; p < kIssuers; ++p) {
-                        if (p < k_stages) {
+                        if (p < real_units) {
 #pragma unroll
                             for (int hh = 0; hh < 2; ++hh) {  // 16 columns at a time: register budget
                                 uint32_t v2[16];
@@ -459,6 +503,21 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                             }
                         }
                     }
+                }
+                if (takes_partials) {  // helpers in CTA order (= K order), on top of this CTA's own sum
+                    for (int h = sg.first_helper; h < cta; ++h) {
+                        const float* part = a.split_partial + ((size_t)h * NT + c0) * kBlockM + q * 32 + lane;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (c0 + j < n_valid) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(part + j * kBlockM));
+                    }
+                }
+                if (gives_partial) {  // fp32, token-major: a warp writes 128 contiguous bytes per token
+                    float* part = a.split_partial + ((size_t)cta * NT + c0) * kBlockM + q * 32 + lane;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c0 + j < n_valid) part[j * kBlockM] = __uint_as_float(v[j]);
+                    continue;
                 }
                 // lane = feature, v[j] = token c0+j  ->  shared [token][feature]
 #pragma unroll
@@ -480,6 +539,11 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     }
                 }
                 __syncwarp();
+            }
+            if (gives_partial) {  // publish: stores, fence, then this warp's count on the flag
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicAdd(&a.split_flags[cta], 1u);
             }
             tc_fence_before();
             __syncwarp();
@@ -506,8 +570,13 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         // takes it = group, group + kDqGroups, ... Everything that follows from `it` is kept incrementally:
         // the tensor-memory slot is always `group` (kARing == kDqGroups or a multiple handled below), the
         // weight stage advances by kDqGroups / kWUnits slots per step and the K unit inside it never changes.
-        const int my_tiles = first_tile < total_tiles ? (total_tiles - 1 - first_tile) / tile_stride + 1 : 0;
-        const uint32_t total_it = (uint32_t)my_tiles * (uint32_t)k_walk;
+        uint32_t total_it = 0;
+        for (int si = 0; si < walk.n_seg; ++si) {
+            const KSegment g = walk.seg(si, cta);
+            total_it += (uint32_t)(g.ks1 - g.ks0);
+        }
+        int seg_i = 0;
+        KSegment sg = walk.seg(0, cta);  // segment that holds unit `it` (n_seg == 0: never used)
         const uint32_t w_base_u32 = smem_u32(w_base);
         constexpr int kWStep = kDqGroups / Cfg::kWUnits;        // weight stages per step of this group
         const int unit = group % Cfg::kWUnits;                  // which K unit of the weight stage (k_walk is a multiple of kWUnits)
@@ -515,7 +584,6 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         uint32_t ph = 0;
         int d = group % kARing;
         uint32_t dph = 0;
-        int ks = group;
 #ifdef XMOE_TRACE
         const long long dq_t_begin = clock64();
 #endif
@@ -523,7 +591,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         const uint32_t scale_off = Cfg::kWRawBytes + unit * 256 + row * 2;
         const uint32_t a_lane0 = tmem_base + ((uint32_t)(quadrant * 32) << 16);
         for (uint32_t it = (uint32_t)group; it < total_it; it += kDqGroups) {
-            while (ks >= k_walk) ks -= k_walk;
+            while ((int)it >= sg.it0 + (sg.ks1 - sg.ks0)) sg = walk.seg(++seg_i, cta);
+            const int ks = sg.ks0 + ((int)it - sg.it0);
             {
                 XMOE_T0();
                 if (!mbar_wait(&w_full[s], ph, abort_flag, a.status, XMOE_DEV_TIMEOUT_TMA)) break;
@@ -579,7 +648,6 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             }
             if (lane == 0) mbar_arrive(&w_empty[s]);
             XMOE_TACC(dq_work);
-            ks += kDqGroups;
             s += kWStep;
             if (s >= kWStages) { s -= kWStages; ph ^= 1u; }
             if (kARing == kDqGroups) {
@@ -609,7 +677,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
     if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
-template <int NT>
+template <int NT, bool KSPLIT>
 int launch_ff2_nt(const Ff2Args& a, cudaStream_t stream) {
     using Cfg = Ff2Cfg<NT>;
     static bool attr_set_dev[kMaxDevices] = {};
@@ -617,12 +685,12 @@ int launch_ff2_nt(const Ff2Args& a, cudaStream_t stream) {
     if (dev < 0) return XMOE_ERR_CUDA;
     bool& attr_set = attr_set_dev[dev];
     if (!attr_set) {
-        if (cudaFuncSetAttribute(ff2_w4a16_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(ff2_w4a16_kernel<NT, KSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)Cfg::kSmemBytes) != cudaSuccess)
             return XMOE_ERR_CUDA;
         attr_set = true;
     }
-    ff2_w4a16_kernel<NT><<<a.num_sms, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(a);
+    ff2_w4a16_kernel<NT, KSPLIT><<<a.num_sms, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(a);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 
@@ -636,11 +704,12 @@ extern "C" int xmoe_ff2_trace_dump(long long* host_out) {
 
 int launch_ff2(const Ff2Args& a, cudaStream_t stream) {
     if (a.E_tot + 1 > kMaxExperts || a.H % 8 || a.I % 32) return XMOE_ERR_SHAPE;
+    const bool split = a.split_partial != nullptr && a.split_flags != nullptr;
     switch (a.nt) {
-        case 32: return launch_ff2_nt<32>(a, stream);
-        case 64: return launch_ff2_nt<64>(a, stream);
-        case 128: return launch_ff2_nt<128>(a, stream);
-        case 256: return launch_ff2_nt<256>(a, stream);
+        case 32: return split ? launch_ff2_nt<32, true>(a, stream) : launch_ff2_nt<32, false>(a, stream);
+        case 64: return split ? launch_ff2_nt<64, true>(a, stream) : launch_ff2_nt<64, false>(a, stream);
+        case 128: return launch_ff2_nt<128, false>(a, stream);
+        case 256: return launch_ff2_nt<256, false>(a, stream);
         default: return XMOE_ERR_SHAPE;
     }
 }

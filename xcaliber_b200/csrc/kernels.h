@@ -112,6 +112,10 @@ struct Ff2Args {
     // the epilogue's stores are the return transfer.
     const unsigned long long* row_dst;
     uint32_t* status;
+    // Tiles cut along K across CTAs (token tiles of NT <= 64 only; both null = whole tiles per CTA):
+    // split_partial fp32 [CTAs][NT][128], one slot per CTA; split_flags u32 [CTAs], ZERO at launch.
+    float* split_partial;
+    uint32_t* split_flags;
     int E_tot, H, I, groups;  // groups = ceil(I / 128)
     int nt;
     int num_sms;
