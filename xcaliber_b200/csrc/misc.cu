@@ -57,6 +57,7 @@ int launch_combine(const CombineArgs& a, cudaStream_t stream) {
 // index-ordered pass that hands the remaining quota to the first ties.
 // ------------------------------------------------------------------------------------
 constexpr int kTopkThreads = 256;
+constexpr int kTopkMaxExperts = 1024 + 8;
 
 __global__ __launch_bounds__(kTopkThreads) void act_topk_general_kernel(uint16_t* __restrict__ yact,
                                                                 const int32_t* __restrict__ counts,
@@ -289,9 +290,163 @@ __global__ __launch_bounds__(kTopkThreads) void act_topk_kernel(uint16_t* __rest
     }
 }
 
+// Warp-per-row path, I = 256 * VEC (VEC 16-byte pieces per lane, read coalesced): no block-wide barriers, eight rows
+// of a CTA progress independently. Histograms live in a per-warp slice of shared memory; the two bucket searches
+// are the warp routine above. The row is read once into registers and only pieces that change are written back.
+// Ties at the threshold: the common case (every entry equal to the threshold survives) needs no ordering; otherwise
+// the entries are ranked in index order, which for the coalesced layout is (piece, lane, position in the piece).
+template <int VEC>
+__global__ __launch_bounds__(kTopkThreads) void act_topk_warp_kernel(uint16_t* __restrict__ yact,
+                                                                     const int32_t* __restrict__ counts,
+                                                                     const int32_t* __restrict__ offsets, int e_tot,
+                                                                     int keep, int max_rows) {
+    __shared__ int hist_all[8][256];
+    __shared__ int s_off[kTopkMaxExperts + 1], s_cnt[kTopkMaxExperts];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int* hist = hist_all[warp];
+    // expert segments once per CTA in shared memory: which rows are padding is then a search without global loads
+    for (int e = threadIdx.x; e <= e_tot; e += blockDim.x) {
+        s_off[e] = offsets[e];
+        if (e < e_tot) s_cnt[e] = counts[e];
+    }
+    __syncthreads();
+    const int r_end = min(max_rows, s_off[e_tot]);
+    constexpr int I = 256 * VEC;
+    for (int r = blockIdx.x * 8 + warp; r < r_end; r += gridDim.x * 8) {
+    int lo = 0, hi = e_tot;  // largest e with offsets[e] <= r
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (s_off[mid] <= r) lo = mid; else hi = mid;
+    }
+    if (r - s_off[lo] >= s_cnt[lo]) continue;  // a padding row
+    uint4* row4 = reinterpret_cast<uint4*>(yact + (size_t)r * I);
+    uint32_t w[VEC][4];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+        const uint4 q = row4[v * 32 + lane];
+        w[v][0] = q.x; w[v][1] = q.y; w[v][2] = q.z; w[v][3] = q.w;
+    }
+    // Level 1 = the bf16 exponent (top 8 of the 15 magnitude bits). A row's exponents sit in a handful of values
+    // (shared-memory atomics on them serialise), and the threshold is almost always within eight exponents of the
+    // row's largest: count those eight per lane in one packed 64-bit register, add them up over the warp.
+    uint32_t mmax2 = 0u;  // largest magnitude of either half (packed 16-bit max); its exponent is the row's largest
+#pragma unroll
+    for (int v = 0; v < VEC; ++v)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mmax2 = __vmaxu2(mmax2, w[v][j] & 0x7fff7fffu);
+    const uint32_t emax = __reduce_max_sync(0xffffffffu, max(mmax2 & 0xffffu, mmax2 >> 16)) >> 7;
+    unsigned long long packed = 0ull;  // byte d = this lane's entries with exponent emax - d (a lane holds 8 * VEC <= 128)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t d0 = emax - ((w[v][j] >> 7) & 0xffu), d1 = emax - ((w[v][j] >> 23) & 0xffu);
+            if (d0 < 8u) packed += 1ull << (8u * d0);
+            if (d1 < 8u) packed += 1ull << (8u * d1);
+        }
+    int bucket = -1, above1 = 0;
+#pragma unroll
+    for (int d = 0; d < 8; ++d) {
+        const int tot = __reduce_add_sync(0xffffffffu, (int)((packed >> (8 * d)) & 0xffull));
+        if (bucket < 0) {
+            if (above1 + tot >= keep || emax == (uint32_t)d) bucket = (int)emax - d;  // exponent 0 is the last bucket
+            else above1 += tot;
+        }
+    }
+    if (bucket < 0) {  // a heavy-tailed row: the general histogram over all 256 exponents
+#pragma unroll
+        for (int j = 0; j < 8; ++j) hist[lane * 8 + j] = 0;
+        __syncwarp();
+#pragma unroll
+        for (int v = 0; v < VEC; ++v)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                atomicAdd(&hist[(w[v][j] & 0x7fffu) >> 7], 1);
+                atomicAdd(&hist[(w[v][j] >> 23) & 0xffu], 1);
+            }
+        __syncwarp();
+        topk_find_bucket<8>(hist, keep, 0, bucket, above1);
+        __syncwarp();
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) hist[lane * 4 + j] = 0;
+    __syncwarp();
+#pragma unroll
+    for (int v = 0; v < VEC; ++v)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m0 = (int)(w[v][j] & 0x7fffu), m1 = (int)((w[v][j] >> 16) & 0x7fffu);
+            if ((m0 >> 7) == bucket) atomicAdd(&hist[m0 & 127], 1);
+            if ((m1 >> 7) == bucket) atomicAdd(&hist[m1 & 127], 1);
+        }
+    __syncwarp();
+    int b2, above2;
+    topk_find_bucket<4>(hist, keep, above1, b2, above2);
+    const int thr = (bucket << 7) | b2;
+    const int need_equal = keep - above2;  // entries equal to the threshold that survive (the first ones in index order)
+    // entries equal to the threshold, per piece
+    int eq[VEC], eq_lane = 0;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+        int c = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            c += ((int)(w[v][j] & 0x7fffu) == thr) + ((int)((w[v][j] >> 16) & 0x7fffu) == thr);
+        eq[v] = c;
+        eq_lane += c;
+    }
+    const int eq_total = __reduce_add_sync(0xffffffffu, eq_lane);
+    const bool all_ties_survive = eq_total <= need_equal;
+    int before_piece = 0;  // slow path: threshold entries in earlier pieces (all lanes)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+        int quota = 1 << 30;
+        if (!all_ties_survive) {
+            int incl = eq[v];
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += o;
+            }
+            quota = need_equal - before_piece - (incl - eq[v]);
+            before_piece += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        uint32_t o[4];
+        bool changed = false;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t word = w[v][j];
+            const int m0 = (int)(word & 0x7fffu), m1 = (int)((word >> 16) & 0x7fffu);
+            bool k0 = m0 > thr, k1 = m1 > thr;
+            if (m0 == thr && quota > 0) { --quota; k0 = true; }
+            if (m1 == thr && quota > 0) { --quota; k1 = true; }
+            if (!k0) word &= 0xffff0000u;
+            if (!k1) word &= 0x0000ffffu;
+            changed |= word != w[v][j];
+            o[j] = word;
+        }
+        if (changed) row4[v * 32 + lane] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    __syncwarp();
+    }  // rows of this warp
+}
+
+template <int VEC>
+void launch_act_topk_warp(const ActTopkArgs& a, cudaStream_t stream) {
+    int blocks = (a.max_rows + 7) / 8;
+    if (blocks > 148 * 8) blocks = 148 * 8;  // warps walk the rows with a stride
+    act_topk_warp_kernel<VEC><<<blocks, kTopkThreads, 0, stream>>>((uint16_t*)a.yact, a.counts, a.offsets, a.E_tot,
+                                                                   a.keep, a.max_rows);
+}
+
 int launch_act_topk(const ActTopkArgs& a, cudaStream_t stream) {
     if (a.keep <= 0 || a.keep >= a.I || a.max_rows <= 0) return XMOE_OK;
-    if (a.I <= 8 * kTopkThreads && a.I % 8 == 0)
+    if (a.E_tot > kTopkMaxExperts) return XMOE_ERR_SHAPE;
+    if (a.I == 512) launch_act_topk_warp<2>(a, stream);
+    else if (a.I == 1024) launch_act_topk_warp<4>(a, stream);
+    else if (a.I == 2048) launch_act_topk_warp<8>(a, stream);
+    else if (a.I == 4096) launch_act_topk_warp<16>(a, stream);
+    else if (a.I <= 8 * kTopkThreads && a.I % 8 == 0)
         act_topk_kernel<<<a.max_rows, kTopkThreads, 0, stream>>>((uint16_t*)a.yact, a.counts, a.offsets, a.E_tot, a.I,
                                                                  a.keep);
     else
