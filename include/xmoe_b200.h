@@ -130,6 +130,17 @@ int xmoe_forward_routed_bounded(const xmoe_config* cfg, const xmoe_weights* w, c
                                 const int32_t* n_valid_dev, void* y, void* workspace, size_t workspace_bytes,
                                 xmoe_stream_t stream);
 
+/* The layer without its combine, the FF2 rows written TOKEN-MAJOR into a caller buffer: rows_out bf16
+ * [n_tokens * k_eff, hidden], row (token, slot) at index token * k_eff + slot (k_eff = top_k + num_shared_experts;
+ * slots whose expert id is -1 are left untouched). The FF2 epilogue stores there directly, so no gather follows.
+ * Routing either from router_logits (topk_idx NULL) or supplied (topk_idx / topk_w as in xmoe_forward_routed);
+ * act_scale as there. The caller sums a token's rows itself: xmoe_combine with topk_row[t, s] = t * k_eff + s, or,
+ * as the expert-parallel host does for replicated shared experts, lets them land in the buffer that the combine of
+ * another exchange already reads. No reference counterpart. */
+int xmoe_forward_scatter(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* router_logits,
+                         const int32_t* topk_idx, const void* topk_w, const float* act_scale, int32_t n_tokens,
+                         void* rows_out, void* workspace, size_t workspace_bytes, xmoe_stream_t stream);
+
 /* Per-stage device timing of xmoe_forward* calls, the counterpart of the reference harness's
  * per-kernel timing (sm120a/benchmarks/benchmark.cu:381-399). begin(max_steps > 0) makes every
  * forward record CUDA events between its stages on the caller's stream; read() synchronises

@@ -226,3 +226,28 @@ def test_gate_gemm_and_gated_forward(name, n):
     assert torch.equal(layer.last_logits.cpu(), lg)
     y2 = layer.forward(x.cuda(), lg.cuda())
     assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("n", [9, 300])
+def test_forward_scatter_writes_rows_token_major(n):
+    # the layer without its combine: the FF2 epilogue stores row (token, slot) at rows_out[token * k_eff + slot];
+    # the same bits as the packed rows of a plain forward, for router-made and for caller-supplied routing
+    shape = synth.scaled_shape(synth.SHAPES["toy"], num_shared_experts=1)
+    w, layer = Hh.build_layer(shape)
+    x, logits = synth.make_inputs(shape, w, n)
+    xd, ld = x.cuda(), logits.cuda()
+    y = layer.forward(xd, ld)
+    v = layer.view(n)
+    packed = v["out_rows"][v["topk_row"].reshape(-1).long()].clone()           # [n * k_eff, H] token-major
+    idx, gate = v["topk_idx"][:, : shape.top_k].contiguous().clone(), v["topk_w"][:, : shape.top_k].contiguous().clone()
+    poison = torch.full((n * shape.k_eff + 3, shape.hidden), -7.0, dtype=torch.bfloat16, device="cuda")
+    out = layer.forward_scatter(xd, poison.clone(), router_logits=ld)
+    torch.cuda.synchronize()
+    assert layer.status(n) == 0
+    assert torch.equal(out[: n * shape.k_eff], packed) and (out[n * shape.k_eff:] == -7.0).all()
+    out2 = layer.forward_scatter(xd, poison.clone(), topk_idx=idx, topk_w=gate)
+    assert torch.equal(out2[: n * shape.k_eff], packed)
+    # and the combine over those rows is the layer output
+    from xcaliber_b200 import ops
+    slots = torch.arange(n * shape.k_eff, dtype=torch.int32, device="cuda").reshape(n, shape.k_eff)
+    assert torch.equal(ops.combine(out, slots), y)

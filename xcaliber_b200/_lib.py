@@ -74,6 +74,8 @@ SIGNATURES = {
                                       _P]),
     "xmoe_forward_routed_bounded": (C.c_int, [C.POINTER(XMoEConfig), C.POINTER(XMoEWeights), _P, _P, _P, _P, _I, _P, _P,
                                               _P, _SZ, _P]),
+    "xmoe_forward_scatter": (C.c_int, [C.POINTER(XMoEConfig), C.POINTER(XMoEWeights), _P, _P, _P, _P, _P, _I, _P, _P,
+                                       _SZ, _P]),
     "xmoe_gate_logits": (C.c_int, [_P, _P, _I, _I, _I, _P, _P, _P]),
     "xmoe_forward_gated": (C.c_int, [C.POINTER(XMoEConfig), C.POINTER(XMoEWeights), _P, _P, _P, _I, _P, _P, _SZ, _P]),
     "xmoe_probe_mma_rate": (C.c_int, [_I, _I, C.POINTER(C.c_double), _P]),

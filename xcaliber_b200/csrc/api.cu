@@ -169,7 +169,7 @@ struct Layout {
     int k_eff, e_tot, kb_pad, mb, groups, nt, chunks;
     size_t rows;  // packed-row capacity
     size_t off_status, off_amax, off_scale, off_topk_idx, off_topk_w, off_topk_off, off_topk_row, off_hist, off_counts,
-        off_offsets, off_row_token, off_row_weight, off_xq, off_sfx, off_yact, off_out, off_ff2_partial, total;
+        off_offsets, off_row_token, off_row_weight, off_xq, off_sfx, off_yact, off_out, off_ff2_partial, off_row_dst, total;
     size_t off_x_in, off_logits_in, off_y_out, total_host_io;
 };
 
@@ -215,6 +215,7 @@ Layout make_layout(const xmoe_config* c, int n) {
     L.off_out = take(L.rows * (size_t)c->hidden * 2);
     // small token tiles: one fp32 partial-sum slot [token tile][128] per CTA for FF2's K split
     L.off_ff2_partial = take(ff2_token_tile(c, L.nt) <= 64 ? (size_t)kMaxSplitCtas * 64 * 128 * 4 : 0);
+    L.off_row_dst = take(L.rows * 8);  // per-row destinations of xmoe_forward_routed_scatter
     L.total = o;
     L.off_x_in = take((size_t)n * c->hidden * 2);
     L.off_logits_in = take((size_t)n * c->num_experts * 2);
@@ -338,16 +339,17 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
                  const int32_t* ext_idx, const void* ext_w, const float* ext_scale, int n, void* y, void* ws,
                  size_t ws_bytes, cudaStream_t stream, const int32_t* n_valid_dev = nullptr,
                  const xmoe_ep_buffers* ep_ret = nullptr, unsigned long long* row_dst = nullptr,
-                 bool prequantised = false, bool scalars_precleared = false) {
+                 bool prequantised = false, bool scalars_precleared = false, void* scatter_rows = nullptr) {
     int rc = check_cfg(cfg);
     if (prequantised && (!ext_idx || !ext_scale || cfg->top_k + cfg->num_shared_experts != 1)) return XMOE_ERR_ARG;
     if (ep_ret && (!row_dst || !ext_idx || cfg->top_k + cfg->num_shared_experts != 1)) return XMOE_ERR_ARG;
+    if (scatter_rows && (ep_ret || y)) return XMOE_ERR_ARG;
     if (rc) return rc;
     if (n < 0) return XMOE_ERR_ARG;
     if (n == 0) return XMOE_OK;
     if (n > (1 << 22)) return XMOE_ERR_LIMIT;
     if (!w || !x || !ws || (!logits && !ext_idx)) return XMOE_ERR_ARG;
-    if (!y && !ext_idx) return XMOE_ERR_ARG;  // y may be null only with caller-supplied routing (rows stay in the workspace)
+    if (!y && !ext_idx && !scatter_rows) return XMOE_ERR_ARG;  // y may be null only when the rows stay in the workspace or go to scatter_rows
     if (!w->w13_packed || !w->w13_sf || !w->w13_gs || !w->w2_q || !w->w2_scale) return XMOE_ERR_ARG;
     if (reinterpret_cast<uintptr_t>(ws) & 1023u) return XMOE_ERR_WORKSPACE;
     const Layout L = make_layout(cfg, n);
@@ -456,6 +458,10 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     if (ep_ret) {  // expert-parallel receive side: FF2 will store every row at its home rank
         if (cudaMemsetAsync(row_dst, 0, L.rows * 8, stream) != cudaSuccess) return XMOE_ERR_CUDA;
         if ((rc = launch_ep_row_dst(ep_ret, topk_row, row_dst, stream))) return rc;
+    } else if (scatter_rows) {  // FF2 stores row (token, slot) at scatter_rows[token * k_eff + slot]
+        row_dst = (unsigned long long*)(b + L.off_row_dst);
+        if (cudaMemsetAsync(row_dst, 0, L.rows * 8, stream) != cudaSuccess) return XMOE_ERR_CUDA;
+        if ((rc = launch_scatter_row_dst(topk_row, n * L.k_eff, H, scatter_rows, row_dst, stream))) return rc;
     }
     prof_mark(2, stream);
 
@@ -512,7 +518,7 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     prof_mark(6, stream);
 
     if ((rc = run_ff2(w->w2_q, w->w2_scale, b + L.off_yact, counts, offsets, b + L.off_out, status, L.e_tot, H, I,
-                      L.rows, ff2_token_tile(cfg, L.nt), stream, ep_ret ? row_dst : nullptr,
+                      L.rows, ff2_token_tile(cfg, L.nt), stream, (ep_ret || scatter_rows) ? row_dst : nullptr,
                       (float*)(b + L.off_ff2_partial), (uint32_t*)(b + kFf2FlagsOffset), (size_t)n * L.k_eff)))
         return rc;
     if (ep_ret && (rc = launch_ep_signal_ret(ep_ret, stream))) return rc;
@@ -586,6 +592,14 @@ int xmoe_forward_routed_bounded(const xmoe_config* cfg, const xmoe_weights* w, c
     if (!topk_idx || !topk_w) return XMOE_ERR_ARG;
     return forward_impl(cfg, w, x, nullptr, topk_idx, topk_w, act_scale, n, y, workspace, workspace_bytes,
                         (cudaStream_t)stream, n_valid_dev);
+}
+
+int xmoe_forward_scatter(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* router_logits,
+                         const int32_t* topk_idx, const void* topk_w, const float* act_scale, int32_t n, void* rows_out,
+                         void* workspace, size_t workspace_bytes, xmoe_stream_t stream) {
+    if (!rows_out || (!router_logits && (!topk_idx || !topk_w))) return XMOE_ERR_ARG;
+    return forward_impl(cfg, w, x, topk_idx ? nullptr : router_logits, topk_idx, topk_w, act_scale, n, nullptr, workspace,
+                        workspace_bytes, (cudaStream_t)stream, nullptr, nullptr, nullptr, false, false, rows_out);
 }
 
 int xmoe_gate_logits(const void* x, const void* gate_w, int32_t n, int32_t H, int32_t E, void* logits, uint32_t* status,

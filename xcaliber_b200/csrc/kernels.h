@@ -153,6 +153,9 @@ int launch_ff2(const Ff2Args& a, cudaStream_t stream);
 int launch_ff2_pair(const Ff2Args& a, cudaStream_t stream);  // 256-token tiles on CTA pairs (2-SM MMA)
 int launch_combine(const CombineArgs& a, cudaStream_t stream);
 int launch_act_topk(const ActTopkArgs& a, cudaStream_t stream);
+// topk_row is [N, k_eff] dense (n_slots = N * k_eff); row_dst must be zero on entry
+int launch_scatter_row_dst(const int32_t* topk_row, int n_slots, int hidden, void* rows_out, unsigned long long* row_dst,
+                           cudaStream_t stream);
 int launch_prep_nvfp4_sf(const void* sf_in, void* sf_out, int n_mats, int rows, int kblocks16, int mb, int kb_pad,
                          cudaStream_t stream);
 int launch_repack_gptq(const void* qweight, void* out, int E, int K, int O, cudaStream_t stream);

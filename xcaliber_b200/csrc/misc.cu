@@ -39,6 +39,27 @@ __global__ __launch_bounds__(256) void combine_kernel(const uint4* __restrict__ 
     }
 }
 
+// Destination table for FF2 rows that go straight to a token-major buffer rows_out [N * k_eff, H]: packed row
+// topk_row[t, s] -> byte address of row t * k_eff + s (slots without a row are skipped; row_dst is zeroed first,
+// so padding rows keep "nowhere").
+__global__ void scatter_row_dst_kernel(const int32_t* __restrict__ topk_row, int n_slots, size_t row_bytes,
+                                       unsigned long long base, unsigned long long* __restrict__ row_dst) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_slots; i += gridDim.x * blockDim.x) {
+        const int r = topk_row[i];
+        if (r >= 0) row_dst[r] = base + (unsigned long long)i * row_bytes;
+    }
+}
+
+int launch_scatter_row_dst(const int32_t* topk_row, int n_slots, int hidden, void* rows_out, unsigned long long* row_dst,
+                           cudaStream_t stream) {
+    if (n_slots <= 0) return XMOE_OK;
+    int blocks = (n_slots + 255) / 256;
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    scatter_row_dst_kernel<<<blocks, 256, 0, stream>>>(topk_row, n_slots, (size_t)hidden * 2,
+                                                       (unsigned long long)(uintptr_t)rows_out, row_dst);
+    return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+
 int launch_combine(const CombineArgs& a, cudaStream_t stream) {
     if (a.N <= 0) return XMOE_OK;
     if (a.H % 8) return XMOE_ERR_SHAPE;

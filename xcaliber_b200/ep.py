@@ -282,6 +282,16 @@ class ExpertParallelMoE:
     def _local_experts(self, x_rows, e_local, w):
         return self._local_layer(self._home_tokens)[1].forward_routed(x_rows, e_local, w, act_scale=self._scale)
 
+    def _shared_routing(self, n: int, device):
+        """Every token to every shared expert with weight 1 (cached per batch size)."""
+        key = ("shared_routing", n)
+        cached = self._row_dst.get(key)
+        if cached is None:
+            ns = self.shape.num_shared_experts
+            idx = torch.arange(ns, dtype=torch.int32, device=device).expand(n, ns).contiguous()
+            cached = self._row_dst[key] = (idx, torch.ones(n, ns, dtype=torch.bfloat16, device=device))
+        return cached
+
     def _shared(self, x):
         ns = self.shape.num_shared_experts
         n = x.shape[0]
@@ -317,6 +327,14 @@ class ExpertParallelMoE:
         _lib.check(dispatch(px.ref, x.data_ptr(), idx.data_ptr(), w.data_ptr(), px.topk_off.data_ptr(),
                             px.counts.data_ptr(), n, k, k, px.amax_global.data_ptr(), st), "xmoe_ep_dispatch")
         self._scale = ops.act_scale_from_amax(px.amax_global)
+        k_eff = k
+        if self.shared is not None:
+            # the replicated shared experts run on the home tokens while the other ranks' rows are still arriving;
+            # their FF2 epilogue writes each row where the final combine reads it (after the n * k routed slots)
+            ns = self.shape.num_shared_experts
+            sh_idx, sh_w = self._shared_routing(n, x.device)
+            self.shared.forward_scatter(x, px.ret_rows[n * k:], topk_idx=sh_idx, topk_w=sh_w, act_scale=self._scale)
+            k_eff = k + ns
         _lib.check(lib.xmoe_ep_wait_data(px.ref, px.e_recv.data_ptr(), px.w_recv.data_ptr(), px.n_recv.data_ptr(), st),
                    "xmoe_ep_wait_data")
         tile, local = self._local_layer(n)
@@ -340,11 +358,6 @@ class ExpertParallelMoE:
                 v = local.view(px.cap_rows)
                 ptrs = self._local_ptrs[tile] = (v["out_rows"].data_ptr(), v["topk_row"].data_ptr())
             _lib.check(lib.xmoe_ep_return(px.ref, ptrs[0], ptrs[1], n * k, st), "xmoe_ep_return")
-        k_eff = k
-        if self.shared is not None:
-            y_sh = self._shared(x)
-            px.ret_rows[n * k: n * k + y_sh.shape[0]].copy_(y_sh)
-            k_eff = k + self.shape.num_shared_experts
         _lib.check(lib.xmoe_ep_wait_ret(px.ref, st), "xmoe_ep_wait_ret")
         return ops.combine(px.ret_rows, px.slots(n, k_eff, x.device))
 

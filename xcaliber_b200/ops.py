@@ -228,6 +228,25 @@ class FusedMoE:
                                                      _ptr(n_valid), None, ws.data_ptr(), ws.numel(), _stream()),
               "xmoe_forward_routed_bounded")
 
+    def forward_scatter(self, x: torch.Tensor, rows_out: torch.Tensor, router_logits: torch.Tensor | None = None,
+                        topk_idx: torch.Tensor | None = None, topk_w: torch.Tensor | None = None,
+                        act_scale: torch.Tensor | None = None) -> torch.Tensor:
+        """The layer without its combine: FF2 row (token, slot) lands at rows_out[token * k_eff + slot] (bf16
+        [>= N * k_eff, hidden], contiguous), written by the FF2 epilogue itself. Routing from router_logits, or
+        supplied (topk_idx int32 / topk_w bf16, both [N, top_k], contiguous)."""
+        self._check_x(x, router_logits)
+        n = x.shape[0]
+        if n == 0:
+            return rows_out
+        if rows_out.dtype != torch.bfloat16 or not rows_out.is_contiguous() or \
+                rows_out.numel() < n * self.shape.k_eff * self.shape.hidden:
+            raise RuntimeError("rows_out must be a contiguous bf16 buffer of at least N * k_eff rows")
+        ws = self.workspace(n)
+        check(_lib.lib().xmoe_forward_scatter(C.byref(self.cfg), C.byref(self._wstruct), x.data_ptr(), _ptr(router_logits),
+                                              _ptr(topk_idx), _ptr(topk_w), _ptr(act_scale), n, rows_out.data_ptr(),
+                                              ws.data_ptr(), ws.numel(), _stream()), "xmoe_forward_scatter")
+        return rows_out
+
     def forward_host(self, x_host: torch.Tensor, logits_host: torch.Tensor, y_host: torch.Tensor) -> torch.Tensor:
         """Host (pinned) buffers in and out; copies and the stream sync happen inside the C call."""
         n = x_host.shape[0]
