@@ -336,6 +336,16 @@ def main() -> int:
             parity = parity_spot_check(shape, ckpt, layer, x_cpu, logits_cpu, y_step, n, world)
     sync_all()
 
+    ep_phases = None
+    if world > 1 and layer.peer is not None:
+        # where an expert-parallel step spends its time on this rank (a second short run, so that the event records do
+        # not sit inside the timed region)
+        layer.profile_phases(True)
+        for _ in range(5):
+            fwd()
+        ep_phases = {k: round(v, 5) for k, v in layer.phase_ms().items()}
+        layer.profile_phases(False)
+        sync_all()
     ops.profile_begin(args.steps)
     sampler = ClockSampler(local_rank, args.clock_csv)
     sampler.start()
@@ -534,6 +544,8 @@ def main() -> int:
                         "calls_in_flight": E2E_DEPTH if world == 1 else 1, "serial_value": e2e_serial_value},
                 "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline,
                 "device_status": statuses, **parity, **extra}
+        if ep_phases is not None:
+            line["ep_phase_ms_rank0"] = ep_phases
         if decode is not None:
             line["decode"] = decode
         emit(line)

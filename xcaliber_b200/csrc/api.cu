@@ -161,9 +161,18 @@ int pick_token_tile(const xmoe_config* c, int n) {
     return 32;
 }
 
-// FF2 may use a wider token tile than FF1: with a long K (I >= 2048) the 256-token tile keeps the
-// bf16 pipe at its full rate and the un-overlapped epilogue is small against the main loop.
-int ff2_token_tile(const xmoe_config* c, int nt) { return (nt == 128 && c->inter >= 2048) ? 256 : nt; }
+// FF2 may use a wider token tile than FF1: the 256-token tile (CTA pairs) keeps the bf16 pipe at its full rate
+// (an N = 128 MMA is bound by the issuing thread, not by the pipe), but its accumulator is single, so the
+// epilogue is not overlapped: it pays with a long K (I >= min_inter) and with experts that fill the tile
+// (average rows per expert >= min_rows = 96: at 128 rows per expert the pair kernel still wins, 385 against
+// 416 us on the gpt-oss shape; at 72 it loses, 1163 against 979 us on the DeepSeek-V3 shape). `rows_in_use`
+// = N * k_eff.
+int ff2_token_tile(const xmoe_config* c, int nt, size_t rows_in_use) {
+    static const int min_inter = [] { const char* e = getenv("XMOE_FF2_T256_MIN_INTER"); return e ? atoi(e) : 2048; }();
+    static const int min_rows = [] { const char* e = getenv("XMOE_FF2_T256_MIN_ROWS"); return e ? atoi(e) : 96; }();
+    const size_t e_tot = (size_t)c->num_experts + c->num_shared_experts;
+    return (nt == 128 && c->inter >= min_inter && rows_in_use >= (size_t)min_rows * e_tot) ? 256 : nt;
+}
 
 struct Layout {
     int k_eff, e_tot, kb_pad, mb, groups, nt, chunks;
@@ -214,7 +223,7 @@ Layout make_layout(const xmoe_config* c, int n) {
     L.off_yact = take(L.rows * (size_t)c->inter * 2);
     L.off_out = take(L.rows * (size_t)c->hidden * 2);
     // small token tiles: one fp32 partial-sum slot [token tile][128] per CTA for FF2's K split
-    L.off_ff2_partial = take(ff2_token_tile(c, L.nt) <= 64 ? (size_t)kMaxSplitCtas * 64 * 128 * 4 : 0);
+    L.off_ff2_partial = take(L.nt <= 64 ? (size_t)kMaxSplitCtas * 64 * 128 * 4 : 0);
     L.off_row_dst = take(L.rows * 8);  // per-row destinations of xmoe_forward_routed_scatter
     L.total = o;
     L.off_x_in = take((size_t)n * c->hidden * 2);
@@ -518,7 +527,8 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     prof_mark(6, stream);
 
     if ((rc = run_ff2(w->w2_q, w->w2_scale, b + L.off_yact, counts, offsets, b + L.off_out, status, L.e_tot, H, I,
-                      L.rows, ff2_token_tile(cfg, L.nt), stream, (ep_ret || scatter_rows) ? row_dst : nullptr,
+                      L.rows, ff2_token_tile(cfg, L.nt, (size_t)n * L.k_eff), stream,
+                      (ep_ret || scatter_rows) ? row_dst : nullptr,
                       (float*)(b + L.off_ff2_partial), (uint32_t*)(b + kFf2FlagsOffset), (size_t)n * L.k_eff)))
         return rc;
     if (ep_ret && (rc = launch_ep_signal_ret(ep_ret, stream))) return rc;

@@ -53,6 +53,11 @@ constexpr int kABytes = kTokHalf * kStageKBytes;   // 16 KiB: my tokens
 constexpr int kBBytes = kWTile * kStageKBytes;     // 16 KiB: my half of the weight tile
 constexpr int kStageBytes = kABytes + kBBytes + 3 * kSfBytes;  // 38 KiB
 constexpr int kStages = 5;
+#ifndef XMOE_FF1_PRODUCERS
+#define XMOE_FF1_PRODUCERS 2
+#endif
+constexpr int kProducers = XMOE_FF1_PRODUCERS;  // 2: tokens and weights are requested by different threads
+constexpr int kWeightProducerWarp = 13;
 // Warp roles, arranged so that register reallocation (setmaxnreg, per group of 4 consecutive warps)
 // can move registers from the single-thread roles to the epilogue:
 //   warps 0-3  : TMA producer, MMA issuer (peer: relay), scale-factor copies of tokens / gate rows
@@ -95,7 +100,8 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_pair_kernel(const __gri
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full_bar[s], leader ? 2 : 1);  // leader: own bytes + the peer's report that its stage landed
+            // one arrival per producer thread of this CTA; leader: + the peer's report that its stage landed
+            mbar_init(&full_bar[s], kProducers + (leader ? 1 : 0));
             mbar_init(&sf_ready[s], 3);
             mbar_init(&empty_bar[s], 1);
         }
@@ -196,13 +202,19 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_pair_kernel(const __gri
                             break;
                         }
                         uint8_t* st = smem + (size_t)s * kStageBytes;
-                        mbar_expect_tx(&full_bar[s], kStageBytes);
-                        tma_load_2d(st, &a.tm_x, ks * kStageKBytes, tok_row, &full_bar[s]);
-                        tma_load_2d(st + kABytes, &a.tm_w, ks * kStageKBytes, w_row, &full_bar[s]);
                         uint8_t* sf = st + kABytes + kBBytes;
-                        tma_load_1d(sf, sfx + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
-                        tma_load_1d(sf + kSfBytes, sfw_g + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
-                        tma_load_1d(sf + 2 * kSfBytes, sfw_u + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                        if (kProducers == 1) {
+                            mbar_expect_tx(&full_bar[s], kStageBytes);
+                            tma_load_2d(st, &a.tm_x, ks * kStageKBytes, tok_row, &full_bar[s]);
+                            tma_load_2d(st + kABytes, &a.tm_w, ks * kStageKBytes, w_row, &full_bar[s]);
+                            tma_load_1d(sf, sfx + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                            tma_load_1d(sf + kSfBytes, sfw_g + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                            tma_load_1d(sf + 2 * kSfBytes, sfw_u + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                        } else {  // this thread: my tokens and their scale factors
+                            mbar_expect_tx(&full_bar[s], kABytes + kSfBytes);
+                            tma_load_2d(st, &a.tm_x, ks * kStageKBytes, tok_row, &full_bar[s]);
+                            tma_load_1d(sf, sfx + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                        }
                         if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
                     }
                 }
@@ -271,6 +283,31 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_pair_kernel(const __gri
                             break;
                         }
                         mbar_arrive_cluster(leader_full + s * 8u);
+                        if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+                    }
+                }
+            }
+        } else if (kProducers == 2 && warp == kWeightProducerWarp) {
+            // ---- second producer: my half of the weight tile and the weight scale factors of both halves ----
+            if (lane == 0) {
+                uint32_t s = 0, ph = 0;
+                bool ok = true;
+                for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
+                    const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
+                    const int w_row = t.e * 2 * a.I + (int)rank * a.I + t.wt * kWTile;  // leader: gate rows, peer: up rows
+                    const uint8_t* sfw_g = a.sfw + ((size_t)(t.e * 2 + 0) * a.mb + t.wt) * a.kb_pad * 512;
+                    const uint8_t* sfw_u = a.sfw + ((size_t)(t.e * 2 + 1) * a.mb + t.wt) * a.kb_pad * 512;
+                    for (int ks = 0; ks < k_stages; ++ks) {
+                        if (!mbar_wait_cluster(&empty_bar[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
+                            ok = false;
+                            break;
+                        }
+                        uint8_t* st = smem + (size_t)s * kStageBytes;
+                        uint8_t* sf = st + kABytes + kBBytes;
+                        mbar_expect_tx(&full_bar[s], kBBytes + 2 * kSfBytes);
+                        tma_load_2d(st + kABytes, &a.tm_w, ks * kStageKBytes, w_row, &full_bar[s]);
+                        tma_load_1d(sf + kSfBytes, sfw_g + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                        tma_load_1d(sf + 2 * kSfBytes, sfw_u + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
                         if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
                     }
                 }

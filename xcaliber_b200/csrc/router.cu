@@ -116,13 +116,13 @@ __global__ __launch_bounds__(256) void router_topk_flat_kernel(
 // experts; ties always go to the lower index. Weights are the unbiased scores of the
 // winners, normalised over k, times routed_scale.
 // ------------------------------------------------------------------------------------
+// Largest 64-bit key of the warp: two 32-bit warp reductions (the largest high word, then the largest low word
+// among the lanes that hold it) instead of five rounds of 64-bit shuffles.
 __device__ __forceinline__ uint64_t warp_max_u64(uint64_t v) {
-#pragma unroll
-    for (int d = 16; d; d >>= 1) {
-        const uint64_t o = __shfl_xor_sync(0xffffffffu, v, d);
-        v = o > v ? o : v;
-    }
-    return v;
+    const uint32_t hi = (uint32_t)(v >> 32), lo = (uint32_t)v;
+    const uint32_t best_hi = __reduce_max_sync(0xffffffffu, hi);
+    const uint32_t best_lo = __reduce_max_sync(0xffffffffu, hi == best_hi ? lo : 0u);
+    return ((uint64_t)best_hi << 32) | best_lo;
 }
 __device__ __forceinline__ uint32_t ordered_f32(float f) {
     const uint32_t b = __float_as_uint(f);
@@ -146,14 +146,17 @@ __global__ __launch_bounds__(256) void router_topk_grouped_kernel(
     const uint16_t* row = logits + (size_t)token * E;
     const uint32_t gs = (uint32_t)E / (uint32_t)n_group;
 
-    // key = {ordered choice score, ~expert}; 0 = absent / dead.
+    // key = {ordered choice score, ~expert}; 0 = absent / dead. gid = the expert's group (one division per slot,
+    // not one per slot and group)
     uint64_t keys[J];
     float score[J];
+    int gid[J];
 #pragma unroll
     for (int j = 0; j < J; ++j) {
         const uint32_t e = lane + 32u * j;
         keys[j] = 0ull;
         score[j] = 0.f;
+        gid[j] = e < (uint32_t)E ? (int)(e / gs) : -1;
         if (e < (uint32_t)E) {
             const float s = lut[row[e]];
             score[j] = s;
@@ -169,17 +172,13 @@ __global__ __launch_bounds__(256) void router_topk_grouped_kernel(
         for (int g = 0; g < n_group; ++g) {
             uint64_t b1 = 0ull;
 #pragma unroll
-            for (int j = 0; j < J; ++j) {
-                const uint32_t e = lane + 32u * j;
-                if (e < (uint32_t)E && e / gs == (uint32_t)g) b1 = keys[j] > b1 ? keys[j] : b1;
-            }
+            for (int j = 0; j < J; ++j)
+                if (gid[j] == g) b1 = keys[j] > b1 ? keys[j] : b1;
             const uint64_t w1 = warp_max_u64(b1);
             uint64_t b2 = 0ull;
 #pragma unroll
-            for (int j = 0; j < J; ++j) {
-                const uint32_t e = lane + 32u * j;
-                if (e < (uint32_t)E && e / gs == (uint32_t)g && keys[j] != w1) b2 = keys[j] > b2 ? keys[j] : b2;
-            }
+            for (int j = 0; j < J; ++j)
+                if (gid[j] == g && keys[j] != w1) b2 = keys[j] > b2 ? keys[j] : b2;
             const uint64_t w2 = warp_max_u64(b2);
             const float sum = __fadd_rn(unordered_f32((uint32_t)(w1 >> 32)), unordered_f32((uint32_t)(w2 >> 32)));
             if (lane == (uint32_t)g) gscore = sum;
@@ -195,10 +194,8 @@ __global__ __launch_bounds__(256) void router_topk_grouped_kernel(
             if (lane == g) gkey = 0ull;
         }
 #pragma unroll
-        for (int j = 0; j < J; ++j) {
-            const uint32_t e = lane + 32u * j;
-            if (e < (uint32_t)E && !((allowed >> (e / gs)) & 1u)) keys[j] = 0ull;
-        }
+        for (int j = 0; j < J; ++j)
+            if (gid[j] >= 0 && !((allowed >> gid[j]) & 1u)) keys[j] = 0ull;
     }
 
     float my_score = 0.f;
@@ -353,17 +350,32 @@ __global__ __launch_bounds__(256) void route_scatter_kernel(
     }
     __syncthreads();
 
-    // in-order rank assignment: a warp walks its 32 tokens; lane k owns slot k.
+    // in-order rank assignment: a warp walks its 32 tokens; lane k owns slot k. The walk is serial (a token's rank
+    // depends on the tokens before it), so its inputs are fetched up front, 32 independent loads per lane, instead of
+    // one dependent global load per step.
     const int k_eff = topk + n_shared;
+    const int t_first = chunk * kPackChunk + warp * 32;
+    int e_pre[32];
+    uint16_t w_pre[32];
+#pragma unroll
     for (int i = 0; i < 32; ++i) {
-        const int t = chunk * kPackChunk + warp * 32 + i;
+        e_pre[i] = -1;
+        w_pre[i] = 0;
+        if (lane < topk && t_first + i < N) {
+            e_pre[i] = topk_idx[(size_t)(t_first + i) * idx_stride + lane];
+            w_pre[i] = topk_w[(size_t)(t_first + i) * idx_stride + lane];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const int t = t_first + i;
         if (t >= N) break;
         if (lane < k_eff) {
             int e;
             uint16_t w;
             if (lane < topk) {
-                e = topk_idx[(size_t)t * idx_stride + lane];
-                w = topk_w[(size_t)t * idx_stride + lane];
+                e = e_pre[i];
+                w = w_pre[i];
             } else {
                 e = E + (lane - topk);
                 w = 0x3f80u;  // 1.0 in bf16

@@ -269,6 +269,30 @@ class ExpertParallelMoE:
                                                       checkpoint.w2_scales[sh], device=device)
             self.shared = ops.FusedMoE(sh_shape, spw)
         self._scale = None
+        self._phase_events = None  # set by profile_phases(True): CUDA events between the phases of every call
+
+    # -- optional per-phase timing (benchmarks) ---------------------------------------------------------
+    PHASES = ("route", "dispatch", "shared", "wait_data", "local", "wait_ret", "combine")
+
+    def profile_phases(self, on: bool) -> None:
+        """Record a CUDA event at every phase boundary of the following peer-transport calls."""
+        self._phase_events = [] if on else None
+
+    def phase_ms(self) -> dict:
+        """Mean milliseconds per phase over the recorded calls (synchronises); clears the record."""
+        calls, self._phase_events = self._phase_events or [], []
+        torch.cuda.synchronize()
+        out = {name: 0.0 for name in self.PHASES}
+        for marks in calls:
+            for name, a, b in zip(self.PHASES, marks[:-1], marks[1:]):
+                out[name] += a.elapsed_time(b)
+        return {k: v / max(len(calls), 1) for k, v in out.items()}
+
+    def _mark(self, marks):
+        if marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            marks.append(ev)
 
     def _local_layer(self, home_tokens: int):
         """The local pipeline with the token tile fixed from this rank's own batch (both transports
@@ -312,6 +336,8 @@ class ExpertParallelMoE:
         if n > px.max_tokens:
             raise RuntimeError(f"{n} tokens exceed the exchange buffers (max_tokens={px.max_tokens})")
         x = x.contiguous()
+        marks = [] if self._phase_events is not None else None
+        self._mark(marks)
         idx, w = ops.router_topk(router_logits, self.shape, self.router_weights)
         scale_local = ops.act_amax(x)
         st = _stream()
@@ -322,11 +348,13 @@ class ExpertParallelMoE:
                                        px.pack_status.data_ptr(), st), "xmoe_route_pack")
         _lib.check(lib.xmoe_ep_post_counts(px.ref, px.counts.data_ptr(), scale_local[2:3].data_ptr(), st),
                    "xmoe_ep_post_counts")
+        self._mark(marks)
         quantised = self.fused_return and self.quantised_dispatch
         dispatch = lib.xmoe_ep_dispatch_quantised if quantised else lib.xmoe_ep_dispatch
         _lib.check(dispatch(px.ref, x.data_ptr(), idx.data_ptr(), w.data_ptr(), px.topk_off.data_ptr(),
                             px.counts.data_ptr(), n, k, k, px.amax_global.data_ptr(), st), "xmoe_ep_dispatch")
         self._scale = ops.act_scale_from_amax(px.amax_global)
+        self._mark(marks)
         k_eff = k
         if self.shared is not None:
             # the replicated shared experts run on the home tokens while the other ranks' rows are still arriving;
@@ -335,8 +363,10 @@ class ExpertParallelMoE:
             sh_idx, sh_w = self._shared_routing(n, x.device)
             self.shared.forward_scatter(x, px.ret_rows[n * k:], topk_idx=sh_idx, topk_w=sh_w, act_scale=self._scale)
             k_eff = k + ns
+        self._mark(marks)
         _lib.check(lib.xmoe_ep_wait_data(px.ref, px.e_recv.data_ptr(), px.w_recv.data_ptr(), px.n_recv.data_ptr(), st),
                    "xmoe_ep_wait_data")
+        self._mark(marks)
         tile, local = self._local_layer(n)
         if self.fused_return:
             # the FF2 epilogue stores each row at its home rank; no separate return copy
@@ -358,8 +388,14 @@ class ExpertParallelMoE:
                 v = local.view(px.cap_rows)
                 ptrs = self._local_ptrs[tile] = (v["out_rows"].data_ptr(), v["topk_row"].data_ptr())
             _lib.check(lib.xmoe_ep_return(px.ref, ptrs[0], ptrs[1], n * k, st), "xmoe_ep_return")
+        self._mark(marks)
         _lib.check(lib.xmoe_ep_wait_ret(px.ref, st), "xmoe_ep_wait_ret")
-        return ops.combine(px.ret_rows, px.slots(n, k_eff, x.device))
+        self._mark(marks)
+        y = ops.combine(px.ret_rows, px.slots(n, k_eff, x.device))
+        self._mark(marks)
+        if marks is not None:
+            self._phase_events.append(marks)
+        return y
 
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
         if self.peer is not None:
