@@ -122,7 +122,8 @@ int xmoe_forward_routed(const xmoe_config* cfg, const xmoe_weights* w, const voi
                         const void* topk_w, const float* act_scale, int32_t n_tokens, void* y, void* workspace,
                         size_t workspace_bytes, xmoe_stream_t stream);
 /* Same for a buffer of n_tokens rows of which only the first *n_valid_dev (device int32, may be
- * NULL) are in use: the others must carry expert id -1 and are not scanned by the quantiser.
+ * NULL) are in use: the others are neither walked by the route pack nor scanned by the quantiser (their entries
+ * of the workspace's index arrays keep whatever an earlier call left there).
  * y may be NULL here and above: the combine is skipped and the FF2 rows stay in the workspace.
  * No reference counterpart (used by the expert-parallel receive path). */
 int xmoe_forward_routed_bounded(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const int32_t* topk_idx,

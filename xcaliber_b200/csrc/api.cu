@@ -462,6 +462,7 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
     p.row_token = (int32_t*)(b + L.off_row_token);
     p.row_weight = b + L.off_row_weight;
     p.status = status;
+    p.n_valid = n_valid_dev;
     prof_mark(1, stream);
     if ((rc = launch_route_pack(p, stream))) return rc;
     if (ep_ret) {  // expert-parallel receive side: FF2 will store every row at its home rank

@@ -304,10 +304,17 @@ __global__ __launch_bounds__(kThreads, 1) void ff1_nvfp4_pair_kernel(const __gri
                         }
                         uint8_t* st = smem + (size_t)s * kStageBytes;
                         uint8_t* sf = st + kABytes + kBBytes;
+#ifdef XMOE_FF1_EXPERIMENT_SKIP_SFU  // timing experiment only (wrong results): one request fewer per stage
+                        mbar_expect_tx(&full_bar[s], kBBytes + kSfBytes);
+                        tma_load_2d(st + kABytes, &a.tm_w, ks * kStageKBytes, w_row, &full_bar[s]);
+                        tma_load_1d(sf + kSfBytes, sfw_g + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+                        (void)sfw_u;
+#else
                         mbar_expect_tx(&full_bar[s], kBBytes + 2 * kSfBytes);
                         tma_load_2d(st + kABytes, &a.tm_w, ks * kStageKBytes, w_row, &full_bar[s]);
                         tma_load_1d(sf + kSfBytes, sfw_g + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
                         tma_load_1d(sf + 2 * kSfBytes, sfw_u + (size_t)ks * kSfBytes, kSfBytes, &full_bar[s]);
+#endif
                         if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
                     }
                 }

@@ -619,11 +619,16 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 bool ok = true;
                 // 16 bytes (32 weights) at a time: four words -> sixteen bf16x2 registers -> one 16-column store
                 constexpr int kChunksPerPart = kStageK / 32 / Cfg::kSplit;
+                // all of the row's 16-byte pieces first (independent loads in flight together: with one load per
+                // piece the warps stalled on the shared-memory scoreboard for a third of their issue cycles)
+                uint4 raw[kStageK / 32];
+#pragma unroll
+                for (int q = 0; q < kStageK / 32; ++q)
+                    raw[q] = lds_u128(st + row_off + (((uint32_t)(unit * (kStageK / 32) + q) ^ swz) * 16));
 #pragma unroll
                 for (int q = 0; q < kStageK / 32; ++q) {
                     const int part = q / kChunksPerPart;
-                    const uint32_t chunk = (uint32_t)(unit * (kStageK / 32) + q) ^ swz;
-                    const uint4 r4 = lds_u128(st + row_off + chunk * 16);
+                    const uint4 r4 = raw[q];
                     uint32_t o[16];
                     expand_word(r4.x, o, bias, s2);
                     expand_word(r4.y, o + 4, bias, s2);

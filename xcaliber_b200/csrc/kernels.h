@@ -48,6 +48,7 @@ struct PackArgs {
     int32_t* row_token;  // [R_cap]
     void* row_weight;    // bf16 [R_cap]
     uint32_t* status;
+    const int32_t* n_valid = nullptr;  // optional, device: tokens at and beyond *n_valid are not in use and are not walked
 };
 
 struct ActScale {  // same meaning as the reference's MoeActScale (preamble.cuh:12-15)

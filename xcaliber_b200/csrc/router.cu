@@ -246,10 +246,15 @@ __global__ __launch_bounds__(256) void router_topk_grouped_kernel(
 constexpr int kPackChunk = 256;
 constexpr int kMaxEtot = 1024 + 8;
 
+// n_valid (optional, device): only the first *n_valid tokens are in use (an expert-parallel receive buffer sized for
+// the worst case); chunks beyond them do nothing, and their rows of the index arrays are left as they are.
 __global__ __launch_bounds__(256) void route_hist_kernel(const int32_t* __restrict__ topk_idx, int N, int E,
                                                          int topk, int idx_stride, int n_shared,
-                                                         int32_t* __restrict__ chunk_hist) {
+                                                         int32_t* __restrict__ chunk_hist,
+                                                         const int32_t* __restrict__ n_valid) {
     __shared__ int hist[kMaxEtot];
+    if (n_valid) N = min(N, max(*n_valid, 0));
+    if ((int)blockIdx.x * kPackChunk >= N) return;  // the scatter pass only reads the chunks that hold tokens
     const int e_tot = E + n_shared;
     for (int e = threadIdx.x; e < e_tot; e += blockDim.x) hist[e] = 0;
     __syncthreads();
@@ -269,7 +274,13 @@ __global__ __launch_bounds__(256) void route_scatter_kernel(
     int32_t* __restrict__ topk_idx, uint16_t* __restrict__ topk_w, int N, int E, int topk, int idx_stride,
     int n_shared, const int32_t* __restrict__ chunk_hist, int n_chunks, int32_t* __restrict__ counts,
     int32_t* __restrict__ offsets, int32_t* __restrict__ topk_off, int32_t* __restrict__ topk_row,
-    int32_t* __restrict__ row_token, uint16_t* __restrict__ row_weight, uint32_t* __restrict__ status) {
+    int32_t* __restrict__ row_token, uint16_t* __restrict__ row_weight, uint32_t* __restrict__ status,
+    const int32_t* __restrict__ n_valid) {
+    if (n_valid) {
+        N = min(N, max(*n_valid, 0));
+        if (n_chunks > 1) n_chunks = max(1, (N + kPackChunk - 1) / kPackChunk);
+        if ((int)blockIdx.x >= n_chunks) return;  // chunk 0 always runs: it writes the counts and offsets
+    }
     __shared__ int total[kMaxEtot];
     __shared__ int before_chunk[kMaxEtot];
     __shared__ int start[kMaxEtot + 1];
@@ -440,11 +451,11 @@ int launch_route_pack(const PackArgs& a, cudaStream_t stream) {
     const int chunks = route_pack_chunks(a.N);
     if (chunks > 1)  // a single chunk builds its totals inside the scatter kernel
         route_hist_kernel<<<chunks, 256, 0, stream>>>(a.topk_idx, a.N, a.E, a.topk, a.idx_stride, a.n_shared,
-                                                      a.chunk_hist);
+                                                      a.chunk_hist, a.n_valid);
     route_scatter_kernel<<<chunks, 256, 0, stream>>>(a.topk_idx, (uint16_t*)a.topk_w, a.N, a.E, a.topk,
                                                      a.idx_stride, a.n_shared, a.chunk_hist, chunks, a.counts,
                                                      a.offsets, a.topk_off, a.topk_row, a.row_token,
-                                                     (uint16_t*)a.row_weight, a.status);
+                                                     (uint16_t*)a.row_weight, a.status, a.n_valid);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 
