@@ -117,10 +117,12 @@ struct Ff2Cfg {
     // every role with its barrier hand-offs but without loads, expansion or MMAs. Then stage
     // number = 2 * weight stage + unit, group = stage % 4 owns tensor-memory slot stage % kARing
     // and always meets the same weight slots (kARing and the weight ring are multiples of
-    // kDqGroups). The token ring and kARing are multiples of kIssuers (issuer = stage-in-tile % 4;
-    // tiles whose stage count is not a multiple of 4 shift that pairing, but with one accumulator
-    // stage every tile starts with all earlier stages consumed).
-    static constexpr int kAccStages = NT == 128 ? 2 : 1;
+    // kDqGroups). The token ring and kARing are multiples of kIssuers, and an issuing thread takes the
+    // units whose CTA-wide number is its own index modulo kIssuers (not the position inside the tile), so
+    // that it, too, always meets the same token and tensor-memory slots, whatever the tile lengths.
+    // two accumulator sets where tensor memory has room (NT 128: 2 x 128 columns; NT 32: 2 x 4 issuers x 32): the
+    // epilogue of one tile (or tile segment) overlaps the MMAs of the next
+    static constexpr int kAccStages = (NT == 128 || NT == 32) ? 2 : 1;
     static constexpr int kFirstDq = kFirstDqWarp + (kIssuers - 1);
     static constexpr int kThreads = 32 * (kFirstDq + 4 * kDqGroups);
     static constexpr int kAccBase = kARing * kACols;          // accumulators follow the A ring
@@ -132,7 +134,6 @@ struct Ff2Cfg {
                       (kIssuers == 1 || (kARing % kIssuers == 0 && (kBStages * kWUnits) % kIssuers == 0)),
                   "ring ownership");
     static_assert((kWStages * kWUnits) % kDqGroups == 0, "weight ring ownership");
-    static_assert(kIssuers == 1 || kAccStages == 1, "issuer/slot pairing relies on the per-tile drain");
     static constexpr size_t kSmemBytes =
         1024 + (size_t)kBStages * kBStageBytes + (size_t)kWStages * kWStageBytes + kTailBytes;
     static_assert(kSmemBytes <= 232448, "shared memory");
@@ -397,8 +398,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                     const int n_valid = t.count - t.nt_idx * NT;
                     slab16 = n_valid <= 8 ? 64u : (n_valid <= 16 ? 128u : (uint32_t)kSlab16);
                 }
-                // this thread's K units of the segment: the issuer-th, then every kIssuers-th
-                for (int ks = sg.ks0 + issuer; ks < sg.ks1; ks += kIssuers) {
+                // this thread's K units of the segment: those whose CTA-wide number is `issuer` modulo kIssuers
+                for (int ks = sg.ks0 + ((issuer - sg.it0) & (kIssuers - 1)); ks < sg.ks1; ks += kIssuers) {
                     const uint32_t it = (uint32_t)(sg.it0 + ks - sg.ks0);
                     const uint32_t bt = it / Cfg::kWUnits;  // token stage of this K unit
                     const uint32_t s = bt % kBStages, ph = (bt / kBStages) & 1u;
@@ -485,12 +486,16 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
             for (int c0 = 0; c0 < NT; c0 += 32) {
                 if (c0 >= n_valid) break;
                 uint32_t v[32];
-                tmem_ld32(lane_addr + c0, v);
+                // the segment's unit at offset o went to issuer (it0 + o) mod kIssuers: start from the issuer of
+                // offset 0 (it always has data), then add the issuers of offsets 1, 2, 3 that exist
+                const int p0 = sg.it0 & (kIssuers - 1);
+                tmem_ld32(lane_addr + p0 * NT + c0, v);
                 tmem_ld_wait();
-                if (kIssuers > 1) {  // add the other issuers' partial sums, in issuer order
+                if (kIssuers > 1) {
 #pragma unroll
-                    for (int p = 1; p < kIssuers; ++p) {
-                        if (p < real_units) {
+                    for (int o = 1; o < kIssuers; ++o) {
+                        if (o < real_units) {
+                            const int p = (p0 + o) & (kIssuers - 1);
 #pragma unroll
                             for (int hh = 0; hh < 2; ++hh) {  // 16 columns at a time: register budget
                                 uint32_t v2[16];
