@@ -442,25 +442,29 @@ def main() -> int:
     flops_ff2 = 2.0 * rows_local * shape.hidden * shape.inter
     w_bytes_ff1 = e_local * (2 * shape.inter * shape.hidden // 2 + 2 * shape.inter * shape.hidden // 16 + 8)
     w_bytes_ff2 = e_local * (shape.hidden * shape.inter // 2 + 2 * shape.hidden * ((shape.inter + 127) // 128))
-    avg_rows_per_expert = rows_local / max(e_local, 1)
-    tensor_bound = avg_rows_per_expert >= 256
     dom_ms = per_stage.get(dominant, 0.0)
+    # the bound of the dominant kernel is the slower of its two floors: algorithmic bytes at the measured copy
+    # bandwidth, flops at the tensor peak (NVFP4: nominal dense; bf16: measured burst)
+    fl = flops_ff1 if dominant == "ff1" else flops_ff2
+    by = (w_bytes_ff1 + rows_local * (shape.hidden // 2 + shape.hidden // 16 + 2 * shape.inter)) if dominant == "ff1" \
+        else (w_bytes_ff2 + rows_local * 2 * (shape.inter + shape.hidden))
+    tensor_peak = NVFP4_NOMINAL_TFLOPS if dominant == "ff1" else peaks["bf16_tflops"]
+    floor_tensor_ms = fl / (tensor_peak * 1e12) * 1e3
+    floor_hbm_ms = by / (peaks["hbm_gbs"] * 1e9) * 1e3
+    tensor_bound = floor_tensor_ms >= floor_hbm_ms
     if tensor_bound:
-        fl = flops_ff1 if dominant == "ff1" else flops_ff2
         achieved = fl / (dom_ms * 1e-3) / 1e12 if dom_ms else 0.0
         # the timed region is tens of milliseconds, not a seconds-long step: the burst figure is the denominator
-        peak = NVFP4_NOMINAL_TFLOPS if dominant == "ff1" else peaks["bf16_tflops"]
-        roofline = {"kernel": dominant, "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                    "frac": achieved / peak if peak else None, "traffic": None,
+        roofline = {"kernel": dominant, "bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
+                    "frac": achieved / tensor_peak if tensor_peak else None, "traffic": None,
                     "peak_source": ("nominal dense NVFP4 (no measured FP4 figure)" if dominant == "ff1"
                                     else f"{peaks['source']} bf16 burst"),
                     "frac_of_sustained": None if dominant == "ff1" else achieved / peaks["bf16_tflops_sustained"]}
     else:
-        by = (w_bytes_ff1 + rows_local * (shape.hidden // 2 + shape.hidden // 16 + 2 * shape.inter)) if dominant == "ff1" \
-            else (w_bytes_ff2 + rows_local * 2 * (shape.inter + shape.hidden))
         achieved = by / (dom_ms * 1e-3) / 1e9 if dom_ms else 0.0
         roofline = {"kernel": dominant, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": f"{peaks['source']} copy"}
+    roofline["floor_ms"] = {"tensor": round(floor_tensor_ms, 5), "hbm": round(floor_hbm_ms, 5)}
     traffic_file = ROOT / "profiles" / "traffic.json"
     if traffic_file.exists():
         tr = json.loads(traffic_file.read_text()).get(f"{args.workload}:{n}:{dominant}")
