@@ -301,7 +301,7 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
         const char* e = getenv("XMOE_FF2_PAIR");
         return !(e && e[0] == '0');
     }();
-    const bool pair = nt >= 256 && pair_enabled && num_sms() >= 2 && H > 128;
+    const bool pair = nt >= 256 && pair_enabled && num_sms() >= 2 && H > 128 && I % 64 == 0;
     const bool k64 = nt >= 256 && !pair;
     // weight box: 128 rows x (small token tiles: 128 bytes = two K units; else 64 or 32 bytes)
     const bool wide = nt <= 64;
@@ -310,12 +310,18 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
                           wide ? CU_TENSOR_MAP_SWIZZLE_128B
                                : (k64 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B));
     if (rc) return rc;
-    a.tok3d = (nt <= 64 && I % 64 == 0) ? 1 : 0;
-    if (a.tok3d) {
+    a.tok3d = ((nt <= 64 && I % 64 == 0) || pair) ? 1 : 0;
+    if (pair) {
+        // one copy per K unit (two slabs of K 64) of the 128, 64 or 32 token rows a CTA stages
+        if ((rc = make_tmap_kslabs(&a.tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 128, 2)) ||
+            (rc = make_tmap_kslabs(&a.tm_y_small, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 32, 2)) ||
+            (rc = make_tmap_kslabs(&a.tm_y_mid, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64, 2)))
+            return rc;
+    } else if (a.tok3d) {
         // small token tiles: one copy per two K units (K 256 = four slabs), for the full tile and for 8 / 16 rows
         if ((rc = make_tmap_kslabs(&a.tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, (uint32_t)nt, 4)) ||
-            (rc = make_tmap_kslabs(&a.tm_y8, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 8, 4)) ||
-            (rc = make_tmap_kslabs(&a.tm_y16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 16, 4)))
+            (rc = make_tmap_kslabs(&a.tm_y_small, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 8, 4)) ||
+            (rc = make_tmap_kslabs(&a.tm_y_mid, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 16, 4)))
             return rc;
     } else {
         rc = make_tmap_2d(&a.tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64,
@@ -323,10 +329,10 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
         if (rc) return rc;
     }
     if (nt <= 64 && !a.tok3d) {
-        rc = make_tmap_2d(&a.tm_y8, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64, 8,
+        rc = make_tmap_2d(&a.tm_y_small, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64, 8,
                           CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
-        rc = make_tmap_2d(&a.tm_y16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64, 16,
+        rc = make_tmap_2d(&a.tm_y_mid, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, yact, (uint64_t)I, rows, 64, 16,
                           CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
     }

@@ -62,12 +62,13 @@ constexpr int kTailBytes = 5120 + 8192;  // barriers + tile prefix + epilogue tr
 constexpr int kFirstDqWarp = 7;
 
 // NT <= 128: one K stage = one int4 group (K 128). NT = 128 has two accumulators (the epilogue
-// overlaps the next tile); NT = 32 / 64 spend the tensor-memory columns on one accumulator per
-// issuing thread instead. NT = 256 (long-K prefill): a single issuing thread sustains one K=16
+// overlaps the next tile) or, as TWO_ISSUERS, one accumulator for each of two issuing threads; NT = 32 / 64
+// spend the tensor-memory columns on one accumulator per issuing thread (four). NT = 256 (long-K prefill): a single issuing thread sustains one K=16
 // MMA per ~70 cycles at best, so only N = 256 (128 cycles of tensor pipe) runs the bf16 pipe at
 // full rate; the 256-column accumulator is then single and the stages are K 64.
-template <int NT>
+template <int NT, bool TWO_ISSUERS = false>
 struct Ff2Cfg {
+    static_assert(!TWO_ISSUERS || NT == 128, "the two-issuer variant exists for 128-token tiles");
     static constexpr int kStageK = NT >= 256 ? 64 : 128;
     static constexpr int kRawBytes = kBlockM * kStageK / 2;   // int4 tile: 128 rows x kStageK/2 bytes
     // Small token tiles are HBM-bound: their weight stage spans two K units, so that every row
@@ -97,9 +98,10 @@ struct Ff2Cfg {
 #ifndef XMOE_FF2_SPLIT
 #define XMOE_FF2_SPLIT 1
 #endif
-    static constexpr int kWStages = NT == 128 ? 12 : (NT == 64 ? XMOE_FF2_WS64 : (NT == 32 ? XMOE_FF2_WS32 : 16));  // weight ring (HBM latency)
-    static constexpr int kBStages = NT >= 256 ? 4 : (NT >= 128 ? 3 : (NT == 32 ? XMOE_FF2_BS32 : XMOE_FF2_BS64));  // token ring (L2 latency)
-    static constexpr int kIssuers = NT <= 64 ? 4 : 1;         // MMA-issuing threads (K stages round-robin)
+
+    static constexpr int kWStages = NT == 128 ? (TWO_ISSUERS ? 8 : 12) : (NT == 64 ? XMOE_FF2_WS64 : (NT == 32 ? XMOE_FF2_WS32 : 16));  // weight ring (HBM latency)
+    static constexpr int kBStages = NT >= 256 ? 4 : (NT >= 128 ? (TWO_ISSUERS ? 4 : 3) : (NT == 32 ? XMOE_FF2_BS32 : XMOE_FF2_BS64));  // token ring (L2 latency)
+    static constexpr int kIssuers = NT <= 64 ? 4 : (TWO_ISSUERS ? 2 : 1);         // MMA-issuing threads (K stages round-robin)
     static constexpr int kARing = NT >= 256 ? 8 : 4;          // expanded-weight buffers in tensor memory
     // Small token tiles hand a buffer over in two halves (K 64 each, own barriers): the issuer starts on the
     // first half while the second is still being expanded, and the dequant group gets the first half back
@@ -122,7 +124,7 @@ struct Ff2Cfg {
     // that it, too, always meets the same token and tensor-memory slots, whatever the tile lengths.
     // two accumulator sets where tensor memory has room (NT 128: 2 x 128 columns; NT 32: 2 x 4 issuers x 32): the
     // epilogue of one tile (or tile segment) overlaps the MMAs of the next
-    static constexpr int kAccStages = (NT == 128 || NT == 32) ? 2 : 1;
+    static constexpr int kAccStages = ((NT == 128 && !TWO_ISSUERS) || NT == 32) ? 2 : 1;
     static constexpr int kFirstDq = kFirstDqWarp + (kIssuers - 1);
     static constexpr int kThreads = 32 * (kFirstDq + 4 * kDqGroups);
     static constexpr int kAccBase = kARing * kACols;          // accumulators follow the A ring
@@ -193,10 +195,10 @@ __device__ __forceinline__ void expand_word(uint32_t w, uint32_t* o, __nv_bfloat
     o[3] = bits_from_bf162(__hmul2(__hsub2(bf162_from_bits(nib_pair_to_bf16_bits(w >> 12)), bias), s2));
 }
 
-template <int NT, bool KSPLIT>
-__global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(const __grid_constant__ Ff2Args a) {
+template <int NT, bool KSPLIT, bool TWO_ISSUERS>
+__global__ __launch_bounds__(Ff2Cfg<NT, TWO_ISSUERS>::kThreads, 1) void ff2_w4a16_kernel(const __grid_constant__ Ff2Args a) {
     static_assert(!KSPLIT || NT <= 64, "tiles are cut along K only for small token tiles");
-    using Cfg = Ff2Cfg<NT>;
+    using Cfg = Ff2Cfg<NT, TWO_ISSUERS>;
     constexpr int kARing = Cfg::kARing, kDqGroups = Cfg::kDqGroups, kAccBase = Cfg::kAccBase;
     constexpr int kStageK = Cfg::kStageK, kACols = Cfg::kACols;
     constexpr int kAccStages = Cfg::kAccStages, kWStages = Cfg::kWStages, kBStages = Cfg::kBStages;
@@ -248,8 +250,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         prefetch_tmap(&a.tm_w);
         prefetch_tmap(&a.tm_y);
         if (NT <= 64) {
-            prefetch_tmap(&a.tm_y8);
-            prefetch_tmap(&a.tm_y16);
+            prefetch_tmap(&a.tm_y_small);
+            prefetch_tmap(&a.tm_y_mid);
         }
     }
     if (warp == 1) {
@@ -332,8 +334,8 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 int box_rows = NT;
                 if (NT <= 64) {
                     const int n_valid = t.count - t.nt_idx * NT;
-                    if (n_valid <= 8) { tm = &a.tm_y8; box_rows = 8; }
-                    else if (n_valid <= 16) { tm = &a.tm_y16; box_rows = 16; }
+                    if (n_valid <= 8) { tm = &a.tm_y_small; box_rows = 8; }
+                    else if (n_valid <= 16) { tm = &a.tm_y_mid; box_rows = 16; }
                 }
                 const uint32_t slab_bytes = (uint32_t)box_rows * 128u;  // one slab: box_rows x 64 K
                 for (int ks = sg.ks0; ks < sg.ks1; ks += Cfg::kWUnits) {
@@ -372,7 +374,6 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
         // stages round-robin, each into its own accumulator; the epilogue adds the partial sums.
         if (lane == 0) {
             const int issuer = warp == 1 ? 0 : warp - kFirstDqWarp + 1;
-            constexpr uint32_t idesc = umma_idesc_bf16(kBlockM, NT);
             constexpr int kSlab16 = (NT * 128) >> 4;
             const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(b_base));
             uint32_t tile_n = 0;
@@ -393,10 +394,14 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
                 uint32_t first = 1u;
                 // slab stride of this tile's token stages: the producer fetches 8 or 16 rows when the tile holds that few
                 uint32_t slab16 = (uint32_t)kSlab16;
-                if (NT <= 64) {
+                uint32_t idesc = umma_idesc_bf16(kBlockM, NT);
+                if (NT <= 64 || TWO_ISSUERS) {
                     const TileInfo t = tile_decode(sg.tile, prefix, a.counts, a.offsets, a.E_tot, NT);
                     const int n_valid = t.count - t.nt_idx * NT;
-                    slab16 = n_valid <= 8 ? 64u : (n_valid <= 16 ? 128u : (uint32_t)kSlab16);
+                    if (NT <= 64) slab16 = n_valid <= 8 ? 64u : (n_valid <= 16 ? 128u : (uint32_t)kSlab16);
+                    // two issuers keep the tensor pipe, not the issuing thread, busy: a ragged tile then runs with a
+                    // narrower MMA N (its rows rounded up to 32; the columns beyond it are never stored)
+                    if (TWO_ISSUERS && n_valid < NT) idesc = umma_idesc_bf16(kBlockM, (uint32_t)((n_valid + 31) & ~31));
                 }
                 // this thread's K units of the segment: those whose CTA-wide number is `issuer` modulo kIssuers
                 for (int ks = sg.ks0 + ((issuer - sg.it0) & (kIssuers - 1)); ks < sg.ks1; ks += kIssuers) {
@@ -687,20 +692,20 @@ __global__ __launch_bounds__(Ff2Cfg<NT>::kThreads, 1) void ff2_w4a16_kernel(cons
     if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
-template <int NT, bool KSPLIT>
+template <int NT, bool KSPLIT, bool TWO_ISSUERS = false>
 int launch_ff2_nt(const Ff2Args& a, cudaStream_t stream) {
-    using Cfg = Ff2Cfg<NT>;
+    using Cfg = Ff2Cfg<NT, TWO_ISSUERS>;
     static bool attr_set_dev[kMaxDevices] = {};
     const int dev = device_slot();
     if (dev < 0) return XMOE_ERR_CUDA;
     bool& attr_set = attr_set_dev[dev];
     if (!attr_set) {
-        if (cudaFuncSetAttribute(ff2_w4a16_kernel<NT, KSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(ff2_w4a16_kernel<NT, KSPLIT, TWO_ISSUERS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)Cfg::kSmemBytes) != cudaSuccess)
             return XMOE_ERR_CUDA;
         attr_set = true;
     }
-    ff2_w4a16_kernel<NT, KSPLIT><<<a.num_sms, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(a);
+    ff2_w4a16_kernel<NT, KSPLIT, TWO_ISSUERS><<<a.num_sms, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(a);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 
@@ -718,7 +723,10 @@ int launch_ff2(const Ff2Args& a, cudaStream_t stream) {
     switch (a.nt) {
         case 32: return split ? launch_ff2_nt<32, true>(a, stream) : launch_ff2_nt<32, false>(a, stream);
         case 64: return split ? launch_ff2_nt<64, true>(a, stream) : launch_ff2_nt<64, false>(a, stream);
-        case 128: return launch_ff2_nt<128, false>(a, stream);
+        // 128-token tiles: with a long K (>= 12 units) two issuing threads, each with its own accumulator, beat one
+        // thread with two accumulator sets (DeepSeek-V3 shape, 16 units: 917 against 970-1020 us at 2048 tokens, 704
+        // against 994 us at 256); with a short K the overlapped epilogue wins (Qwen3 shape, 6 units: 275 against 383 us)
+        case 128: return a.groups >= 12 ? launch_ff2_nt<128, false, true>(a, stream) : launch_ff2_nt<128, false>(a, stream);
         case 256: return launch_ff2_nt<256, false>(a, stream);
         default: return XMOE_ERR_SHAPE;
     }

@@ -186,6 +186,8 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
         mbar_fence_init();
         prefetch_tmap(&a.tm_w);
         prefetch_tmap(&a.tm_y);
+        prefetch_tmap(&a.tm_y_small);
+        prefetch_tmap(&a.tm_y_mid);
     }
     if (warp == 1) {
         tmem_alloc_pair(tmem_slot, kTmemCols);
@@ -233,16 +235,19 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
             bool ok = true;
             for (int item = cluster_id; item < total_tiles && ok; item += n_clusters) {
                 const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
-                const int row = t.row0 + (int)rank * (tile_n_eff(t) >> 1);
+                // each CTA stages half of the tile's MMA N: the smallest of the 32-, 64- and 128-row boxes that holds it
+                const int half = tile_n_eff(t) >> 1;
+                const int row = t.row0 + (int)rank * half;
+                const CUtensorMap* tm = half <= 32 ? &a.tm_y_small : (half <= 64 ? &a.tm_y_mid : &a.tm_y);
+                const uint32_t stage_bytes = (half <= 32 ? 32u : (half <= 64 ? 64u : 128u)) * 256u;  // two slabs of K 64
                 for (int ks = 0; ks < k_stages; ++ks) {
                     if (!mbar_wait(&b_empty[s], ph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_MMA)) {
                         ok = false;
                         break;
                     }
                     uint8_t* b = b_base + (size_t)s * kBStageBytes;
-                    mbar_expect_tx(&b_full[s], kBStageBytes);
-                    tma_load_2d(b, &a.tm_y, ks * kStageK, row, &b_full[s]);
-                    tma_load_2d(b + kTokHalf * 128, &a.tm_y, ks * kStageK + 64, row, &b_full[s]);
+                    mbar_expect_tx(&b_full[s], stage_bytes);
+                    tma_load_3d(b, tm, 0, row, ks * (kStageK / 64), &b_full[s]);  // zero-filled beyond I
                     if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -250,7 +255,6 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
     } else if (warp == 1) {
         if (lane == 0 && leader) {
             // ------------------------------ MMA issuer (leader CTA) -----------------
-            constexpr int kSlab16 = (kTokHalf * 128) >> 4;
             const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(b_base));
             uint32_t tile_n = 0, s = 0, ph = 0, d = 0, dph = 0;
             bool ok = true;
@@ -268,8 +272,10 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
                 const uint32_t acc = tmem_base + kAccBase;
                 // the ragged last token tile of an expert runs with a narrower N (cost ~ N, floor at the
                 // issue rate): each CTA then stages N/2 of its rows instead of 128
-                const uint32_t idesc =
-                    umma_idesc_bf16(2 * kBlockM, (uint32_t)tile_n_eff(tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile)));
+                const int n_eff = tile_n_eff(tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile));
+                const uint32_t idesc = umma_idesc_bf16(2 * kBlockM, (uint32_t)n_eff);
+                // distance between the two K 64 slabs of a stage, in 16-byte units: the rows of the box the producers used
+                const uint32_t slab16 = (n_eff <= 64 ? 32u : (n_eff <= 128 ? 64u : 128u)) * 8u;
                 for (int ks = 0; ks < k_stages; ++ks) {
                     {
                         XMOE_T0();
@@ -287,7 +293,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
                     const uint32_t b_lo = b_lo0 + s * (uint32_t)(kBStageBytes >> 4);
 #pragma unroll
                     for (int kk = 0; kk < kStageK / 16; ++kk)
-                        mma_bf16_ts_pair(acc, a_tmem + kk * 8, b_lo + (kk >> 2) * kSlab16 + (kk & 3) * 2, idesc,
+                        mma_bf16_ts_pair(acc, a_tmem + kk * 8, b_lo + (kk >> 2) * slab16 + (kk & 3) * 2, idesc,
                                          (ks | kk) ? 1u : 0u);
                     // release the token stage and the A buffer in both CTAs
                     tc_commit_pair_mask(smem_u32(&b_empty[s]), 3);

@@ -98,11 +98,13 @@ struct Ff1Args {
 struct Ff2Args {
     CUtensorMap tm_w;  // u8 [E_tot*H, I/2], box (128 | 64 | 32) B x 128 rows, swizzle = box width
     CUtensorMap tm_y;  // bf16 [R_cap, I], box 64 elems x NT rows, 128-byte swizzle
-    // token tiles of NT <= 64 only: the same tensor with 8- and 16-row boxes, used when a tile holds
-    // that few tokens (the MMA still reads NT rows; the columns of the stale ones are never stored)
-    CUtensorMap tm_y8, tm_y16;
-    // NT <= 64 and I % 64 == 0: the three maps above are 3-D views [I/64][R_cap][64] of the same tensor with
-    // boxes of 4 x rows x 64, so that ONE copy fetches K 256 of a token tile as four 128-byte-swizzle slabs
+    // The same tensor with smaller boxes, used when a tile holds few tokens. Token tiles of NT <= 64: 8 and
+    // 16 rows (the MMA still reads NT rows; the columns of the stale ones are never stored). CTA pairs: 32 and
+    // 64 rows per CTA (the MMA N is the tile's rows rounded up to 32, each CTA stages half of them).
+    CUtensorMap tm_y_small, tm_y_mid;
+    // tok3d (NT <= 64 with I % 64 == 0, and always on CTA pairs): the three maps above are 3-D views
+    // [I/64][R_cap][64] of the same tensor with boxes of kblocks x rows x 64, so that ONE copy fetches K 256
+    // (NT <= 64) or K 128 (pairs) of a token tile as 128-byte-swizzle slabs of K 64
     int tok3d;
     const void* w2_scale;  // bf16 [E_tot, G, H]
     const int32_t* counts;
