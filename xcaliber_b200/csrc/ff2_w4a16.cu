@@ -26,8 +26,8 @@
 //               start at 10) that take the K stages round-robin into separate accumulators,
 //               which the epilogue adds in a fixed order: one thread issues at most one MMA per
 //               ~70 cycles, far below what the tensor pipe takes for N = 32.
-//   warps 2-5   epilogue: tcgen05.ld, transpose 32x32 blocks through shared memory so that
-//               each lane owns one token row, 16-byte stores to [packed row, H]
+//   warps 2-5   epilogue: tcgen05.ld (lane = output feature, register = token), bf16 stores of 64
+//               contiguous bytes per warp instruction to [packed row, H]
 // All mbarrier waits are bounded (see common.cuh).
 #include <cuda_bf16.h>
 
@@ -58,7 +58,7 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kMaxExperts = 1024 + 8;
 constexpr int kTmemCols = 512;
-constexpr int kTailBytes = 5120 + 8192;  // barriers + tile prefix + epilogue transpose
+constexpr int kTailBytes = 5120;  // barriers + tile prefix
 constexpr int kFirstDqWarp = 7;
 
 // NT <= 128: one K stage = one int4 group (K 128). NT = 128 has two accumulators (the epilogue
@@ -219,7 +219,6 @@ __global__ __launch_bounds__(Ff2Cfg<NT, TWO_ISSUERS>::kThreads, 1) void ff2_w4a1
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     int* prefix = reinterpret_cast<int*>(tail + 768);
-    uint16_t* transpose = reinterpret_cast<uint16_t*>(tail + 5120);  // 4 warps x 32 x 32 bf16
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -384,6 +383,17 @@ __global__ __launch_bounds__(Ff2Cfg<NT, TWO_ISSUERS>::kThreads, 1) void ff2_w4a1
                 const KSegment sg = walk.seg(si, cta);
                 const uint32_t as = tile_n % kAccStages;
                 const uint32_t aph = (tile_n / kAccStages) & 1u;
+                // slab stride of this tile's token stages: the producer fetches 8 or 16 rows when the tile holds that few
+                uint32_t slab16 = (uint32_t)kSlab16;
+                uint32_t idesc = umma_idesc_bf16(kBlockM, NT);
+                if (NT <= 64 || TWO_ISSUERS) {  // (decoded before the wait for the accumulator: the epilogue may still hold it)
+                    const TileInfo t = tile_decode(sg.tile, prefix, a.counts, a.offsets, a.E_tot, NT);
+                    const int n_valid = t.count - t.nt_idx * NT;
+                    if (NT <= 64) slab16 = n_valid <= 8 ? 64u : (n_valid <= 16 ? 128u : (uint32_t)kSlab16);
+                    // two issuers keep the tensor pipe, not the issuing thread, busy: a ragged tile then runs with a
+                    // narrower MMA N (its rows rounded up to 32; the columns beyond it are never stored)
+                    if (TWO_ISSUERS && n_valid < NT) idesc = umma_idesc_bf16(kBlockM, (uint32_t)((n_valid + 31) & ~31));
+                }
                 {
                     XMOE_T0();
                     if (!mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
@@ -392,17 +402,6 @@ __global__ __launch_bounds__(Ff2Cfg<NT, TWO_ISSUERS>::kThreads, 1) void ff2_w4a1
                 tc_fence_after();
                 const uint32_t acc = tmem_base + kAccBase + (as * kIssuers + issuer) * NT;
                 uint32_t first = 1u;
-                // slab stride of this tile's token stages: the producer fetches 8 or 16 rows when the tile holds that few
-                uint32_t slab16 = (uint32_t)kSlab16;
-                uint32_t idesc = umma_idesc_bf16(kBlockM, NT);
-                if (NT <= 64 || TWO_ISSUERS) {
-                    const TileInfo t = tile_decode(sg.tile, prefix, a.counts, a.offsets, a.E_tot, NT);
-                    const int n_valid = t.count - t.nt_idx * NT;
-                    if (NT <= 64) slab16 = n_valid <= 8 ? 64u : (n_valid <= 16 ? 128u : (uint32_t)kSlab16);
-                    // two issuers keep the tensor pipe, not the issuing thread, busy: a ragged tile then runs with a
-                    // narrower MMA N (its rows rounded up to 32; the columns beyond it are never stored)
-                    if (TWO_ISSUERS && n_valid < NT) idesc = umma_idesc_bf16(kBlockM, (uint32_t)((n_valid + 31) & ~31));
-                }
                 // this thread's K units of the segment: those whose CTA-wide number is `issuer` modulo kIssuers
                 for (int ks = sg.ks0 + ((issuer - sg.it0) & (kIssuers - 1)); ks < sg.ks1; ks += kIssuers) {
                     const uint32_t it = (uint32_t)(sg.it0 + ks - sg.ks0);
@@ -457,7 +456,6 @@ __global__ __launch_bounds__(Ff2Cfg<NT, TWO_ISSUERS>::kThreads, 1) void ff2_w4a1
         const int q = warp & 3;
         uint32_t tile_n = 0;
         uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
-        uint16_t* tp = transpose + q * 1024;  // this warp's 32 tokens x 32 features
         for (int si = 0; si < walk.n_seg; ++si, ++tile_n) {
             const KSegment sg = walk.seg(si, cta);
             const TileInfo t = tile_decode(sg.tile, prefix, a.counts, a.offsets, a.E_tot, NT);
@@ -491,6 +489,11 @@ __global__ __launch_bounds__(Ff2Cfg<NT, TWO_ISSUERS>::kThreads, 1) void ff2_w4a1
             for (int c0 = 0; c0 < NT; c0 += 32) {
                 if (c0 >= n_valid) break;
                 uint32_t v[32];
+                unsigned long long my_row = 0ull;  // where token c0 + lane goes (0: nowhere)
+                if (!gives_partial && c0 + lane < n_valid) {
+                    const int prow = t.row0 + c0 + lane;
+                    my_row = a.row_dst ? a.row_dst[prow] : (unsigned long long)(uintptr_t)(out + (size_t)prow * a.H);
+                }
                 // the segment's unit at offset o went to issuer (it0 + o) mod kIssuers: start from the issuer of
                 // offset 0 (it always has data), then add the issuers of offsets 1, 2, 3 that exist
                 const int p0 = sg.it0 & (kIssuers - 1);
@@ -529,26 +532,16 @@ __global__ __launch_bounds__(Ff2Cfg<NT, TWO_ISSUERS>::kThreads, 1) void ff2_w4a1
                         if (c0 + j < n_valid) part[j * kBlockM] = __uint_as_float(v[j]);
                     continue;
                 }
-                // lane = feature, v[j] = token c0+j  ->  shared [token][feature]
+                // lane = feature, v[j] = token c0 + j: store j of the warp writes 32 consecutive bf16 (64 bytes, two
+                // whole sectors) of one output row. The row's home is this GPU's row buffer or (expert parallel) a
+                // peer's return buffer; its address is fetched by the lane of the token's number and handed round.
+                const int hf = h_base + lane;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) tp[j * 32 + lane] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
-                __syncwarp();
-                // lane = token: 32 features = 64 contiguous bytes of its output row
-                const uint4* src = reinterpret_cast<const uint4*>(tp + lane * 32);
-                const uint4 r0 = src[0], r1 = src[1], r2 = src[2], r3 = src[3];
-                if (c0 + lane < n_valid) {
-                    const int prow = t.row0 + c0 + lane;
-                    // the row's home: this GPU's row buffer, or (expert parallel) a peer's return buffer
-                    uint16_t* row_ptr = a.row_dst ? reinterpret_cast<uint16_t*>(a.row_dst[prow]) : out + (size_t)prow * a.H;
-                    if (row_ptr) {
-                        uint4* dst = reinterpret_cast<uint4*>(row_ptr + h_base);
-                        if (h_base < a.H) dst[0] = r0;
-                        if (h_base + 8 < a.H) dst[1] = r1;
-                        if (h_base + 16 < a.H) dst[2] = r2;
-                        if (h_base + 24 < a.H) dst[3] = r3;
-                    }
+                for (int j = 0; j < 32; ++j) {
+                    const unsigned long long row = __shfl_sync(0xffffffffu, my_row, j);
+                    if (row && hf < a.H)
+                        reinterpret_cast<uint16_t*>((uintptr_t)row)[hf] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
                 }
-                __syncwarp();
             }
             if (gives_partial) {  // publish: stores, fence, then this warp's count on the flag
                 __threadfence();

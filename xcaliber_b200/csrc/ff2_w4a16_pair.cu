@@ -59,9 +59,12 @@ constexpr int kDqGroups = 4;
 constexpr int kAccBase = kARing * kACols;  // 256
 static_assert(kWStages % kDqGroups == 0 && kARing % kDqGroups == 0, "ring slots must stay with one dequant group");
 constexpr int kTmemCols = 512;
-constexpr int kFirstDqWarp = 7;
-constexpr int kThreads = 32 * (kFirstDqWarp + 4 * kDqGroups);  // 736
-constexpr int kTailBytes = 5120 + 16384;  // barriers + tile prefix + two 32-token x 128-feature staging tiles
+// warps: 0 weight producer, 1 MMA issuer / relay, 2-5 and 7-10 epilogue (two sets of four, one warp per tensor-memory
+// lane quadrant in each set; the sets take alternate 32-token chunks of a tile), 6 token producer, 11-26 dequantisers
+constexpr int kEpiSets = 2;
+constexpr int kFirstDqWarp = 7 + 4 * (kEpiSets - 1);
+constexpr int kThreads = 32 * (kFirstDqWarp + 4 * kDqGroups);  // 864
+constexpr int kTailBytes = 5120;  // barriers + tile prefix
 constexpr size_t kSmemBytes = 1024 + (size_t)kBStages * kBStageBytes + (size_t)kWStages * kWStageBytes + kTailBytes;
 static_assert(kSmemBytes <= 232448, "shared memory");
 static_assert(kAccBase + kTokTile <= kTmemCols, "TMEM budget");
@@ -130,10 +133,6 @@ __device__ __forceinline__ void mma_bf16_ts_pair(uint32_t d_tmem, uint32_t a_tme
         : "memory");
 }
 
-// STAGED: the epilogue gathers 32 tokens x 128 features in shared memory and stores 256-byte row segments (rows
-// that go to other GPUs); otherwise each lane stores its own 64-byte piece straight after a per-warp transpose
-// (local rows: no cross-warp barrier in the epilogue, 1.6 % faster on one GPU).
-template <bool STAGED>
 __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __grid_constant__ Ff2Args a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -148,11 +147,9 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
     uint64_t* adq_empty = adq_full + 8;                    // [8]  each CTA: MMAs reading the A buffer retired
     uint64_t* acc_full = adq_empty + 8;                    // [1]  each CTA
     uint64_t* acc_empty = acc_full + 1;                    // [1]  leader: both epilogues drained
-    uint64_t* epi_bar = acc_empty + 1;                     // [2]  local: the four epilogue warps filled a staging tile
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 2);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     int* prefix = reinterpret_cast<int*>(tail + 640);
-    uint16_t* transpose = reinterpret_cast<uint16_t*>(tail + 5120);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -179,9 +176,7 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
             mbar_init(&adq_empty[s], 1);
         }
         mbar_init(acc_full, 1);
-        mbar_init(acc_empty, 8);
-        mbar_init(&epi_bar[0], 4);
-        mbar_init(&epi_bar[1], 4);
+        mbar_init(acc_empty, 2 * 4 * kEpiSets);
         *abort_flag = 0u;
         mbar_fence_init();
         prefetch_tmap(&a.tm_w);
@@ -263,6 +258,15 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
             const long long t_start = clock64();
             (void)t_start;
             for (int item = cluster_id; item < total_tiles && ok; item += n_clusters, ++tile_n) {
+                // the ragged last token tile of an expert runs with a narrower N (cost ~ N, floor at the
+                // issue rate): each CTA then stages N/2 of its rows instead of 128. Decoded before the wait for the
+                // accumulator, i.e. while the epilogue of the previous tile runs.
+                int n_eff;
+                {
+                    XMOE_T0();
+                    n_eff = tile_n_eff(tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile));
+                    XMOE_TACC(tw_bp);
+                }
                 {
                     XMOE_T0();
                     if (!mbar_wait_cluster(acc_empty, (tile_n & 1u) ^ 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_EPI)) break;
@@ -270,9 +274,6 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
                 }
                 tc_fence_after();
                 const uint32_t acc = tmem_base + kAccBase;
-                // the ragged last token tile of an expert runs with a narrower N (cost ~ N, floor at the
-                // issue rate): each CTA then stages N/2 of its rows instead of 128
-                const int n_eff = tile_n_eff(tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile));
                 const uint32_t idesc = umma_idesc_bf16(2 * kBlockM, (uint32_t)n_eff);
                 // distance between the two K 64 slabs of a stage, in 16-byte units: the rows of the box the producers used
                 const uint32_t slab16 = (n_eff <= 64 ? 32u : (n_eff <= 128 ? 64u : 128u)) * 8u;
@@ -328,98 +329,53 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
                 }
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < kFirstDqWarp) {
         // ------------------------------ epilogue (my 128 features x 256 tokens) -----
-        // tcgen05.ld gives a thread one feature (lane) of 32 tokens (columns). The four warps write their 32
-        // features of 32 tokens into a shared staging tile [token][128 features], meet on a barrier, and then
-        // every warp stores whole 256-byte row segments (two token rows per instruction, 16 bytes per lane): the
-        // stores of a row are contiguous, which is what peer memory over NVLink needs (each lane storing its own
-        // 64-byte piece of a different row, FF2 took 0.83 instead of 0.69 ms with 7/8 of the rows remote).
-        // Two staging tiles alternate; a warp refills a tile only after it has passed the barrier of the tile in
-        // between, which every warp reaches after its reads of the earlier one.
-        if constexpr (STAGED) {
-            const int q = warp & 3;
-            uint32_t tile_n = 0, chunk_n = 0;
-            uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
-            const uint32_t leader_acc_empty = map_to_cta(smem_u32(acc_empty), 0);
-            for (int item = cluster_id; item < total_tiles; item += n_clusters, ++tile_n) {
-                const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
-                if (!mbar_wait_cluster(acc_full, tile_n & 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
-                tc_fence_after();
-                const int h_cta = (t.wt * 2 + (int)rank) * kBlockM;  // first feature of this CTA
-                const int n_valid = min(kTokTile, t.count - t.nt_idx * kTokTile);
-                const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAccBase;
-                bool ok = true;
-                for (int c0 = 0; c0 < kTokTile && c0 < n_valid; c0 += 32, ++chunk_n) {
-                    uint16_t* stage = transpose + (chunk_n & 1u) * (32 * kBlockM);
-                    uint32_t v[32];
-                    tmem_ld32(lane_addr + c0, v);
-                    tmem_ld_wait();
-    #pragma unroll
-                    for (int j = 0; j < 32; ++j) stage[j * kBlockM + q * 32 + lane] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&epi_bar[chunk_n & 1u]);
-                    if (!mbar_wait(&epi_bar[chunk_n & 1u], (chunk_n >> 1) & 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) { ok = false; break; }
-                    // this warp's 8 token rows of the tile, two per instruction; lane = 16-byte piece of a 256-byte row
-                    const int piece = lane & 15;
-    #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int j = q * 8 + i * 2 + (lane >> 4);
-                        if (c0 + j < n_valid && h_cta + piece * 8 < a.H) {
-                            const int prow = t.row0 + c0 + j;
-                            // the row's home: this GPU's row buffer, or (expert parallel) a peer's return buffer
-                            uint16_t* row_ptr = a.row_dst ? reinterpret_cast<uint16_t*>(a.row_dst[prow]) : out + (size_t)prow * a.H;
-                            if (row_ptr)
-                                *reinterpret_cast<uint4*>(row_ptr + h_cta + piece * 8) =
-                                    *reinterpret_cast<const uint4*>(stage + j * kBlockM + piece * 8);
-                        }
-                    }
+        // tcgen05.ld gives a thread one feature (lane) of 32 tokens (registers), so store j of a warp writes 32
+        // consecutive bf16 (64 bytes, two whole sectors) of token j's output row: no transpose. A row's home is this
+        // GPU's row buffer or (expert parallel) a peer's return buffer; the addresses are fetched once per chunk by
+        // the lane of the token's number and handed round by shuffle. 64 contiguous bytes per instruction also suit
+        // peer memory over NVLink (lanes each storing 16-byte pieces of different rows did not: 0.83 against
+        // 0.69 ms with 7/8 of the rows remote; staging whole 256-byte segments through shared memory was slower
+        // than this at 2 and at 8 GPUs). Two sets of four warps take the 32-token chunks of a tile alternately (a
+        // warp reaches the lane quadrant warp % 4 of tensor memory): the accumulator is single, so the MMAs of the
+        // next tile wait for the whole drain.
+        const int q = warp & 3;
+        const int set = warp < 6 ? 0 : 1;
+        uint32_t tile_n = 0;
+        uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
+        const uint32_t leader_acc_empty = map_to_cta(smem_u32(acc_empty), 0);
+        for (int item = cluster_id; item < total_tiles; item += n_clusters, ++tile_n) {
+            const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
+            if (!mbar_wait_cluster(acc_full, tile_n & 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
+            tc_fence_after();
+            const int h = (t.wt * 2 + (int)rank) * kBlockM + q * 32 + lane;  // this lane's feature
+            const int n_valid = min(kTokTile, t.count - t.nt_idx * kTokTile);
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAccBase;
+#ifdef XMOE_TRACE
+            const long long te0 = clock64();
+#endif
+            for (int c0 = set * 32; c0 < n_valid; c0 += 32 * kEpiSets) {
+                uint32_t v[32];
+                tmem_ld32(lane_addr + c0, v);
+                const int prow = t.row0 + c0 + lane;
+                unsigned long long my_row = 0ull;
+                if (c0 + lane < n_valid)
+                    my_row = a.row_dst ? a.row_dst[prow] : (unsigned long long)(uintptr_t)(out + (size_t)prow * a.H);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const unsigned long long row = __shfl_sync(0xffffffffu, my_row, j);
+                    if (row && h < a.H)
+                        reinterpret_cast<uint16_t*>((uintptr_t)row)[h] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
                 }
-                if (!ok) break;
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
             }
-        } else {
-            const int q = warp & 3;
-            uint32_t tile_n = 0;
-            uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
-            uint16_t* tp = transpose + q * 1024;
-            const uint32_t leader_acc_empty = map_to_cta(smem_u32(acc_empty), 0);
-            for (int item = cluster_id; item < total_tiles; item += n_clusters, ++tile_n) {
-                const TileInfo t = tile_decode(item, prefix, a.counts, a.offsets, a.E_tot, kTokTile);
-                if (!mbar_wait_cluster(acc_full, tile_n & 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
-                tc_fence_after();
-                const int h_base = (t.wt * 2 + (int)rank) * kBlockM + q * 32;
-                const int n_valid = min(kTokTile, t.count - t.nt_idx * kTokTile);
-                const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAccBase;
-                for (int c0 = 0; c0 < kTokTile; c0 += 32) {
-                    if (c0 >= n_valid) break;
-                    uint32_t v[32];
-                    tmem_ld32(lane_addr + c0, v);
-                    tmem_ld_wait();
-    #pragma unroll
-                    for (int j = 0; j < 32; ++j) tp[j * 32 + lane] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
-                    __syncwarp();
-                    const uint4* src = reinterpret_cast<const uint4*>(tp + lane * 32);
-                    const uint4 r0 = src[0], r1 = src[1], r2 = src[2], r3 = src[3];
-                    if (c0 + lane < n_valid) {
-                        const int prow = t.row0 + c0 + lane;
-                        uint16_t* row_ptr = a.row_dst ? reinterpret_cast<uint16_t*>(a.row_dst[prow]) : out + (size_t)prow * a.H;
-                        if (row_ptr) {
-                            uint4* dst = reinterpret_cast<uint4*>(row_ptr + h_base);
-                            if (h_base < a.H) dst[0] = r0;
-                            if (h_base + 8 < a.H) dst[1] = r1;
-                            if (h_base + 16 < a.H) dst[2] = r2;
-                            if (h_base + 24 < a.H) dst[3] = r3;
-                        }
-                    }
-                    __syncwarp();
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
-            }
+#ifdef XMOE_TRACE
+            if (warp == 2 && lane == 0 && cluster_id < 148 && leader) g_ff2p_trace[cluster_id * 8 + 7] += clock64() - te0;
+#endif
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
         }
     } else {
         // ------------------------------ dequantiser (my 128 rows -> my tensor memory) --
@@ -488,14 +444,13 @@ extern "C" int xmoe_ff2_pair_trace_dump(long long* host_out) {
 }
 #endif
 
-template <bool STAGED>
-int launch_ff2_pair_t(const Ff2Args& a, cudaStream_t stream) {
+int launch_ff2_pair(const Ff2Args& a, cudaStream_t stream) {
     static bool attr_set_dev[kMaxDevices] = {};
     const int dev = device_slot();
     if (dev < 0) return XMOE_ERR_CUDA;
     bool& attr_set = attr_set_dev[dev];
     if (!attr_set) {
-        if (cudaFuncSetAttribute(ff2_w4a16_pair_kernel<STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(ff2_w4a16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kSmemBytes) != cudaSuccess)
             return XMOE_ERR_CUDA;
         attr_set = true;
@@ -519,16 +474,12 @@ int launch_ff2_pair_t(const Ff2Args& a, cudaStream_t stream) {
     int& resident_clusters = resident_clusters_dev[dev];
     if (!resident_clusters) {
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, ff2_w4a16_pair_kernel<STAGED>, &cfg) != cudaSuccess || n <= 0) n = a.num_sms / 2;
+        if (cudaOccupancyMaxActiveClusters(&n, ff2_w4a16_pair_kernel, &cfg) != cudaSuccess || n <= 0) n = a.num_sms / 2;
         resident_clusters = n < a.num_sms / 2 ? n : a.num_sms / 2;
         if (getenv("XMOE_DEBUG")) fprintf(stderr, "xmoe: ff2 pair kernel: %d resident clusters of 2 CTAs (occupancy query %d, %d SMs)\n", resident_clusters, n, a.num_sms);
     }
     cfg.gridDim = dim3((unsigned)(2 * resident_clusters), 1, 1);
-    return cudaLaunchKernelEx(&cfg, ff2_w4a16_pair_kernel<STAGED>, a) == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
-}
-
-int launch_ff2_pair(const Ff2Args& a, cudaStream_t stream) {
-    return a.row_dst ? launch_ff2_pair_t<true>(a, stream) : launch_ff2_pair_t<false>(a, stream);
+    return cudaLaunchKernelEx(&cfg, ff2_w4a16_pair_kernel, a) == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }
 
 }  // namespace xmoe
