@@ -328,10 +328,13 @@ int xmoe_ep_status(const xmoe_ep_buffers* b, xmoe_stream_t stream, uint32_t* bit
  * H % 64 == 0, E <= 256. status: a device status word as in the workspace (bounded waits report there). */
 int xmoe_gate_logits(const void* x, const void* gate_w, int32_t n_tokens, int32_t hidden, int32_t num_experts,
                      void* logits, uint32_t* status, xmoe_stream_t stream);
-/* xmoe_forward with the gate GEMM inside: the caller passes x and the router weight; logits_scratch holds
- * n_tokens * num_experts bf16. */
+/* xmoe_forward with the gate inside: the caller passes x and the router weight gate_w bf16 [num_experts, hidden].
+ * ONE kernel runs the gate GEMM and, in its epilogue, the router (bf16 rounding of the logits, top-k, gate
+ * weights) straight into the workspace's routing arrays: the same bits as xmoe_gate_logits followed by
+ * xmoe_forward, without the logits passing through HBM. logits_out: NULL, or n_tokens * num_experts bf16 that
+ * also receive the logits. */
 int xmoe_forward_gated(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* gate_w,
-                       void* logits_scratch, int32_t n_tokens, void* y, void* workspace, size_t workspace_bytes,
+                       void* logits_out, int32_t n_tokens, void* y, void* workspace, size_t workspace_bytes,
                        xmoe_stream_t stream);
 
 /* Measurement aid, no reference counterpart: the rate at which this GPU retires tcgen05.mma

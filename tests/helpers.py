@@ -22,6 +22,11 @@ def bits(t):
     return O.bf16_bits(t)
 
 
+def bits_t(t):
+    """bf16 tensor -> int16 tensor of its bit patterns (on the tensor's device)."""
+    return t.contiguous().view(torch.int16)
+
+
 def assert_routing_equal(view, ref, n=None):
     """Routing indices, packed rows and counts must be bit-exact."""
     S.assert_routing_equal(view, ref["pack"])

@@ -201,11 +201,12 @@ def test_activation_topk_exact_with_ties(rows, inter, keep):
     np.testing.assert_array_equal(O.bf16_bits(yd[:rows].cpu()), ref)
 
 
-@pytest.mark.parametrize("name,n", [("toy", 200), ("toy", 7), ("dsv3s", 300), ("qwen3s", 129)])
+@pytest.mark.parametrize("name,n", [("toy", 200), ("toy", 7), ("dsv3s", 300), ("qwen3s", 129), ("toysig", 65)])
 def test_gate_gemm_and_gated_forward(name, n):
     # the gate GEMM inside the library: logits against an fp32 matmul, then the gated forward must equal
     # the plain forward fed with those logits, bit for bit
     shape = {"toy": synth.SHAPES["toy"],
+             "toysig": synth.scaled_shape(synth.SHAPES["toy"], scoring="sigmoid", renormalize=False),
              "dsv3s": synth.scaled_shape(synth.SHAPES["dsv3"], hidden=512, inter=256, num_experts=64, act_topk_keep=0),
              "qwen3s": synth.scaled_shape(synth.SHAPES["qwen3"], hidden=512, inter=256, num_experts=128)}[name]
     from xcaliber_b200 import ops
@@ -220,12 +221,21 @@ def test_gate_gemm_and_gated_forward(name, n):
     step = torch.maximum(ref.abs(), ref.pow(2).mean().sqrt()) * 2.0 ** -7
     assert ((lg.float() - ref).abs() <= step).all()
     assert (lg == ref.to(torch.bfloat16)).float().mean() > 0.9
-    y = layer.forward_gated(x.cuda(), gw.cuda())
-    torch.cuda.synchronize()
-    assert layer.status(n) == 0
-    assert torch.equal(layer.last_logits.cpu(), lg)
+    # ONE kernel for gate GEMM + router: with and without the logits written out, the routing arrays and the
+    # output must equal the two-step path (gate_logits, then forward) bit for bit
     y2 = layer.forward(x.cuda(), lg.cuda())
-    assert torch.equal(y, y2)
+    v2 = layer.view(n)
+    idx2, w2 = v2["topk_idx"].clone(), v2["topk_w"].clone()
+    for keep in (True, False):
+        v2["topk_idx"].fill_(-5)
+        y = layer.forward_gated(x.cuda(), gw.cuda(), keep_logits=keep)
+        torch.cuda.synchronize()
+        assert layer.status(n) == 0
+        if keep:
+            assert torch.equal(layer.last_logits.cpu(), lg)
+        v = layer.view(n)
+        assert torch.equal(v["topk_idx"], idx2) and torch.equal(Hh.bits_t(v["topk_w"]), Hh.bits_t(w2))
+        assert torch.equal(y, y2)
 
 
 @pytest.mark.parametrize("n", [9, 300])

@@ -420,7 +420,9 @@ int forward_impl(const xmoe_config* cfg, const xmoe_weights* w, const void* x, c
         if (cudaEventRecord(side->join, side->stream) != cudaSuccess) return XMOE_ERR_CUDA;
     }
 
-    if (ext_idx) {
+    if (ext_idx && (const void*)ext_idx == (const void*)topk_idx) {
+        // routed in place: the gate GEMM of xmoe_forward_gated wrote the workspace's own arrays
+    } else if (ext_idx) {
         // caller-supplied routing: widen [N, top_k] to the [N, k_eff] workspace arrays
         if (L.k_eff == cfg->top_k) {  // same row pitch: one flat copy each (a pitched copy of 4-byte rows is slow)
             if (cudaMemcpyAsync(topk_idx, ext_idx, (size_t)n * L.k_eff * 4, cudaMemcpyDeviceToDevice, stream) !=
@@ -619,34 +621,74 @@ int xmoe_forward_scatter(const xmoe_config* cfg, const xmoe_weights* w, const vo
                         workspace_bytes, (cudaStream_t)stream, nullptr, nullptr, nullptr, false, false, rows_out);
 }
 
+namespace {
+// tensor maps of the gate GEMM: x [n, H] in boxes of min(n, 128) rows, gate_w [E, H] in one box of E rows
+int gate_tmaps(const void* x, const void* gate_w, int n, int H, int E, CUtensorMap* tm_x, CUtensorMap* tm_w, int* n_pad,
+               int* x_box, int* w_box) {
+    if (H <= 0 || H % 64 || E <= 0 || E > 256) return XMOE_ERR_SHAPE;
+    *n_pad = (E + 15) & ~15;
+    *x_box = n < 128 ? n : 128;
+    *w_box = E < *n_pad ? E : *n_pad;
+    int rc = make_tmap_2d(tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)H, (uint64_t)n, 64, (uint32_t)*x_box,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    return make_tmap_2d(tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, gate_w, (uint64_t)H, (uint64_t)E, 64, (uint32_t)*w_box,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+}
+}  // namespace
+
 int xmoe_gate_logits(const void* x, const void* gate_w, int32_t n, int32_t H, int32_t E, void* logits, uint32_t* status,
                      xmoe_stream_t stream) {
     if (!x || !gate_w || !logits || !status || n < 0) return XMOE_ERR_ARG;
     if (H <= 0 || H % 64 || E <= 0 || E > 256) return XMOE_ERR_SHAPE;
     if (n == 0) return XMOE_OK;
-    const int n_pad = (E + 15) & ~15;
-    const int x_box = n < 128 ? n : 128;
-    const int w_box = E < n_pad ? E : n_pad;
     CUtensorMap tm_x, tm_w;
-    int rc = make_tmap_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)H, (uint64_t)n, 64, (uint32_t)x_box,
-                          CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc) return rc;
-    rc = make_tmap_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, gate_w, (uint64_t)H, (uint64_t)E, 64, (uint32_t)w_box,
-                      CU_TENSOR_MAP_SWIZZLE_128B);
+    int n_pad, x_box, w_box;
+    const int rc = gate_tmaps(x, gate_w, n, H, E, &tm_x, &tm_w, &n_pad, &x_box, &w_box);
     if (rc) return rc;
     return launch_gate_logits(tm_x, tm_w, logits, n, E, H, n_pad, x_box, w_box, status, (cudaStream_t)stream);
 }
 
 int xmoe_forward_gated(const xmoe_config* cfg, const xmoe_weights* w, const void* x, const void* gate_w,
-                       void* logits_scratch, int32_t n, void* y, void* workspace, size_t workspace_bytes,
+                       void* logits_out, int32_t n, void* y, void* workspace, size_t workspace_bytes,
                        xmoe_stream_t stream) {
-    if (!cfg || !gate_w || !logits_scratch || !workspace) return XMOE_ERR_ARG;
-    if (n == 0) return XMOE_OK;
-    uint32_t* gate_status = (uint32_t*)workspace + kGateStatusWord;
-    if (cudaMemsetAsync(workspace, 0, kClearedBytes, (cudaStream_t)stream) != cudaSuccess) return XMOE_ERR_CUDA;
-    int rc = xmoe_gate_logits(x, gate_w, n, cfg->hidden, cfg->num_experts, logits_scratch, gate_status, stream);
+    if (!cfg || !w || !x || !gate_w || !workspace) return XMOE_ERR_ARG;
+    int rc = check_cfg(cfg);
     if (rc) return rc;
-    return forward_impl(cfg, w, x, logits_scratch, nullptr, nullptr, nullptr, n, y, workspace, workspace_bytes,
+    if (n < 0) return XMOE_ERR_ARG;
+    if (n == 0) return XMOE_OK;
+    if (n > (1 << 22)) return XMOE_ERR_LIMIT;
+    if (reinterpret_cast<uintptr_t>(workspace) & 1023u) return XMOE_ERR_WORKSPACE;
+    const Layout L = make_layout(cfg, n);
+    if (workspace_bytes < L.total) return XMOE_ERR_WORKSPACE;
+    uint8_t* b = (uint8_t*)workspace;
+    uint32_t* gate_status = (uint32_t*)workspace + kGateStatusWord;
+    CUtensorMap tm_x, tm_w;
+    int n_pad, x_box, w_box;
+    if ((rc = gate_tmaps(x, gate_w, n, cfg->hidden, cfg->num_experts, &tm_x, &tm_w, &n_pad, &x_box, &w_box))) return rc;
+    if (cudaMemsetAsync(workspace, 0, kClearedBytes, (cudaStream_t)stream) != cudaSuccess) return XMOE_ERR_CUDA;
+    // ONE kernel: gate GEMM, bf16 rounding of the logits, top-k and gate weights into the workspace's routing arrays
+    RouterArgs r;
+    r.logits = nullptr;
+    r.lut = w->sigmoid_lut;
+    r.bias = w->router_bias;
+    r.expert_scale = w->expert_scale;
+    r.topk_idx = (int32_t*)(b + L.off_topk_idx);
+    r.topk_w = b + L.off_topk_w;
+    r.N = n;
+    r.E = cfg->num_experts;
+    r.topk = cfg->top_k;
+    r.idx_stride = L.k_eff;
+    r.scoring = cfg->scoring;
+    r.renorm = cfg->renormalize;
+    r.n_group = cfg->n_group > 0 ? cfg->n_group : 1;
+    r.topk_group = cfg->topk_group;
+    r.routed_scale = cfg->routed_scale;
+    if ((rc = launch_gate_route(tm_x, tm_w, logits_out, n, cfg->num_experts, cfg->hidden, n_pad, x_box, w_box, gate_status,
+                                r, (cudaStream_t)stream)))
+        return rc;
+    // the layer takes the routing where it already lies (forward_impl recognises its own arrays)
+    return forward_impl(cfg, w, x, nullptr, r.topk_idx, r.topk_w, nullptr, n, y, workspace, workspace_bytes,
                         (cudaStream_t)stream, nullptr, nullptr, nullptr, false, /*scalars_precleared=*/true);
 }
 

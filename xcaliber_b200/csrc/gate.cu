@@ -8,10 +8,17 @@
 // gate rows as N (E rounded up to 16, at most 256), both staged by TMA with the 128-byte swizzle,
 // K 64 per stage. The accumulator (128 lanes x N columns of tensor memory) is read back by four
 // warps, lane = token, and stored as bf16 rows. Every wait is bounded.
+//
+// ROUTE != 0 (xmoe_forward_gated): the same kernel also routes. Each epilogue warp rounds the logits of its
+// 32 tokens to bf16 into a shared-memory tile (the pipeline stages are free by then) and then runs the
+// router's own per-token routine (router_core.cuh, one warp per token) on those rows: top-k indices and gate
+// weights go straight to the layer's workspace, the same bits as the gate GEMM followed by the router kernel,
+// and the logits need not touch HBM at all (they are stored only when the caller passes a buffer).
 #include <cuda_bf16.h>
 
 #include "common.cuh"
 #include "kernels.h"
+#include "router_core.cuh"
 
 namespace xmoe {
 
@@ -22,11 +29,13 @@ constexpr int kGateStages = 4;
 constexpr int kGateThreads = 192;  // producer warp, MMA warp, 4 epilogue warps
 constexpr int kGateABytes = kGateM * 128;
 
+// ROUTE: 0 logits only, 1 flat softmax top-k, 2 flat sigmoid top-k, 3 group-limited sigmoid top-k
+template <int ROUTE>
 __global__ __launch_bounds__(kGateThreads, 1) void gate_logits_kernel(const __grid_constant__ CUtensorMap tm_x,
                                                                      const __grid_constant__ CUtensorMap tm_w,
                                                                      uint16_t* __restrict__ logits, int n, int E, int H,
                                                                      int n_pad, int x_box_rows, int w_box_rows,
-                                                                     uint32_t* status) {
+                                                                     uint32_t* status, const RouterArgs r) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int b_bytes = n_pad * 128;
@@ -101,15 +110,42 @@ __global__ __launch_bounds__(kGateThreads, 1) void gate_logits_kernel(const __gr
             tc_fence_after();
             const int t = row0 + q * 32 + lane;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+            // ROUTE: this warp's 32 x E bf16 logits, row pitch n_pad + 2 (odd in 32-bit words: the lanes' 2-byte
+            // stores of one column fall into 32 different banks). All MMAs have retired: the stages are free.
+            const int pitch = n_pad + 2;
+            uint16_t* tile = reinterpret_cast<uint16_t*>(smem) + (size_t)q * 32 * pitch;
             for (int c0 = 0; c0 < n_pad; c0 += 16) {
                 uint32_t v[16];
                 tmem_ld16(lane_addr + c0, v);
                 tmem_ld_wait();
-                if (t < n) {
+                if (ROUTE) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) tile[lane * pitch + c0 + j] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
+                }
+                if (logits && t < n) {
                     uint16_t* dst = logits + (size_t)t * E + c0;
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         if (c0 + j < E) dst[j] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
+                }
+            }
+            if (ROUTE) {
+                __syncwarp();
+                const uint16_t* es = reinterpret_cast<const uint16_t*>(r.expert_scale);
+                uint16_t* tw = reinterpret_cast<uint16_t*>(r.topk_w);
+                for (int i = 0; i < 32; ++i) {
+                    const int token = row0 + q * 32 + i;
+                    if (token >= n) break;  // uniform across the warp
+                    const uint16_t* row = tile + i * pitch;
+                    if (ROUTE == 1)
+                        route_token_flat<false>(row, (uint32_t)lane, (uint32_t)token, es, r.topk_idx, tw, E, r.topk,
+                                                r.idx_stride, r.routed_scale, r.renorm);
+                    else if (ROUTE == 2)
+                        route_token_flat<true>(row, (uint32_t)lane, (uint32_t)token, es, r.topk_idx, tw, E, r.topk,
+                                               r.idx_stride, r.routed_scale, r.renorm);
+                    else
+                        route_token_grouped<8>(row, (uint32_t)lane, (uint32_t)token, r.lut, r.bias, es, r.topk_idx, tw, E,
+                                               r.topk, r.idx_stride, r.n_group, r.topk_group, r.routed_scale, r.renorm);
                 }
             }
         }
@@ -121,22 +157,47 @@ __global__ __launch_bounds__(kGateThreads, 1) void gate_logits_kernel(const __gr
 
 }  // namespace
 
-int launch_gate_logits(const CUtensorMap& tm_x, const CUtensorMap& tm_w, void* logits, int n, int E, int H, int n_pad,
-                       int x_box_rows, int w_box_rows, uint32_t* status, cudaStream_t stream) {
-    if (n <= 0) return XMOE_OK;
+namespace {
+template <int ROUTE>
+int launch_gate_t(const CUtensorMap& tm_x, const CUtensorMap& tm_w, void* logits, int n, int E, int H, int n_pad,
+                  int x_box_rows, int w_box_rows, uint32_t* status, const RouterArgs& r, cudaStream_t stream) {
     const size_t smem = 1024 + (size_t)kGateStages * (kGateABytes + (size_t)n_pad * 128) + 256;
     static size_t configured_dev[kMaxDevices] = {};
     const int dev = device_slot();
     if (dev < 0) return XMOE_ERR_CUDA;
     size_t& configured = configured_dev[dev];
     if (smem > configured) {
-        if (cudaFuncSetAttribute(gate_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(gate_logits_kernel<ROUTE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return XMOE_ERR_CUDA;
         configured = smem;
     }
-    gate_logits_kernel<<<(n + kGateM - 1) / kGateM, kGateThreads, smem, stream>>>(tm_x, tm_w, (uint16_t*)logits, n, E, H,
-                                                                                  n_pad, x_box_rows, w_box_rows, status);
+    gate_logits_kernel<ROUTE><<<(n + kGateM - 1) / kGateM, kGateThreads, smem, stream>>>(
+        tm_x, tm_w, (uint16_t*)logits, n, E, H, n_pad, x_box_rows, w_box_rows, status, r);
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
+}
+}  // namespace
+
+int launch_gate_logits(const CUtensorMap& tm_x, const CUtensorMap& tm_w, void* logits, int n, int E, int H, int n_pad,
+                       int x_box_rows, int w_box_rows, uint32_t* status, cudaStream_t stream) {
+    if (n <= 0) return XMOE_OK;
+    return launch_gate_t<0>(tm_x, tm_w, logits, n, E, H, n_pad, x_box_rows, w_box_rows, status, RouterArgs{}, stream);
+}
+
+// The gate GEMM with the router in its epilogue: `r` as for launch_router_topk (r.logits unused, r.N == n, r.E == E);
+// logits may be null.
+int launch_gate_route(const CUtensorMap& tm_x, const CUtensorMap& tm_w, void* logits, int n, int E, int H, int n_pad,
+                      int x_box_rows, int w_box_rows, uint32_t* status, const RouterArgs& r, cudaStream_t stream) {
+    if (n <= 0) return XMOE_OK;
+    if (r.n_group > 1 || r.bias != nullptr) {  // the checks of launch_router_topk
+        if (r.scoring != 1 || r.lut == nullptr) return XMOE_ERR_SHAPE;
+        if (r.n_group < 1 || r.n_group > 32 || E % r.n_group) return XMOE_ERR_SHAPE;
+        if (r.n_group > 1 && (E / r.n_group < 2 || r.topk_group < 1 || r.topk_group > r.n_group ||
+                              r.topk > r.topk_group * (E / r.n_group)))
+            return XMOE_ERR_SHAPE;
+        return launch_gate_t<3>(tm_x, tm_w, logits, n, E, H, n_pad, x_box_rows, w_box_rows, status, r, stream);
+    }
+    return r.scoring == 1 ? launch_gate_t<2>(tm_x, tm_w, logits, n, E, H, n_pad, x_box_rows, w_box_rows, status, r, stream)
+                          : launch_gate_t<1>(tm_x, tm_w, logits, n, E, H, n_pad, x_box_rows, w_box_rows, status, r, stream);
 }
 
 }  // namespace xmoe

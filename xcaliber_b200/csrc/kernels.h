@@ -180,6 +180,8 @@ int launch_ep_signal_ret(const xmoe_ep_buffers* b, cudaStream_t stream);
 // stale shared memory and only feed accumulator rows / columns that are never stored)
 int launch_gate_logits(const CUtensorMap& tm_x, const CUtensorMap& tm_w, void* logits, int n, int E, int H, int n_pad,
                        int x_box_rows, int w_box_rows, uint32_t* status, cudaStream_t stream);
+int launch_gate_route(const CUtensorMap& tm_x, const CUtensorMap& tm_w, void* logits, int n, int E, int H, int n_pad,
+                      int x_box_rows, int w_box_rows, uint32_t* status, const RouterArgs& r, cudaStream_t stream);
 int probe_mma_rate(int kind, int n_mma, double* tflops_out, cudaStream_t stream);
 int launch_repack_kmajor_int4(const void* w_in, void* out, size_t n_words, cudaStream_t stream);
 

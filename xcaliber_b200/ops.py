@@ -177,19 +177,22 @@ class FusedMoE:
                                       n, y.data_ptr(), ws.data_ptr(), ws.numel(), _stream()), "xmoe_forward")
         return y
 
-    def forward_gated(self, x: torch.Tensor, gate_weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        """The layer with the router gate GEMM inside: gate_weight bf16 [num_experts, hidden]. The logits it
-        used stay in `self.last_logits` (bf16 [N, num_experts])."""
+    def forward_gated(self, x: torch.Tensor, gate_weight: torch.Tensor, out: torch.Tensor | None = None,
+                      keep_logits: bool = False) -> torch.Tensor:
+        """The layer with the router gate inside: gate_weight bf16 [num_experts, hidden]. One kernel runs the gate
+        GEMM and the router; the logits reach HBM only with keep_logits (then in `self.last_logits`, bf16
+        [N, num_experts])."""
         self._check_x(x, None)
         n = x.shape[0]
         y = torch.empty_like(x) if out is None else out
         if n == 0:
             return y
         gw = gate_weight.to(torch.bfloat16).contiguous()
-        self.last_logits = torch.empty(n, self.shape.num_experts, dtype=torch.bfloat16, device=x.device)
+        self.last_logits = (torch.empty(n, self.shape.num_experts, dtype=torch.bfloat16, device=x.device)
+                            if keep_logits else None)
         ws = self.workspace(n)
         check(_lib.lib().xmoe_forward_gated(C.byref(self.cfg), C.byref(self._wstruct), x.data_ptr(), gw.data_ptr(),
-                                            self.last_logits.data_ptr(), n, y.data_ptr(), ws.data_ptr(), ws.numel(),
+                                            _ptr(self.last_logits), n, y.data_ptr(), ws.data_ptr(), ws.numel(),
                                             _stream()), "xmoe_forward_gated")
         return y
 
