@@ -336,6 +336,13 @@ int run_ff2(const void* w2_q, const void* w2_scale, const void* yact, const int3
                           CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
     }
+    a.scale2d = 0;
+    if (nt <= 64 && H >= 128) {
+        if ((rc = make_tmap_2d(&a.tm_s, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w2_scale, (uint64_t)H,
+                               (uint64_t)e_tot * (uint64_t)((I + 127) / 128), 128, 2, CU_TENSOR_MAP_SWIZZLE_NONE)))
+            return rc;
+        a.scale2d = 1;
+    }
     a.w2_scale = w2_scale;
     a.counts = counts;
     a.offsets = offsets;

@@ -248,6 +248,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT, TWO_ISSUERS>::kThreads, 1) void ff2_w4a1
         mbar_fence_init();
         prefetch_tmap(&a.tm_w);
         prefetch_tmap(&a.tm_y);
+        if (NT <= 64 && a.scale2d) prefetch_tmap(&a.tm_s);
         if (NT <= 64) {
             prefetch_tmap(&a.tm_y_small);
             prefetch_tmap(&a.tm_y_mid);
@@ -304,13 +305,22 @@ __global__ __launch_bounds__(Ff2Cfg<NT, TWO_ISSUERS>::kThreads, 1) void ff2_w4a1
                         XMOE_TACC(tw_prod);
                     }
                     uint8_t* st = w_base + (size_t)s * Cfg::kWStageBytes;
-                    const int units = min(Cfg::kWUnits, k_stages - ks);
-                    mbar_expect_tx(&w_full[s], Cfg::kWRawBytes + (uint32_t)units * scale_bytes);
-                    tma_load_2d(st, &a.tm_w, ks * (kStageK / 2), w_row, &w_full[s]);
-                    for (int u = 0; u < units; ++u)
-                        tma_load_1d(st + Cfg::kWRawBytes + u * 256,
-                                    scales + ((size_t)t.e * a.groups + ((ks + u) * kStageK) / 128) * a.H + h0, scale_bytes,
-                                    &w_full[s]);
+                    if (Cfg::kWUnits == 2 && a.scale2d) {
+                        // the scales of both K units in one request (a box of 2 groups x 128 features; beyond the
+                        // tensor it is zero-filled, beyond the expert's groups it feeds a phantom unit): every
+                        // request costs the copy engine about the same whatever its size
+                        mbar_expect_tx(&w_full[s], Cfg::kWRawBytes + 512u);
+                        tma_load_2d(st, &a.tm_w, ks * (kStageK / 2), w_row, &w_full[s]);
+                        tma_load_2d(st + Cfg::kWRawBytes, &a.tm_s, h0, t.e * a.groups + ks, &w_full[s]);
+                    } else {
+                        const int units = min(Cfg::kWUnits, k_stages - ks);
+                        mbar_expect_tx(&w_full[s], Cfg::kWRawBytes + (uint32_t)units * scale_bytes);
+                        tma_load_2d(st, &a.tm_w, ks * (kStageK / 2), w_row, &w_full[s]);
+                        for (int u = 0; u < units; ++u)
+                            tma_load_1d(st + Cfg::kWRawBytes + u * 256,
+                                        scales + ((size_t)t.e * a.groups + ((ks + u) * kStageK) / 128) * a.H + h0, scale_bytes,
+                                        &w_full[s]);
+                    }
                     if (++s == (uint32_t)kWStages) { s = 0; ph ^= 1u; }
                 }
             }

@@ -106,6 +106,10 @@ struct Ff2Args {
     // [I/64][R_cap][64] of the same tensor with boxes of kblocks x rows x 64, so that ONE copy fetches K 256
     // (NT <= 64) or K 128 (pairs) of a token tile as 128-byte-swizzle slabs of K 64
     int tok3d;
+    // NT <= 64 and H >= 128: the scales as a 2-D tensor [E_tot * G, H] with boxes of 2 groups x 128 features, so that
+    // ONE copy fetches the scales of both K units of a weight stage (scale2d = 1)
+    CUtensorMap tm_s;
+    int scale2d;
     const void* w2_scale;  // bf16 [E_tot, G, H]
     const int32_t* counts;
     const int32_t* offsets;
