@@ -23,7 +23,14 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     failures = []
-    for name, kw, n in [("toy", dict(), 96), ("dsv3", dict(hidden=512, inter=256, num_experts=64, act_topk_keep=0), 80)]:
+    # toy; DeepSeek-V3-like routing (groups, bias, shared expert) without and with the activation top-k; a gpt-oss-like
+    # shape (clamped SwiGLU, partial tiles); a shape whose FF2 runs on CTA pairs with rows stored at their home ranks
+    cases = [("toy", dict(), 96),
+             ("dsv3", dict(hidden=512, inter=256, num_experts=64, act_topk_keep=0), 80),
+             ("dsv3", dict(hidden=512, inter=256, num_experts=64, act_topk_keep=64), 72),
+             ("gptoss", dict(hidden=704, inter=352, num_experts=32), 100),
+             ("toy", dict(hidden=512, inter=2048), 512)]
+    for name, kw, n in cases:
         shape = synth.scaled_shape(synth.SHAPES[name], **kw)
         ck = synth.make_weights(shape, seed=0, device="cpu")
         xs, ls = [], []
@@ -35,7 +42,7 @@ def main():
         # peer: NVFP4 dispatch + FF2 stores rows at their home rank; peer-bf16: bf16 dispatch; peer-copy: also a
         # separate return kernel
         for transport in ("peer", "peer-bf16", "peer-copy", "nccl"):
-            ep = ExpertParallelMoE(shape, ck, device=dev, transport=transport.split("-")[0], max_tokens=128,
+            ep = ExpertParallelMoE(shape, ck, device=dev, transport=transport.split("-")[0], max_tokens=max(128, n + 8 * world),
                                    fused_return=transport != "peer-copy", quantised_dispatch=transport == "peer")
             for _ in range(3):  # repeated calls reuse the exchange buffers and their flags
                 ys[transport] = ep.forward(xs[rank].to(dev), ls[rank].to(dev))
