@@ -138,17 +138,19 @@ __global__ __launch_bounds__(256) void act_quant_pack_kernel(
          unit += (size_t)gridDim.x * 8) {
         const int t = (int)(unit / units_per_token);
         const int h0 = (int)(unit % units_per_token) * 512 + (int)lane * 16;
+        // the token's 16 values are fetched before its row numbers are looked at: the two loads do not depend on
+        // each other, and a warp's iterations are a chain of memory latencies
+        uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (h0 < H) {  // H is a multiple of 16
+            const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * H + h0);
+            const uint4 a = __ldg(src), b = __ldg(src + 1);
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+            w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+        }
         // a token none of whose slots got a row (expert id -1 in caller-supplied routing): nothing to store
         bool any_row = false;
         for (int k = 0; k < k_eff; ++k) any_row |= topk_row[(size_t)t * idx_stride + k] >= 0;
         if (!any_row) continue;
-        uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (h0 < H) {  // H is a multiple of 16
-            const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * H + h0);
-            const uint4 a = src[0], b = src[1];
-            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
-            w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
-        }
         uint32_t sbyte, q_lo, q_hi;
         nvfp4_quantise16(w, xgs, sbyte, q_lo, q_hi);
         // four neighbouring lanes hold the four block scales of one K64 block
