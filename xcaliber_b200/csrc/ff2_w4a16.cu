@@ -68,7 +68,7 @@ constexpr int kFirstDqWarp = 7;
 // full rate; the 256-column accumulator is then single and the stages are K 64.
 template <int NT, bool TWO_ISSUERS = false>
 struct Ff2Cfg {
-    static_assert(!TWO_ISSUERS || NT == 128, "the two-issuer variant exists for 128-token tiles");
+    static_assert(!TWO_ISSUERS || NT <= 128, "the two-issuer variant exists for token tiles of 32, 64 and 128");
     static constexpr int kStageK = NT >= 256 ? 64 : 128;
     static constexpr int kRawBytes = kBlockM * kStageK / 2;   // int4 tile: 128 rows x kStageK/2 bytes
     // Small token tiles are HBM-bound: their weight stage spans two K units, so that every row
@@ -99,9 +99,10 @@ struct Ff2Cfg {
 #define XMOE_FF2_SPLIT 1
 #endif
 
+
     static constexpr int kWStages = NT == 128 ? (TWO_ISSUERS ? 8 : 12) : (NT == 64 ? XMOE_FF2_WS64 : (NT == 32 ? XMOE_FF2_WS32 : 16));  // weight ring (HBM latency)
     static constexpr int kBStages = NT >= 256 ? 4 : (NT >= 128 ? (TWO_ISSUERS ? 4 : 3) : (NT == 32 ? XMOE_FF2_BS32 : XMOE_FF2_BS64));  // token ring (L2 latency)
-    static constexpr int kIssuers = NT <= 64 ? 4 : (TWO_ISSUERS ? 2 : 1);         // MMA-issuing threads (K stages round-robin)
+    static constexpr int kIssuers = TWO_ISSUERS ? 2 : (NT <= 64 ? 4 : 1);         // MMA-issuing threads (K stages round-robin)
     static constexpr int kARing = NT >= 256 ? 8 : 4;          // expanded-weight buffers in tensor memory
     // Small token tiles hand a buffer over in two halves (K 64 each, own barriers): the issuer starts on the
     // first half while the second is still being expanded, and the dequant group gets the first half back
@@ -124,7 +125,7 @@ struct Ff2Cfg {
     // that it, too, always meets the same token and tensor-memory slots, whatever the tile lengths.
     // two accumulator sets where tensor memory has room (NT 128: 2 x 128 columns; NT 32: 2 x 4 issuers x 32): the
     // epilogue of one tile (or tile segment) overlaps the MMAs of the next
-    static constexpr int kAccStages = ((NT == 128 && !TWO_ISSUERS) || NT == 32) ? 2 : 1;
+    static constexpr int kAccStages = NT <= 64 ? 256 / (kIssuers * NT) : ((NT == 128 && !TWO_ISSUERS) ? 2 : 1);
     static constexpr int kFirstDq = kFirstDqWarp + (kIssuers - 1);
     static constexpr int kThreads = 32 * (kFirstDq + 4 * kDqGroups);
     static constexpr int kAccBase = kARing * kACols;          // accumulators follow the A ring
@@ -214,9 +215,10 @@ __global__ __launch_bounds__(Ff2Cfg<NT, TWO_ISSUERS>::kThreads, 1) void ff2_w4a1
     uint64_t* b_empty = b_full + 16;                       // [16] MMAs reading it retired
     uint64_t* adq_full = b_empty + 16;                     // [8]  expanded weights are in tensor memory
     uint64_t* adq_empty = adq_full + 8;                    // [8]  MMAs reading them retired
-    uint64_t* acc_full = adq_empty + 8;                    // [2]
-    uint64_t* acc_empty = acc_full + 2;                    // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* acc_full = adq_empty + 8;                    // [4]
+    uint64_t* acc_empty = acc_full + 4;                    // [4]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 4);
+    static_assert(kAccStages <= 4, "accumulator barrier arrays");
     volatile uint32_t* abort_flag = tmem_slot + 1;
     int* prefix = reinterpret_cast<int*>(tail + 768);
 
@@ -240,7 +242,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT, TWO_ISSUERS>::kThreads, 1) void ff2_w4a1
             mbar_init(&adq_full[s], 4);
             mbar_init(&adq_empty[s], 1);
         }
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kAccStages; ++s) {
             mbar_init(&acc_full[s], kIssuers);
             mbar_init(&acc_empty[s], 4);
         }
@@ -402,7 +404,7 @@ __global__ __launch_bounds__(Ff2Cfg<NT, TWO_ISSUERS>::kThreads, 1) void ff2_w4a1
                     if (NT <= 64) slab16 = n_valid <= 8 ? 64u : (n_valid <= 16 ? 128u : (uint32_t)kSlab16);
                     // two issuers keep the tensor pipe, not the issuing thread, busy: a ragged tile then runs with a
                     // narrower MMA N (its rows rounded up to 32; the columns beyond it are never stored)
-                    if (TWO_ISSUERS && n_valid < NT) idesc = umma_idesc_bf16(kBlockM, (uint32_t)((n_valid + 31) & ~31));
+                    if (NT == 128 && TWO_ISSUERS && n_valid < NT) idesc = umma_idesc_bf16(kBlockM, (uint32_t)((n_valid + 31) & ~31));
                 }
                 {
                     XMOE_T0();
@@ -724,8 +726,16 @@ int launch_ff2(const Ff2Args& a, cudaStream_t stream) {
     if (a.E_tot + 1 > kMaxExperts || a.H % 8 || a.I % 32) return XMOE_ERR_SHAPE;
     const bool split = a.split_partial != nullptr && a.split_flags != nullptr;
     switch (a.nt) {
-        case 32: return split ? launch_ff2_nt<32, true>(a, stream) : launch_ff2_nt<32, false>(a, stream);
-        case 64: return split ? launch_ff2_nt<64, true>(a, stream) : launch_ff2_nt<64, false>(a, stream);
+        // Small token tiles: four issuing threads (one accumulator set for 64 tokens, two for 32), or two issuing
+        // threads with twice the accumulator sets when K is short (<= 8 units): the epilogue then adds two partial
+        // sums instead of four, and with tiles of a few units it, not the MMAs, sets the pace (Qwen3 shape, 6 units,
+        // 512 tokens: 73 -> 55 us; with 23 or 112 units per tile two threads are 5-13 % slower than four).
+        case 32:
+            if (a.groups <= 8) return launch_ff2_nt<32, false, true>(a, stream);
+            return split ? launch_ff2_nt<32, true>(a, stream) : launch_ff2_nt<32, false>(a, stream);
+        case 64:
+            if (a.groups <= 8) return launch_ff2_nt<64, false, true>(a, stream);
+            return split ? launch_ff2_nt<64, true>(a, stream) : launch_ff2_nt<64, false>(a, stream);
         // 128-token tiles: with a long K (>= 12 units) two issuing threads, each with its own accumulator, beat one
         // thread with two accumulator sets (DeepSeek-V3 shape, 16 units: 917 against 970-1020 us at 2048 tokens, 704
         // against 994 us at 256); with a short K the overlapped epilogue wins (Qwen3 shape, 6 units: 275 against 383 us)
