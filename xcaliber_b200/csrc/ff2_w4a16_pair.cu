@@ -350,32 +350,60 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
             if (!mbar_wait_cluster(acc_full, tile_n & 1u, abort_flag, a.status, XMOE_DEV_TIMEOUT_ACC)) break;
             tc_fence_after();
             const int h = (t.wt * 2 + (int)rank) * kBlockM + q * 32 + lane;  // this lane's feature
+            const bool h_ok = h < a.H;
             const int n_valid = min(kTokTile, t.count - t.nt_idx * kTokTile);
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAccBase;
 #ifdef XMOE_TRACE
             const long long te0 = clock64();
 #endif
-            for (int c0 = set * 32; c0 < n_valid; c0 += 32 * kEpiSets) {
-                uint32_t v[32];
-                tmem_ld32(lane_addr + c0, v);
-                const int prow = t.row0 + c0 + lane;
-                unsigned long long my_row = 0ull;
-                if (c0 + lane < n_valid)
-                    my_row = a.row_dst ? a.row_dst[prow] : (unsigned long long)(uintptr_t)(out + (size_t)prow * a.H);
-                tmem_ld_wait();
+            // Halves of 16 tokens in two register sets: while one half is stored the next one is already on its way
+            // from tensor memory, and the accumulator goes back to the MMA thread as soon as the LAST half has been
+            // read, before it is stored.
+            const int c_first = set * 32;
+            bool released = false;
+            if (c_first < n_valid) {
+                uint32_t va[16], vb[16];
+                tmem_ld16(lane_addr + c_first, va);
+                for (int c0 = c_first; c0 < n_valid; c0 += 32 * kEpiSets) {
+                    const int prow = t.row0 + c0 + lane;
+                    unsigned long long my_row = 0ull;
+                    if (c0 + lane < n_valid)
+                        my_row = a.row_dst ? a.row_dst[prow] : (unsigned long long)(uintptr_t)(out + (size_t)prow * a.H);
+                    tmem_ld_wait();                          // va: tokens c0 .. c0 + 15
+                    tmem_ld16(lane_addr + c0 + 16, vb);      // tokens c0 + 16 .. c0 + 31, in flight during the stores of va
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const unsigned long long row = __shfl_sync(0xffffffffu, my_row, j);
-                    if (row && h < a.H)
-                        reinterpret_cast<uint16_t*>((uintptr_t)row)[h] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
+                    for (int j = 0; j < 16; ++j) {
+                        const unsigned long long row = __shfl_sync(0xffffffffu, my_row, j);
+                        if (row && h_ok)
+                            reinterpret_cast<uint16_t*>((uintptr_t)row)[h] = (uint16_t)f32_to_bf16_bits(__uint_as_float(va[j]));
+                    }
+                    tmem_ld_wait();                          // vb
+                    const int c_next = c0 + 32 * kEpiSets;
+                    if (c_next < n_valid) {
+                        tmem_ld16(lane_addr + c_next, va);   // next chunk's first half, in flight during the stores of vb
+                    } else {
+                        // every column this warp reads has been read
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+                        released = true;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const unsigned long long row = __shfl_sync(0xffffffffu, my_row, 16 + j);
+                        if (row && h_ok)
+                            reinterpret_cast<uint16_t*>((uintptr_t)row)[h] = (uint16_t)f32_to_bf16_bits(__uint_as_float(vb[j]));
+                    }
                 }
             }
 #ifdef XMOE_TRACE
             if (warp == 2 && lane == 0 && cluster_id < 148 && leader) g_ff2p_trace[cluster_id * 8 + 7] += clock64() - te0;
 #endif
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+            if (!released) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+            }
         }
     } else {
         // ------------------------------ dequantiser (my 128 rows -> my tensor memory) --
