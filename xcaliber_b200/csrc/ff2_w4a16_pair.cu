@@ -253,10 +253,10 @@ __global__ __launch_bounds__(kThreads, 1) void ff2_w4a16_pair_kernel(const __gri
             const uint32_t b_lo0 = umma_desc_lo_sw128(smem_u32(b_base));
             uint32_t tile_n = 0, s = 0, ph = 0, d = 0, dph = 0;
             bool ok = true;
+#ifdef XMOE_TRACE
             long long tw_b = 0, tw_bp = 0, tw_adq = 0, tw_acc = 0, t_issue = 0;
-            (void)tw_b; (void)tw_bp; (void)tw_adq; (void)tw_acc; (void)t_issue;
             const long long t_start = clock64();
-            (void)t_start;
+#endif
             for (int item = cluster_id; item < total_tiles && ok; item += n_clusters, ++tile_n) {
                 // the ragged last token tile of an expert runs with a narrower N (cost ~ N, floor at the
                 // issue rate): each CTA then stages N/2 of its rows instead of 128. Decoded before the wait for the
