@@ -79,3 +79,59 @@ def test_sigmoid_lut_matches_oracle(built_lib):
     finite = np.isfinite(ref)
     assert (got[finite] == ref[finite]).mean() > 0.9999
     assert np.abs(got[finite] - ref[finite]).max() <= 2 ** -24
+
+
+def _kwalk_lib(tmp_path_factory):
+    import subprocess
+
+    out = tmp_path_factory.mktemp("kwalk") / "libkwalk_host.so"
+    src = Path(__file__).resolve().parent / "kwalk_host.cpp"
+    subprocess.run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", str(src), "-o", str(out)], check=True)
+    lib = C.CDLL(str(out))
+    lib.kwalk_segments.argtypes = [C.c_int] * 5 + [C.POINTER(C.c_int), C.c_int]
+    lib.kwalk_segments.restype = C.c_int
+    return lib
+
+
+def test_k_walk_covers_every_unit_once(tmp_path_factory):
+    """The scheduler the FF2 kernel runs on the device (tiles cut along K, and whole tiles with a balanced stride),
+    compiled for the host: over many tile lists and grids every K unit of every tile belongs to exactly one segment,
+    a CTA's ring numbering (it0) counts the units it walked before, a non-final segment comes first, and the CTAs a
+    finishing segment names as helpers hold exactly the units before its own."""
+    lib = _kwalk_lib(tmp_path_factory)
+    buf = (C.c_int * (6 * 4096))()
+
+    def segments(tiles, k_walk, grid, cta, split):
+        n = lib.kwalk_segments(tiles, k_walk, grid, cta, split, buf, 4096)
+        assert 0 <= n <= 4096
+        return [tuple(buf[6 * i + j] for j in range(6)) for i in range(n)]
+
+    cases = [(t, k, g) for t in (1, 2, 3, 7, 64, 148, 149, 256, 300) for k in (2, 4, 6, 16, 24, 112) for g in (1, 4, 132, 148)]
+    for tiles, k_walk, grid in cases:
+        for split in (0, 1):
+            owner = {}
+            per_cta = {}
+            for cta in range(grid):
+                segs = per_cta[cta] = segments(tiles, k_walk, grid, cta, split)
+                walked = 0
+                for i, (tile, ks0, ks1, it0, first_helper, finishes) in enumerate(segs):
+                    assert 0 <= tile < tiles and 0 <= ks0 < ks1 <= k_walk
+                    assert it0 == walked, (tiles, k_walk, grid, cta, split, segs)
+                    walked += ks1 - ks0
+                    assert finishes == (ks1 == k_walk)
+                    assert finishes or i == 0, "a partial sum must not wait behind other work"
+                    if split:
+                        assert ks0 % 2 == 0, "a segment never starts inside a two-unit weight stage"
+                    for u in range(ks0, ks1):
+                        assert (tile, u) not in owner, "K unit covered twice"
+                        owner[(tile, u)] = cta
+            assert len(owner) == tiles * k_walk, "K unit not covered"
+            for cta, segs in per_cta.items():
+                for tile, ks0, ks1, it0, first_helper, finishes in segs:
+                    if not split or not finishes:
+                        continue
+                    helpers = sorted({owner[(tile, u)] for u in range(ks0)})
+                    assert helpers == list(range(first_helper, cta)), (tiles, k_walk, grid, cta, segs)
+                    for h in helpers:  # each helper holds ONE non-final segment of this tile
+                        hs = [s for s in per_cta[h] if s[0] == tile]
+                        assert len(hs) == 1 and hs[0][5] == 0
