@@ -107,7 +107,7 @@ def test_local_token_tile_rule():
     from xcaliber_b200.ep import local_token_tile
 
     assert local_token_tile(16 * 2, 4) == 32          # decode: 8 rows per expert
-    assert local_token_tile(128 * 2, 8) == 64         # 32 rows per expert
+    assert local_token_tile(128 * 2, 8) == 128        # 32 rows per expert
     assert local_token_tile(4096 * 2, 4) == 128       # prefill
-    assert local_token_tile(40, 1) == 64              # 40 rows on one expert: between the 20- and 48-row marks
-    assert local_token_tile(60, 1) == 64              # above 48 rows per expert but at most 64 rows in all
+    assert local_token_tile(40, 2) == 32              # 20 rows per expert: below the 24-row mark
+    assert local_token_tile(60, 1) == 128

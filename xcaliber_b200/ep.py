@@ -207,11 +207,9 @@ class PeerExchange:
 
 def local_token_tile(rows: int, e_local: int) -> int:
     """Token tile of the local pipeline from the rows a rank expects under balanced routing (the
-    library's own choice would see the receive buffer's capacity, world times larger)."""
-    avg = rows / max(e_local, 1)
-    if avg > 48.0:
-        return 128 if rows > 64 else 64
-    return 64 if avg > 20.0 else 32
+    library's own choice would see the receive buffer's capacity, world times larger): the library's rule,
+    128 from about 24 rows per expert on average, else 32."""
+    return 128 if rows / max(e_local, 1) >= 24.0 else 32
 
 
 class ExpertParallelMoE:
