@@ -173,7 +173,10 @@ int ff2_token_tile(const xmoe_config* c, int nt, size_t rows_in_use) {
     static const int min_inter = [] { const char* e = getenv("XMOE_FF2_T256_MIN_INTER"); return e ? atoi(e) : 2048; }();
     static const int min_rows = [] { const char* e = getenv("XMOE_FF2_T256_MIN_ROWS"); return e ? atoi(e) : 96; }();
     const size_t e_tot = (size_t)c->num_experts + c->num_shared_experts;
-    return (nt == 128 && c->inter >= min_inter && rows_in_use >= (size_t)min_rows * e_tot) ? 256 : nt;
+    // a short K (inter < min_inter) pays only with experts that fill the 256-token tiles several times over (Qwen3
+    // shape, 6 K units: 257 against 273 us at 512 rows per expert, 110 against 101 us at 128)
+    const size_t need = c->inter >= min_inter ? (size_t)min_rows : (size_t)384;
+    return (nt == 128 && rows_in_use >= need * e_tot) ? 256 : nt;
 }
 
 struct Layout {
@@ -269,7 +272,8 @@ int run_ff1(const void* w13_packed, const void* w13_sf, const float* w13_gs, con
     // prefill-sized experts run 256-token tiles on CTA pairs unless XMOE_FF1_PAIR=0
     const char* pair_env = getenv("XMOE_FF1_PAIR");
     const bool pair_enabled = !(pair_env && pair_env[0] == '0');
-    if (nt == 128 && pair_enabled && a.num_sms >= 2 && rows / (size_t)e_tot >= 320) return launch_ff1_pair(a, stream);
+    static const size_t pair_min_rows = [] { const char* e = getenv("XMOE_FF1_PAIR_MIN_ROWS"); return (size_t)(e ? atoi(e) : 320); }();
+    if (nt == 128 && pair_enabled && a.num_sms >= 2 && rows / (size_t)e_tot >= pair_min_rows) return launch_ff1_pair(a, stream);
     return launch_ff1(a, stream);
 }
 
