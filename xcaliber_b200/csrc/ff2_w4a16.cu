@@ -31,6 +31,8 @@
 // All mbarrier waits are bounded (see common.cuh).
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "tile_sched.cuh"
@@ -725,21 +727,25 @@ extern "C" int xmoe_ff2_trace_dump(long long* host_out) {
 int launch_ff2(const Ff2Args& a, cudaStream_t stream) {
     if (a.E_tot + 1 > kMaxExperts || a.H % 8 || a.I % 32) return XMOE_ERR_SHAPE;
     const bool split = a.split_partial != nullptr && a.split_flags != nullptr;
+    // K lengths (in units of 128) at which the two-issuer variants take over; the environment variables are for
+    // measurements
+    static const int small_two_max = [] { const char* e = getenv("XMOE_FF2_SMALL_TWO_MAX_GROUPS"); return e ? atoi(e) : 7; }();
+    static const int t128_two_min = [] { const char* e = getenv("XMOE_FF2_T128_TWO_MIN_GROUPS"); return e ? atoi(e) : 12; }();
     switch (a.nt) {
         // Small token tiles: four issuing threads (one accumulator set for 64 tokens, two for 32), or two issuing
-        // threads with twice the accumulator sets when K is short (<= 8 units): the epilogue then adds two partial
+        // threads with twice the accumulator sets when K is short (<= 7 units): the epilogue then adds two partial
         // sums instead of four, and with tiles of a few units it, not the MMAs, sets the pace (Qwen3 shape, 6 units,
-        // 512 tokens: 73 -> 55 us; with 23 or 112 units per tile two threads are 5-13 % slower than four).
+        // 512 tokens: 73 -> 55 us; with 8 units per tile two threads are 6 % slower than four, with 23 or 112 units 5-13 %).
         case 32:
-            if (a.groups <= 8) return launch_ff2_nt<32, false, true>(a, stream);
+            if (a.groups <= small_two_max) return launch_ff2_nt<32, false, true>(a, stream);
             return split ? launch_ff2_nt<32, true>(a, stream) : launch_ff2_nt<32, false>(a, stream);
         case 64:
-            if (a.groups <= 8) return launch_ff2_nt<64, false, true>(a, stream);
+            if (a.groups <= small_two_max) return launch_ff2_nt<64, false, true>(a, stream);
             return split ? launch_ff2_nt<64, true>(a, stream) : launch_ff2_nt<64, false>(a, stream);
         // 128-token tiles: with a long K (>= 12 units) two issuing threads, each with its own accumulator, beat one
         // thread with two accumulator sets (DeepSeek-V3 shape, 16 units: 917 against 970-1020 us at 2048 tokens, 704
         // against 994 us at 256); with a short K the overlapped epilogue wins (Qwen3 shape, 6 units: 275 against 383 us)
-        case 128: return a.groups >= 12 ? launch_ff2_nt<128, false, true>(a, stream) : launch_ff2_nt<128, false>(a, stream);
+        case 128: return a.groups >= t128_two_min ? launch_ff2_nt<128, false, true>(a, stream) : launch_ff2_nt<128, false>(a, stream);
         case 256: return launch_ff2_nt<256, false>(a, stream);
         default: return XMOE_ERR_SHAPE;
     }
