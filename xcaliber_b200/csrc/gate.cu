@@ -138,10 +138,10 @@ __global__ __launch_bounds__(kGateThreads, 1) void gate_logits_kernel(const __gr
                     if (token >= n) break;  // uniform across the warp
                     const uint16_t* row = tile + i * pitch;
                     if (ROUTE == 1)
-                        route_token_flat<false>(row, (uint32_t)lane, (uint32_t)token, es, r.topk_idx, tw, E, r.topk,
+                        route_token_flat<false, 8>(row, (uint32_t)lane, (uint32_t)token, es, r.topk_idx, tw, E, r.topk,
                                                 r.idx_stride, r.routed_scale, r.renorm);
                     else if (ROUTE == 2)
-                        route_token_flat<true>(row, (uint32_t)lane, (uint32_t)token, es, r.topk_idx, tw, E, r.topk,
+                        route_token_flat<true, 8>(row, (uint32_t)lane, (uint32_t)token, es, r.topk_idx, tw, E, r.topk,
                                                r.idx_stride, r.routed_scale, r.renorm);
                     else
                         route_token_grouped<8>(row, (uint32_t)lane, (uint32_t)token, r.lut, r.bias, es, r.topk_idx, tw, E,

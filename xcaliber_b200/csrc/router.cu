@@ -18,15 +18,15 @@ namespace xmoe {
 // owns experts l + 32*j; every composite key lives in a register, so logits are read
 // from HBM exactly once.
 // ------------------------------------------------------------------------------------
-template <bool SIGMOID>
+template <bool SIGMOID, int J>
 __global__ __launch_bounds__(256) void router_topk_flat_kernel(
     const uint16_t* __restrict__ logits, const uint16_t* __restrict__ expert_scale,
     int32_t* __restrict__ topk_idx, uint16_t* __restrict__ topk_w,
     int N, int E, int topk, int idx_stride, float routed_scale, int renorm) {
     const uint32_t token = blockIdx.x * 8u + (threadIdx.x >> 5);
     if (token >= (uint32_t)N) return;
-    route_token_flat<SIGMOID>(logits + (size_t)token * E, lane_id(), token, expert_scale, topk_idx, topk_w, E, topk,
-                              idx_stride, routed_scale, renorm);
+    route_token_flat<SIGMOID, J>(logits + (size_t)token * E, lane_id(), token, expert_scale, topk_idx, topk_w, E, topk,
+                                 idx_stride, routed_scale, renorm);
 }
 
 // Group-limited sigmoid routing with a selection bias: route_token_grouped (router_core.cuh)
@@ -239,12 +239,23 @@ int launch_router_topk(const RouterArgs& a, cudaStream_t stream) {
             router_topk_grouped_kernel<32><<<grid, block, 0, stream>>>(logits, a.lut, a.bias, es, a.topk_idx,
                                                                (uint16_t*)a.topk_w, a.N, a.E, a.topk, k_eff,
                                                                a.n_group, a.topk_group, a.routed_scale, a.renorm);
-    } else if (a.scoring == 1) {
-        router_topk_flat_kernel<true><<<grid, block, 0, stream>>>(logits, es, a.topk_idx, (uint16_t*)a.topk_w,
-                                                                  a.N, a.E, a.topk, k_eff, a.routed_scale, a.renorm);
     } else {
-        router_topk_flat_kernel<false><<<grid, block, 0, stream>>>(logits, es, a.topk_idx, (uint16_t*)a.topk_w,
-                                                                   a.N, a.E, a.topk, k_eff, a.routed_scale, a.renorm);
+        // slots per lane: the smallest of 1, 2, 4, 8, 32 that holds E / 32
+#define XMOE_FLAT(SIG, J)                                                                                          \
+    router_topk_flat_kernel<SIG, J><<<grid, block, 0, stream>>>(logits, es, a.topk_idx, (uint16_t*)a.topk_w, a.N, a.E, \
+                                                                a.topk, k_eff, a.routed_scale, a.renorm)
+#define XMOE_FLAT_J(SIG)                  \
+    do {                                  \
+        if (a.E <= 32) XMOE_FLAT(SIG, 1);      \
+        else if (a.E <= 64) XMOE_FLAT(SIG, 2);  \
+        else if (a.E <= 128) XMOE_FLAT(SIG, 4); \
+        else if (a.E <= 256) XMOE_FLAT(SIG, 8); \
+        else XMOE_FLAT(SIG, 32);                \
+    } while (0)
+        if (a.scoring == 1) XMOE_FLAT_J(true);
+        else XMOE_FLAT_J(false);
+#undef XMOE_FLAT_J
+#undef XMOE_FLAT
     }
     return cudaGetLastError() == cudaSuccess ? XMOE_OK : XMOE_ERR_CUDA;
 }

@@ -10,17 +10,19 @@
 
 namespace xmoe {
 
-// One token, one warp: `row` = the token's E bf16 logits (global or shared memory), lane l owns experts l + 32*j;
+// One token, one warp: `row` = the token's E <= 32 * J bf16 logits (global or shared memory), lane l owns experts l + 32*j;
 // every composite key lives in a register, so the logits are read exactly once. Writes slots [0, topk) of
 // topk_idx / topk_w at token * idx_stride.
-template <bool SIGMOID>
+// J = slots per lane (ceil(E / 32) rounded up to 1, 2, 4, 8 or 32): the loops over a lane's experts are fully unrolled,
+// and a 128-expert router should not walk 32 slots of which 28 are empty.
+template <bool SIGMOID, int J>
 __device__ __forceinline__ void route_token_flat(const uint16_t* row, uint32_t lane, uint32_t token,
                                                  const uint16_t* __restrict__ expert_scale,
                                                  int32_t* __restrict__ topk_idx, uint16_t* __restrict__ topk_w, int E,
                                                  int topk, int idx_stride, float routed_scale, int renorm) {
-    uint32_t keys[32];
+    uint32_t keys[J];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < J; ++j) {
         const uint32_t e = lane + 32u * j;
         uint32_t key = 0u;
         if (e < (uint32_t)E) {
@@ -38,11 +40,11 @@ __device__ __forceinline__ void route_token_flat(const uint16_t* row, uint32_t l
     if (!SIGMOID && !renorm) {
         uint32_t best = 0u;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) best = max(best, keys[j]);
+        for (int j = 0; j < J; ++j) best = max(best, keys[j]);
         const uint32_t o1 = __reduce_max_sync(0xffffffffu, best) >> 16;
         const float x1 = bf16_bits_to_f32((o1 & 0x8000u) ? (o1 & 0x7fffu) : (~o1 & 0xffffu));
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < J; ++j) {
             if (lane + 32u * j < (uint32_t)E) {
                 const uint32_t o = keys[j] >> 16;
                 const float xe = bf16_bits_to_f32((o & 0x8000u) ? (o & 0x7fffu) : (~o & 0xffffu));
@@ -57,12 +59,12 @@ __device__ __forceinline__ void route_token_flat(const uint16_t* row, uint32_t l
     for (int r = 0; r < topk; ++r) {
         uint32_t best = 0u;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) best = max(best, keys[j]);
+        for (int j = 0; j < J; ++j) best = max(best, keys[j]);
         const uint32_t winner = __reduce_max_sync(0xffffffffu, best);
         const uint32_t e = 0xffffu - (winner & 0xffffu);
         if ((e & 31u) == lane) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
+            for (int j = 0; j < J; ++j)
                 if ((uint32_t)j == (e >> 5)) keys[j] = 0u;
         }
         if (lane == (uint32_t)r) selected = winner;
