@@ -20,7 +20,7 @@ CSRC = Path(__file__).resolve().parent
 PKG = CSRC.parent
 LIB = PKG / "libxmoe_b200.so"
 TORCH_OPS_LIB = PKG / "libxmoe_torch_ops.so"
-SOURCES = ["router.cu", "act_quant.cu", "misc.cu", "ff1_nvfp4.cu", "ff1_nvfp4_prefill.cu", "ff1_nvfp4_pair.cu", "ff2_w4a16.cu", "ff2_w4a16_pair.cu", "ep_p2p.cu", "probe.cu", "gate.cu", "api.cu"]
+SOURCES = ["router.cu", "act_quant.cu", "misc.cu", "ff1_nvfp4.cu", "ff1_nvfp4_prefill.cu", "ff1_nvfp4_pair.cu", "ff2_w4a16.cu", "ff2_w4a16_pair.cu", "ep_p2p.cu", "probe.cu", "gate.cu", "decode_front.cu", "api.cu"]
 HEADERS = ["common.cuh", "kernels.h", "tile_sched.cuh", "cluster.cuh", "nvfp4_quant.cuh", "router_core.cuh", "k_walk.h", "../../include/xmoe_b200.h"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

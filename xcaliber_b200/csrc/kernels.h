@@ -76,6 +76,29 @@ struct QuantArgs {
     bool fused_amax;         // small batches: the kernel takes the amax of x itself and writes *scale (no amax kernel)
 };
 
+// The front of the layer in one launch for decode-sized batches (decode_front.cu): amax + scale, router, permutation,
+// NVFP4 packets, for flat (softmax or sigmoid) routing. Fields as in RouterArgs / PackArgs / QuantArgs; idx_stride of
+// the routing arrays = topk + n_shared.
+struct FrontArgs {
+    const void* x;             // bf16 [N, H]
+    const void* logits;        // bf16 [N, E]
+    const void* expert_scale;  // bf16 [E] or null
+    ActScale* scale;           // out: {XGS, XGSINV, amax}
+    int32_t* topk_idx;
+    uint16_t* topk_w;
+    int32_t* topk_off;
+    int32_t* topk_row;
+    int32_t* counts;
+    int32_t* offsets;
+    int32_t* row_token;
+    uint16_t* row_weight;
+    uint8_t* xq;
+    uint8_t* sfx;
+    int N, E, topk, n_shared, H, kb_pad, nt;
+    int scoring, renorm;
+    float routed_scale;
+};
+
 struct Ff1Args {
     CUtensorMap tm_w;  // u8 [E_tot*2I, H/2], box 128 B x 128 rows, 128-byte swizzle
     CUtensorMap tm_x;  // u8 [R_cap, H/2], box 128 B x NT rows
@@ -149,6 +172,8 @@ int launch_route_pack(const PackArgs& a, cudaStream_t stream);
 int route_pack_static_max_tokens();
 int launch_route_pack_static(PackArgs a, cudaStream_t stream);  // scratch = a fixed device array of the library
 int launch_act_amax(const AmaxArgs& a, cudaStream_t stream);
+bool decode_front_applies(int N, int E, int topk, int n_shared, int H);
+int launch_decode_front(const FrontArgs& a, cudaStream_t stream);
 int launch_act_scale_from_amax(const float* amax, float* scale, cudaStream_t stream);
 int launch_act_quant(const QuantArgs& a, cudaStream_t stream);
 // rows already quantised by a peer: codes [N, H/2] + block scales [N, H/16] -> a.xq / a.sfx (a.x and a.scale unused)
