@@ -166,12 +166,12 @@ int pick_token_tile(const xmoe_config* c, int n) {
 // FF2 may use a wider token tile than FF1: the 256-token tile (CTA pairs) keeps the bf16 pipe at its full rate
 // (an N = 128 MMA is bound by the issuing thread, not by the pipe), but its accumulator is single, so the
 // epilogue is not overlapped: it pays with a long K (I >= min_inter) and with experts that fill the tile
-// (average rows per expert >= min_rows = 96: at 128 rows per expert the pair kernel still wins, 385 against
-// 416 us on the gpt-oss shape; at 72 it loses, 1163 against 979 us on the DeepSeek-V3 shape). `rows_in_use`
-// = N * k_eff.
+// (average rows per expert >= min_rows = 112; FF2 time in us, pair against single-CTA kernel: gpt-oss shape at 96 rows
+// per expert 323 / 257, at 128 rows 351 / 364; Mixtral shape at 128 rows 145 / 150, at 192 rows 161 / 196; DeepSeek-V3
+// shape at 72 rows 1050 / 845, at 143 rows 1275 / 1503). `rows_in_use` = N * k_eff.
 int ff2_token_tile(const xmoe_config* c, int nt, size_t rows_in_use) {
     static const int min_inter = [] { const char* e = getenv("XMOE_FF2_T256_MIN_INTER"); return e ? atoi(e) : 2048; }();
-    static const int min_rows = [] { const char* e = getenv("XMOE_FF2_T256_MIN_ROWS"); return e ? atoi(e) : 96; }();
+    static const int min_rows = [] { const char* e = getenv("XMOE_FF2_T256_MIN_ROWS"); return e ? atoi(e) : 112; }();
     const size_t e_tot = (size_t)c->num_experts + c->num_shared_experts;
     // a short K (inter < min_inter) pays only with experts that fill the 256-token tiles several times over (Qwen3
     // shape, 6 K units: 257 against 273 us at 512 rows per expert, 110 against 101 us at 128)
