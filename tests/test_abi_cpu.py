@@ -135,3 +135,21 @@ def test_k_walk_covers_every_unit_once(tmp_path_factory):
                     for h in helpers:  # each helper holds ONE non-final segment of this tile
                         hs = [s for s in per_cta[h] if s[0] == tile]
                         assert len(hs) == 1 and hs[0][5] == 0
+
+
+@pytest.mark.parametrize("shape,n,tile", [
+    ("mixtral", 16, 32), ("mixtral", 64, 32), ("mixtral", 128, 128), ("mixtral", 4096, 128),
+    ("qwen3", 256, 32), ("qwen3", 512, 128), ("gptoss", 512, 32), ("gptoss", 1024, 128),
+    # shared experts take every token, but the routed experts decide: 16 rows per routed expert at 512 tokens
+    ("dsv3", 16, 32), ("dsv3", 512, 32), ("dsv3", 1024, 128),
+])
+def test_token_tile_rule(built_lib, shape, n, tile):
+    """The token tile a call pads every expert's rows to: 128 from 24 rows per routed expert on average, else 32
+    (the workspace view reports the library's choice; nothing here touches the GPU)."""
+    cfg = ops.make_config(synth.SHAPES[shape])
+    nbytes = built_lib.xmoe_workspace_bytes(C.byref(cfg), n)
+    view = _lib.XMoEWorkspaceView()
+    fake = 1 << 20  # only addresses are computed
+    assert built_lib.xmoe_workspace_view_get(C.byref(cfg), n, C.c_void_p(fake), nbytes, C.byref(view)) == 0
+    assert view.token_tile == tile
+    assert view.packed_rows % 128 == 0 and view.k_eff == cfg.top_k + cfg.num_shared_experts
